@@ -1,0 +1,438 @@
+"""Benchmark of the VSA forward+backward hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+
+One "step" is one forward+backward of the whole operator over this rank's share of
+the workload.  The default workload is the 92,160-token / block-64 / topk-180 shape
+``[B=2,H=40,L=92160,D=128]`` bf16 with all blocks full; its 80 (batch, head) slices
+are partitioned contiguously across the N ranks with no data-path collective (heads
+are independent), so total work is fixed and scaling is "strong".  Inputs are
+synthetic N(0,1), generated per (batch, head) slice from ``seed + slice`` so every
+sharding sees identical data.
+
+The JSON line (printed by rank 0) carries: ``value`` = useful sparse TFLOP/s over all
+ranks with inputs resident in HBM (useful FLOPs = 14*B*H*L*topk*be*D per call);
+``e2e`` = the same through the public API with pinned host buffers copied in and the
+results copied out inside the timed region; ``roofline`` for the dominant kernel
+from CUDA events recorded around every launch of the timed steps; ``cpu_baseline``
+= the CPU oracle timed on a bounded sample of the same workload; SM clocks sampled
+during the timed region.
+
+``--impl reference`` times the CPU restatement of the reference algorithm (the
+oracle) on the host cores on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, L, D, block_size, topk, gate, ragged)
+    "c5_92k_be64_tk180": dict(B=2, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False),
+    "c2_16k_be64_tk32_gate": dict(B=1, H=12, L=16384, D=128, block_size=(4, 4, 4), topk=32, gate=True),
+    "small_8k_be64_tk16": dict(B=1, H=8, L=8192, D=128, block_size=(4, 4, 4), topk=16, gate=False),
+}
+DEFAULT_WORKLOAD = "c5_92k_be64_tk180"
+SEED = 1234
+
+
+def useful_flops(slices: int, L: int, topk: int, be: int, D: int) -> float:
+    """fwd 4*be^2*D + bwd 10*be^2*D per (query block, key block) edge."""
+    return 14.0 * slices * L * topk * be * D
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(tflops=float(p.get("bf16_tflops_sustained", p.get("bf16_tflops"))), hbm=float(p["hbm_gbs"]),
+                    source="measured (MEASURED_PEAKS.json, sustained bf16)")
+    return dict(tflops=1400.0, hbm=6650.0, source="fallback (earlier pool measurement, sustained bf16)")
+
+
+# --------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU arm (oracle port of the reference algorithm on a bounded sample)
+# --------------------------------------------------------------------------------------------
+def cpu_sample_setup(cfg, q_blocks: int):
+    """One (batch, head) slice of the workload: full-length K/V, a chunk of ``q_blocks`` query blocks.
+
+    The pooled branch (block means, scores, Top-K) runs over the whole slice; the fine
+    branch, which carries all the counted FLOPs, runs on the chunk.
+    """
+    import torch
+    from oracle import vsa_oracle as O
+
+    be = O.block_elements(cfg["block_size"])
+    L, D, tk = cfg["L"], cfg["D"], cfg["topk"]
+    g = torch.Generator().manual_seed(SEED)
+    q = torch.randn(1, 1, L, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(1, 1, L, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, 1, L, D, generator=g).to(torch.bfloat16)
+    sizes = torch.full((L // be,), be)
+    dout = torch.randn(1, 1, q_blocks * be, D, generator=g)
+
+    def step():
+        scale = D ** -0.5
+        kl, vl = k.clone().requires_grad_(), v.clone().requires_grad_()
+        ql = q.clone().requires_grad_()
+        scores, out_c = O.coarse_compact(ql, kl, vl, sizes, sizes, be, scale)
+        sel = O.select_topk(scores, tk)[:, :, :q_blocks]
+        qs = ql[:, :, :q_blocks * be]
+        out_s = O.sparse_attention(qs, kl, vl, sel, sizes, be, scale, q_blocks_per_chunk=8)
+        out = O.combine(out_s, out_c[:, :, :q_blocks], None, be, torch.float32)
+        out.backward(dout)
+        return out
+
+    flops = useful_flops(1, q_blocks * be, tk, be, D)
+    sample = (f"oracle (CPU restatement of torch_vsa), 1 of {cfg['B'] * cfg['H']} (batch,head) slices, pooled branch "
+              f"on all {L} tokens, fine branch fwd+bwd on the first {q_blocks} of {L // be} query blocks "
+              f"(topk {tk}, block {be}, D {D}), bf16 inputs, fp32 fine math")
+    return step, flops, sample
+
+
+def run_cpu(cfg, steps: int, warmup: int, q_blocks: int = 64):
+    import torch
+    step, flops, sample = cpu_sample_setup(cfg, q_blocks)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(1, steps)
+    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+                sample=sample, ms_per_step=dt * 1e3)
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+def make_slices(cfg, first: int, count: int, device):
+    """q, k, v, dout (and gate) for ``count`` (batch, head) slices starting at ``first``: [1, count, L, D]."""
+    import torch
+    L, D = cfg["L"], cfg["D"]
+    names = ["q", "k", "v", "dout"] + (["gate"] if cfg["gate"] else [])
+    out = {n: torch.empty((1, count, L, D), device=device, dtype=torch.bfloat16) for n in names}
+    gen = torch.Generator(device=device)
+    for i in range(count):
+        gen.manual_seed(SEED + first + i)
+        for n in names:
+            x = torch.randn((L, D), generator=gen, device=device, dtype=torch.float32)
+            if n == "gate":
+                x = torch.sigmoid(x)
+            out[n][0, i] = x.to(torch.bfloat16)
+    return out
+
+
+class KernelTimer:
+    """CUDA events around every C-ABI call while enabled (hooked into simple_vsa_b200._lib.call)."""
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.events = {}
+        self.pending = {}
+
+    def __call__(self, name, phase, stream):
+        ev = self.torch.cuda.Event(enable_timing=True)
+        ev.record(self.torch.cuda.current_stream())
+        if phase == "start":
+            self.pending[name] = ev
+        else:
+            self.events.setdefault(name, []).append((self.pending.pop(name), ev))
+
+    def summary(self):
+        out = {}
+        for name, pairs in self.events.items():
+            ms = [a.elapsed_time(b) for a, b in pairs]
+            out[name] = dict(launches=len(ms), total_ms=sum(ms), avg_ms=sum(ms) / len(ms))
+        return out
+
+
+def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    import simple_vsa_b200 as V
+    from simple_vsa_b200 import _lib
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    be = V.as_block_elements(cfg["block_size"])
+    L, D, tk = cfg["L"], cfg["D"], cfg["topk"]
+    total_slices = cfg["B"] * cfg["H"]
+    per = total_slices // world
+    extra = total_slices % world
+    count = per + (1 if rank < extra else 0)
+    first = rank * per + min(rank, extra)
+    sizes = torch.full((L // be,), be, dtype=torch.int32, device=dev)
+
+    data = make_slices(cfg, first, count, dev)
+    q, k, v, dout = data["q"], data["k"], data["v"], data["dout"]
+    gate = data.get("gate")
+
+    def fwd_bwd(q_, k_, v_, gate_, dout_):
+        q_.grad = k_.grad = v_.grad = None
+        if gate_ is not None:
+            gate_.grad = None
+        out = V.b200_vsa(q_, k_, v_, sizes, sizes, tk, cfg["block_size"], gate_)
+        out.backward(dout_)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    leaves = [t.requires_grad_() for t in (q, k, v)]
+    gl = gate.requires_grad_() if gate is not None else None
+    for _ in range(args.warmup):
+        fwd_bwd(*leaves, gl, dout)
+    barrier()
+
+    # ---- device-resident timing, every kernel bracketed by events ----
+    timer = KernelTimer()
+    sampler = ClockSampler(local_rank)
+    launches_before = _lib.lib.vsa_launch_count()
+    if rank == 0:
+        sampler.start()
+    _lib.recorder = timer
+    barrier()
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for _ in range(args.steps):
+        fwd_bwd(*leaves, gl, dout)
+    t_stop.record()
+    barrier()
+    _lib.recorder = None
+    clocks = sampler.stop() if rank == 0 else None
+    launches = _lib.lib.vsa_launch_count() - launches_before
+    ms_dev = t_start.elapsed_time(t_stop) / args.steps
+    kernels = timer.summary()
+
+    # ---- end to end: pinned host buffers in, results out, inside the timed region ----
+    names = ["q", "k", "v", "dout"] + (["gate"] if gate is not None else [])
+    host_in = {n: torch.empty(data[n].shape, dtype=torch.bfloat16, pin_memory=True) for n in names}
+    for n in names:
+        host_in[n].copy_(data[n].detach())
+    out_names = ["out", "dq", "dk", "dv"] + (["dgate"] if gate is not None else [])
+    host_out = {n: torch.empty(q.shape, dtype=torch.bfloat16, pin_memory=True) for n in out_names}
+    del data, q, k, v, dout, gate, leaves, gl
+    torch.cuda.empty_cache()
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+
+    def e2e_step():
+        dv_ = {n: host_in[n].to(dev, non_blocking=True) for n in names}
+        ql, kl, vl = (dv_[n].requires_grad_() for n in ("q", "k", "v"))
+        g_ = dv_["gate"].requires_grad_() if "gate" in dv_ else None
+        out = fwd_bwd(ql, kl, vl, g_, dv_["dout"])
+        host_out["out"].copy_(out.detach(), non_blocking=True)
+        host_out["dq"].copy_(ql.grad, non_blocking=True)
+        host_out["dk"].copy_(kl.grad, non_blocking=True)
+        host_out["dv"].copy_(vl.grad, non_blocking=True)
+        if g_ is not None:
+            host_out["dgate"].copy_(g_.grad, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e_stop.record()
+    barrier()
+    ms_e2e = e_start.elapsed_time(e_stop) / e2e_steps
+    checksum = float(host_out["out"][0, 0, :64].float().abs().sum())
+
+    # ---- max over ranks ----
+    if world > 1:
+        t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = float(t[0]), float(t[1])
+        lt = torch.tensor([launches], device=dev, dtype=torch.int64)
+        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+        launches = int(lt[0])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    flops_total = useful_flops(total_slices, L, tk, be, D)
+    peaks = measured_peaks()
+    # dominant kernel by total device time
+    fine = {n: kernels[n] for n in ("vsa_sparse_fwd", "vsa_sparse_bwd_dq", "vsa_sparse_bwd_dkdv") if n in kernels}
+    top = max(fine, key=lambda n: fine[n]["total_ms"])
+    # GEMM FLOPs the kernel's algorithm performs per edge: forward S,O = 4; dQ pass S,dP,dQ = 6; dK/dV pass S,dP,dK,dV = 8
+    per_edge = {"vsa_sparse_fwd": 4, "vsa_sparse_bwd_dq": 6, "vsa_sparse_bwd_dkdv": 8}[top]
+    edges = count * (L // be) * tk
+    flops_launch = per_edge * float(be) * be * D * edges
+    achieved = flops_launch / (fine[top]["avg_ms"] * 1e-3) / 1e12
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as fh:
+            tj = json.load(fh)
+        if top in tj:
+            traffic = tj[top]["dram_bytes_per_edge"] * edges
+    step_total = sum(kv["total_ms"] for kv in kernels.values())
+    shares = {n: round(kv["total_ms"] / step_total, 4) for n, kv in sorted(kernels.items())}
+
+    cpu = run_cpu(cfg, steps=args.cpu_steps, warmup=1) if world == 1 and not args.no_cpu else None
+    T = count * L * D * 2
+    n_in, n_out = len(names), len(out_names)
+    line = {
+        "metric": "VSA fwd+bwd useful TFLOPS, 92k tok blk64 bf16" if args.workload == DEFAULT_WORKLOAD
+                  else f"VSA fwd+bwd useful TFLOPS ({args.workload})",
+        "value": flops_total / (ms_dev * 1e-3) / 1e12,
+        "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_dev,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic N(0,1), seeded per (batch,head) slice; random routes come from the operator's own Top-K",
+        "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], L, D], "block_elements": be,
+                   "topk": tk, "gate": cfg["gate"], "slices_per_gpu": count,
+                   "parallelism": f"(batch,head) slices partitioned over {world} GPU(s), no collective",
+                   "l2": "inputs per GPU (%.2f GB) are larger than L2; no flush" % (4 * T / 1e9),
+                   "useful_flops_per_call": flops_total},
+        "impl": "b200",
+        "e2e": {"value": flops_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                "steps": e2e_steps, "h2d_bytes_per_step": n_in * T, "d2h_bytes_per_step": n_out * T,
+                "checksum": checksum},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["tflops"],
+                     "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": traffic,
+                     "peak_source": peaks["source"], "avg_launch_ms": fine[top]["avg_ms"],
+                     "gemm_flops_per_edge_over_be2D": per_edge,
+                     "useful_frac_whole_step": flops_total / world / (ms_dev * 1e-3) / 1e12 / peaks["tflops"]},
+        "kernel_time_share": shares,
+        "kernel_avg_ms": {n: round(kv["avg_ms"], 4) for n, kv in sorted(kernels.items())},
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        import torch
+        from oracle import vsa_oracle as O
+        res = run_cpu(cfg, steps=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
+        be = O.block_elements(cfg["block_size"])
+        line = {"metric": "VSA fwd+bwd useful TFLOPS, 92k tok blk64 bf16" if args.workload == DEFAULT_WORKLOAD
+                else f"VSA fwd+bwd useful TFLOPS ({args.workload})",
+                "value": res["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1), seeded",
+                "impl": "reference",
+                "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], cfg["L"], cfg["D"]],
+                           "block_elements": be, "topk": cfg["topk"], "gate": cfg["gate"]},
+                "cpu_baseline": {k_: res[k_] for k_ in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line), flush=True)
+        return
+
+    if args.gpus > 1 and world == 1:
+        # launched plainly with --gpus N: re-launch under torchrun, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29533"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    if world != args.gpus:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
+    run_gpu(args, cfg, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,163 @@
+/*
+ * vsa_b200.h -- C ABI of the B200 Video Sparse Attention kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), launches on that stream without
+ * synchronising the host, and returns 0 on success or a negative vsa_status.
+ * Nothing is allocated by the library: outputs and scratch buffers are the
+ * caller's.  Nothing throws across the boundary; vsa_last_error_string()
+ * returns the text of the calling thread's most recent failure.
+ *
+ * Layouts (all contiguous, row-major):
+ *   q, out, dout, dq, gate, dgate   [BH, Lq,  D]     BH = batch * heads
+ *   k, v, dk, dv                    [BH, Lkv, D]
+ *   pooled q / k / v and their grads [BH, Qb | Kb, D], Qb = Lq/be, Kb = Lkv/be
+ *   scores, probs                   [BH, Qb, Kb]
+ *   selected                        [BH, Qb, topk]   int32 key-block ids
+ *   kv_sizes [Kb], q_sizes [Qb]     int32 valid tokens per block (shared by all BH)
+ *   lse2, delta                     [BH, Lq]         fp32
+ *   counts, offsets                 [BH, Kb]         int32 (CSR of key block -> query blocks)
+ *   inverse                         [BH, Qb*topk]    int32 query-block ids grouped by key block
+ *
+ * dtype: VSA_BF16 (tensor-core kernels for D = 128 and be = 64 or 256, scalar
+ * kernels otherwise) or VSA_F32 (scalar kernels, the fp32 validation mode).
+ *
+ * Each comment names the function of the reference project (path inside that
+ * project : lines) whose work the entry point replaces.
+ */
+#ifndef VSA_B200_H_
+#define VSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum vsa_status {
+  VSA_OK = 0,
+  VSA_ERR_BAD_ARGUMENT = -1,   /* null pointer, non-positive size, topk out of range ... */
+  VSA_ERR_UNSUPPORTED = -2,    /* shape or dtype outside what the kernels cover */
+  VSA_ERR_LAUNCH = -3,         /* the CUDA runtime refused the launch */
+  VSA_ERR_DEVICE_TIMEOUT = -4  /* a bounded device-side wait ran out */
+} vsa_status;
+
+typedef enum vsa_dtype { VSA_BF16 = 0, VSA_F32 = 1 } vsa_dtype;
+
+/* Text of the last error on the calling thread ("" if none). */
+const char* vsa_last_error_string(void);
+
+/* Library version as major*10000 + minor*100 + patch. */
+int vsa_version(void);
+
+/* Number of kernels this library has launched in the process so far (all threads). */
+int64_t vsa_launch_count(void);
+
+/* Padding-aware block means of q, k and v in ONE pass: fp32 sum of the first
+ * sizes[b] tokens / max(sizes[b],1), rounded to dtype.
+ * Replaces block_mean / fused_block_mean x3: vsa/common.py:55-82,
+ * vsa/fused_common.py:20-59,106-144. */
+int vsa_block_mean3_fwd(const void* q, const void* k, const void* v,
+                        const int32_t* q_sizes, const int32_t* kv_sizes,
+                        void* q_mean, void* k_mean, void* v_mean,
+                        int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
+                        int dtype, void* stream);
+
+/* Single-tensor form of the above (x [BH,L,D] -> mean [BH,L/be,D]). */
+int vsa_block_mean_fwd(const void* x, const int32_t* sizes, void* mean,
+                       int64_t BH, int64_t L, int D, int be, int dtype, void* stream);
+
+/* Block-mean backward folded into the accumulation autograd would do:
+ * dx[t] += dmean[block]/max(size,1) for t < size (padding rows untouched).
+ * Replaces _block_mean_backward_kernel + AccumulateGrad add:
+ * vsa/fused_common.py:62-103,146-172. */
+int vsa_block_mean_bwd_accumulate(void* dx, const void* dmean, const int32_t* sizes,
+                                  int64_t BH, int64_t L, int D, int be,
+                                  int dtype, void* stream);
+
+/* Stand-alone block-mean backward: dx[t] = dmean[block]/max(size,1) for t < size, else 0. */
+int vsa_block_mean_bwd(void* dx, const void* dmean, const int32_t* sizes,
+                       int64_t BH, int64_t L, int D, int be, int dtype, void* stream);
+
+/* Pooled attention: scores = round(round(q_mean k_mean^T) * scale), probs =
+ * round(softmax(scores)), out_c = round(probs v_mean); every rounding to dtype.
+ * Replaces coarse_branch_compact's matmul/softmax/matmul: vsa/common.py:164-166. */
+int vsa_coarse_fwd(const void* q_mean, const void* k_mean, const void* v_mean,
+                   void* scores, void* probs, void* out_c,
+                   int64_t BH, int Qb, int Kb, int D, float scale,
+                   int dtype, void* stream);
+
+/* Top-K key blocks per query block from the pooled scores; ids are written in
+ * ascending order, ties broken towards the lower id.
+ * Replaces scores.topk(...).indices: vsa/torch_impl.py:85, vsa/triton_impl.py:1710. */
+int vsa_topk(const void* scores, int32_t* selected,
+             int64_t rows, int Kb, int topk, int dtype, void* stream);
+
+/* Backward of the pooled attention.  dscores_ws is scratch [BH,Qb,Kb] of dtype,
+ * rowdot_ws is fp32 scratch [BH,Qb].
+ * Replaces autograd of vsa/common.py:164-166. */
+int vsa_coarse_bwd(const void* d_out_c, const void* out_c,
+                   const void* q_mean, const void* k_mean, const void* v_mean,
+                   const void* probs, void* dscores_ws, float* rowdot_ws,
+                   void* dq_mean, void* dk_mean, void* dv_mean,
+                   int64_t BH, int Qb, int Kb, int D, float scale,
+                   int dtype, void* stream);
+
+/* Fine attention of each query block over the valid tokens of its selected key
+ * blocks; lse2 (may be NULL) receives row_max + log2(row_sum) of the scores
+ * times scale*log2(e).
+ * Replaces _triton_sparse_attention_forward and both forward kernels:
+ * vsa/triton_impl.py:39-355,358-473 (oracle form: vsa/torch_impl.py:86-106). */
+int vsa_sparse_fwd(const void* q, const void* k, const void* v,
+                   const int32_t* selected, const int32_t* kv_sizes,
+                   void* out, float* lse2,
+                   int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                   float scale, int dtype, void* stream);
+
+/* CSR of key block -> query blocks from the routing table, built on the device
+ * by count / scan / scatter with exactly Qb*topk stored edges per BH slice.
+ * cursor_ws is int32 scratch [BH,Kb].  Order inside a key row is unspecified.
+ * Replaces _invert_indices and its two kernels: vsa/triton_impl.py:476-595. */
+int vsa_route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets,
+                     int32_t* inverse, int32_t* cursor_ws,
+                     int64_t BH, int Qb, int Kb, int topk, void* stream);
+
+/* Query-owned backward: delta = rowsum(out_s * dout) (written to delta, which
+ * vsa_sparse_bwd_dkdv reads) and dq = scale * sum_edges dS K.
+ * Replaces _delta_kernel/_delta_256_kernel + _vsa_dq_kernel/_vsa_dq_256_kernel:
+ * vsa/triton_impl.py:598-700,703-969. */
+int vsa_sparse_bwd_dq(const void* dout, const void* q, const void* k, const void* v,
+                      const void* out_s, const float* lse2,
+                      const int32_t* selected, const int32_t* kv_sizes,
+                      float* delta, void* dq,
+                      int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                      float scale, int dtype, void* stream);
+
+/* Key-owned backward over the CSR in-edges: dk = scale * sum dS^T Q, dv = sum P^T dO;
+ * rows beyond a ragged block's size get zero.
+ * Replaces _vsa_dkdv_kernel/_vsa_dkdv_256_kernel: vsa/triton_impl.py:972-1318. */
+int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const void* v,
+                        const float* lse2, const float* delta,
+                        const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                        const int32_t* kv_sizes, void* dk, void* dv,
+                        int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                        float scale, int dtype, void* stream);
+
+/* out = out_s + out_c[block] * gate (gate may be NULL) in fp32, one rounding.
+ * Replaces _combine_forward_kernel: vsa/fused_common.py:175-199,259-295. */
+int vsa_combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out,
+                    int64_t BH, int64_t Lq, int D, int be, int dtype, void* stream);
+
+/* Combine backward in one pass over dout: d_out_c[block] = sum over all be
+ * rows of dout*gate, dgate = dout * out_c[block] (dgate/gate may be NULL).
+ * Replaces _combine_coarse_backward_kernel + _combine_gate_backward_kernel:
+ * vsa/fused_common.py:202-256,297-337. */
+int vsa_combine_bwd(const void* dout, const void* gate, const void* out_c,
+                    void* d_out_c, void* dgate,
+                    int64_t BH, int64_t Lq, int D, int be, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VSA_B200_H_ */

@@ -1,0 +1,121 @@
+"""B200-native Video Sparse Attention behind the reference project's operator API.
+
+Drop-in names (same positional order as ``vsa/__init__.py`` of the reference):
+
+* ``video_sparse_attn(q, k, v, variable_block_sizes, q_variable_block_sizes, topk,
+  block_size, compress_attn_weight)`` and its aliases ``b200_vsa``, ``triton_vsa``,
+  ``helion_vsa`` -- the whole operator, differentiable in q, k, v and the gate;
+* ``b200_sparse_attention(q, k, v, selected, variable_block_sizes, *, block_size,
+  sm_scale=None)`` and its aliases ``triton_sparse_attention``,
+  ``helion_sparse_attention`` -- the fine branch on caller-supplied routes;
+* ``block_mean``, ``topk_block_mask``, ``CompressionGate``.
+
+Everything runs in hand-written CUDA kernels for sm_100a loaded from
+``libvsa_b200.so``; importing this package without that library raises.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor, nn
+
+from . import _lib  # noqa: F401  (fails loudly when the CUDA library is absent)
+from .ops import (
+    BlockSize,
+    as_block_elements,
+    block_mean,
+    invert_routes,
+    sparse_attention,
+    validate_vsa_inputs,
+    vsa_forward_full,
+)
+
+__all__ = [
+    "video_sparse_attn", "b200_vsa", "triton_vsa", "helion_vsa",
+    "b200_sparse_attention", "triton_sparse_attention", "helion_sparse_attention",
+    "block_mean", "topk_block_mask", "CompressionGate", "invert_routes",
+    "as_block_elements", "validate_vsa_inputs",
+]
+
+
+def video_sparse_attn(q: Tensor, k: Tensor, v: Tensor, variable_block_sizes: Tensor,
+                      q_variable_block_sizes: Tensor, topk: int, block_size: BlockSize = 64,
+                      compress_attn_weight: Optional[Tensor] = None, *, sm_scale: Optional[float] = None,
+                      return_aux: bool = False):
+    """Video Sparse Attention over ``[batch, heads, seq_len, dim]`` CUDA tensors.
+
+    ``out = pooled_attention(block means)[block] * compress_attn_weight + fine_attention``
+    where the fine branch of each query block attends to the valid tokens of its
+    ``topk`` best key blocks under the pooled scores.  ``block_size`` is a tile shape
+    whose product is the block volume (an int is cubed).  With ``return_aux`` the
+    dict holds ``coarse_scores``, ``block_mask``, ``selected``, ``out_compress``
+    (per query block) and ``out_sparse``.
+    """
+    out, scores, selected, out_c, out_s = vsa_forward_full(
+        q, k, v, variable_block_sizes, q_variable_block_sizes, topk, block_size, compress_attn_weight, sm_scale)
+    if not return_aux:
+        return out
+    mask = torch.zeros_like(scores, dtype=torch.bool).scatter_(-1, selected.long(), True)
+    return out, {"coarse_scores": scores, "block_mask": mask, "selected": selected,
+                 "out_compress": out_c, "out_sparse": out_s}
+
+
+def b200_vsa(q, k, v, variable_block_sizes, q_variable_block_sizes, topk, block_size: BlockSize = 64,
+             compress_attn_weight: Optional[Tensor] = None) -> Tensor:
+    """Eight-argument form shared by every backend of the reference (``vsa/triton_impl.py:1734-1743``)."""
+    return vsa_forward_full(q, k, v, variable_block_sizes, q_variable_block_sizes, topk, block_size,
+                            compress_attn_weight)[0]
+
+
+triton_vsa = b200_vsa
+helion_vsa = b200_vsa
+
+
+def b200_sparse_attention(q, k, v, selected, variable_block_sizes, *, block_size: BlockSize,
+                          sm_scale: Optional[float] = None) -> Tensor:
+    """Fine attention on an externally supplied routing table (``vsa/triton_impl.py:1626-1652``)."""
+    return sparse_attention(q, k, v, selected, variable_block_sizes, block_size=block_size, sm_scale=sm_scale)
+
+
+triton_sparse_attention = b200_sparse_attention
+helion_sparse_attention = b200_sparse_attention
+
+
+def topk_block_mask(scores: Tensor, topk: int) -> Tensor:
+    """Boolean ``[..., Kb]`` mask with exactly ``topk`` True per row, chosen by the Top-K kernel."""
+    if not scores.is_cuda:
+        raise ValueError("the B200 implementation requires CUDA tensors")
+    kb = scores.shape[-1]
+    topk = min(int(topk), kb)
+    flat = scores.contiguous()
+    if flat.dtype not in (torch.bfloat16, torch.float32):
+        flat = flat.float()
+    rows = flat.numel() // kb
+    sel = torch.empty((rows, topk), device=scores.device, dtype=torch.int32)
+    with torch.cuda.device(scores.device):
+        _lib.call("vsa_topk", flat.data_ptr(), sel.data_ptr(), rows, kb, topk,
+                  _lib.VSA_BF16 if flat.dtype == torch.bfloat16 else _lib.VSA_F32,
+                  torch.cuda.current_stream(scores.device).cuda_stream)
+    mask = torch.zeros((rows, kb), device=scores.device, dtype=torch.bool).scatter_(-1, sel.long(), True)
+    return mask.view(scores.shape)
+
+
+class CompressionGate(nn.Module):
+    """Produces ``compress_attn_weight``: a bias-optional ``Linear(dim, dim)`` on the hidden
+    states, reshaped to ``[batch, heads, seq_len, head_dim]`` (no activation).  It sits
+    outside the attention operator; kept here so model code can import it from one place."""
+
+    def __init__(self, dim: int, num_heads: int, bias: bool = True) -> None:
+        super().__init__()
+        if dim % num_heads:
+            raise ValueError(f"dim={dim} must be divisible by num_heads={num_heads}")
+        self.num_heads = num_heads
+        self.to_gate_compress = nn.Linear(dim, dim, bias=bias)
+
+    def forward(self, hidden_states: Tensor) -> Tensor:
+        if hidden_states.ndim != 3:
+            raise ValueError("hidden_states must have shape [batch, seq_len, dim]")
+        b, s, _ = hidden_states.shape
+        return self.to_gate_compress(hidden_states).view(b, s, self.num_heads, -1).transpose(1, 2)

@@ -1,0 +1,226 @@
+// extern "C" boundary of the library: argument checks, dispatch between the
+// tensor-core and the scalar kernels, error text.  No allocation, no host sync.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace vsa {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static std::atomic<long long> g_launches{0};
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (e == cudaSuccess) return VSA_OK;
+  return fail(VSA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// VSA_B200_KERNELS=scalar forces the CUDA-core kernels everywhere (for cross-checks).
+static bool scalar_forced() {
+  const char* e = std::getenv("VSA_B200_KERNELS");
+  return e && std::strcmp(e, "scalar") == 0;
+}
+
+static int check_dtype(int dtype) {
+  if (dtype != VSA_BF16 && dtype != VSA_F32) return fail(VSA_ERR_UNSUPPORTED, "dtype %d is not bf16 (0) or fp32 (1)", dtype);
+  return VSA_OK;
+}
+
+static int check_block_shape(int64_t BH, int64_t Lq, int64_t Lkv, int D, int be) {
+  VSA_REQUIRE(BH >= 0 && Lq >= 0 && Lkv >= 0, "negative extent");
+  VSA_REQUIRE(D >= 1 && be >= 1, "head dim and block volume must be positive");
+  VSA_REQUIRE(Lq % be == 0 && Lkv % be == 0, "sequence lengths must be divisible by block_elements=%d", be);
+  return VSA_OK;
+}
+
+}  // namespace vsa
+
+using namespace vsa;
+
+extern "C" {
+
+const char* vsa_last_error_string(void) { return g_error; }
+
+int vsa_version(void) { return 100; }
+
+int64_t vsa_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
+
+int vsa_block_mean3_fwd(const void* q, const void* k, const void* v, const int32_t* q_sizes, const int32_t* kv_sizes,
+                        void* q_mean, void* k_mean, void* v_mean, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
+                        int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  rc = check_block_shape(BH, Lq, Lkv, D, be);
+  if (rc) return rc;
+  VSA_REQUIRE(q && k && v && q_sizes && kv_sizes && q_mean && k_mean && v_mean, "block mean: null pointer");
+  const void* x[3] = {q, k, v};
+  void* out[3] = {q_mean, k_mean, v_mean};
+  const int32_t* sizes[3] = {q_sizes, kv_sizes, kv_sizes};
+  const int64_t L[3] = {Lq, Lkv, Lkv};
+  return block_mean_fwd(x, out, sizes, L, 3, BH, D, be, dtype, (cudaStream_t)stream);
+}
+
+int vsa_block_mean_fwd(const void* x, const int32_t* sizes, void* mean, int64_t BH, int64_t L, int D, int be,
+                       int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  rc = check_block_shape(BH, L, L, D, be);
+  if (rc) return rc;
+  VSA_REQUIRE(x && sizes && mean, "block mean: null pointer");
+  const void* xs[3] = {x, nullptr, nullptr};
+  void* outs[3] = {mean, nullptr, nullptr};
+  const int32_t* ss[3] = {sizes, nullptr, nullptr};
+  const int64_t Ls[3] = {L, 0, 0};
+  return block_mean_fwd(xs, outs, ss, Ls, 1, BH, D, be, dtype, (cudaStream_t)stream);
+}
+
+int vsa_block_mean_bwd_accumulate(void* dx, const void* dmean, const int32_t* sizes, int64_t BH, int64_t L, int D,
+                                  int be, int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  rc = check_block_shape(BH, L, L, D, be);
+  if (rc) return rc;
+  VSA_REQUIRE(dx && dmean && sizes, "block mean backward: null pointer");
+  return block_mean_bwd(dx, dmean, sizes, BH, L, D, be, dtype, true, (cudaStream_t)stream);
+}
+
+int vsa_block_mean_bwd(void* dx, const void* dmean, const int32_t* sizes, int64_t BH, int64_t L, int D, int be,
+                       int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  rc = check_block_shape(BH, L, L, D, be);
+  if (rc) return rc;
+  VSA_REQUIRE(dx && dmean && sizes, "block mean backward: null pointer");
+  return block_mean_bwd(dx, dmean, sizes, BH, L, D, be, dtype, false, (cudaStream_t)stream);
+}
+
+int vsa_coarse_fwd(const void* q_mean, const void* k_mean, const void* v_mean, void* scores, void* probs, void* out_c,
+                   int64_t BH, int Qb, int Kb, int D, float scale, int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && D >= 1, "coarse forward: bad extents");
+  VSA_REQUIRE(q_mean && k_mean && v_mean && scores && probs && out_c, "coarse forward: null pointer");
+  return coarse_fwd(q_mean, k_mean, v_mean, scores, probs, out_c, BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
+}
+
+int vsa_topk(const void* scores, int32_t* selected, int64_t rows, int Kb, int topk, int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(scores && selected, "topk: null pointer");
+  VSA_REQUIRE(rows >= 0 && Kb >= 1, "topk: bad extents");
+  VSA_REQUIRE(topk >= 1 && topk <= Kb, "topk must be in [1, %d]", Kb);
+  return topk_select(scores, selected, rows, Kb, topk, dtype, (cudaStream_t)stream);
+}
+
+int vsa_coarse_bwd(const void* d_out_c, const void* out_c, const void* q_mean, const void* k_mean, const void* v_mean,
+                   const void* probs, void* dscores_ws, float* rowdot_ws, void* dq_mean, void* dk_mean, void* dv_mean,
+                   int64_t BH, int Qb, int Kb, int D, float scale, int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && D >= 1, "coarse backward: bad extents");
+  VSA_REQUIRE(d_out_c && out_c && q_mean && k_mean && v_mean && probs && dscores_ws && rowdot_ws && dq_mean &&
+                  dk_mean && dv_mean, "coarse backward: null pointer");
+  return coarse_bwd(d_out_c, out_c, q_mean, k_mean, v_mean, probs, dscores_ws, rowdot_ws, dq_mean, dk_mean, dv_mean,
+                    BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
+}
+
+static int check_sparse(int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, int dtype) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  rc = check_block_shape(BH, Lq, Lkv, D, be);
+  if (rc) return rc;
+  VSA_REQUIRE(Lkv >= be, "at least one key block is required");
+  VSA_REQUIRE(topk >= 1 && topk <= Lkv / be, "selected topk must be in [1, %lld]", (long long)(Lkv / be));
+  return VSA_OK;
+}
+
+int vsa_sparse_fwd(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
+                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale,
+                   int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(q && k && v && selected && kv_sizes && out, "sparse forward: null pointer");
+  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
+    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, (cudaStream_t)stream);
+  return sparse_fwd_scalar(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype,
+                           (cudaStream_t)stream);
+}
+
+int vsa_route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse,
+                     int32_t* cursor_ws, int64_t BH, int Qb, int Kb, int topk, void* stream) {
+  VSA_REQUIRE(selected && counts && offsets && inverse && cursor_ws, "route inversion: null pointer");
+  VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && topk >= 1, "route inversion: bad extents");
+  return route_invert(selected, counts, offsets, inverse, cursor_ws, BH, Qb, Kb, topk, (cudaStream_t)stream);
+}
+
+int vsa_sparse_bwd_dq(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
+                      const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
+                      int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale, int dtype,
+                      void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && q && k && v && out_s && lse2 && selected && kv_sizes && delta && dq, "sparse dQ: null pointer");
+  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
+    return sparse_dq_tc(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
+                        (cudaStream_t)stream);
+  return sparse_dq_scalar(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, D, be, topk, scale,
+                          dtype, (cudaStream_t)stream);
+}
+
+int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                        const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                        const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int D,
+                        int be, int topk, float scale, int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && q && k && v && lse2 && delta && counts && offsets && inverse && kv_sizes && dk && dv,
+              "sparse dK/dV: null pointer");
+  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
+    return sparse_dkdv_tc(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
+                          topk, scale, (cudaStream_t)stream);
+  return sparse_dkdv_scalar(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, D, be,
+                            topk, scale, dtype, (cudaStream_t)stream);
+}
+
+int vsa_combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out, int64_t BH, int64_t Lq, int D,
+                    int be, int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  rc = check_block_shape(BH, Lq, Lq, D, be);
+  if (rc) return rc;
+  VSA_REQUIRE(out_s && out_c && out, "combine: null pointer");
+  return combine_fwd(out_s, out_c, gate, out, BH, Lq, D, be, dtype, (cudaStream_t)stream);
+}
+
+int vsa_combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,
+                    int64_t Lq, int D, int be, int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  rc = check_block_shape(BH, Lq, Lq, D, be);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && out_c && d_out_c, "combine backward: null pointer");
+  VSA_REQUIRE(gate || !dgate, "combine backward: dgate requested without a gate");
+  return combine_bwd(dout, gate, out_c, d_out_c, dgate, BH, Lq, D, be, dtype, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,899 @@
+// Scalar (CUDA-core) kernels of the VSA path.
+//
+// Two roles: (1) the bandwidth-bound pieces of every configuration -- block
+// means, pooled softmax, Top-K, gated combine, route inversion -- and (2) the
+// fine attention forward/backward for shapes the tensor-core kernels do not
+// cover (fp32 validation mode, block volumes other than 64/256, head dims
+// other than 128).  Arithmetic follows the reference project's conventions:
+// fp32 accumulation, base-2 log-sum-exp, masks from the per-block sizes.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace vsa {
+
+// =========================================================================================
+// Block means (vsa/common.py:55-82 of the reference): one CTA per (tensor, bh, block).
+// Only the first sizes[b] rows of a block are read, so padding never reaches the sum.
+// =========================================================================================
+struct MeanJob {
+  const void* x[3];
+  void* out[3];
+  const int32_t* sizes[3];
+  int nb[3];
+  long long first_cta[4];   // CTA index ranges per tensor
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128) block_mean_kernel(MeanJob job, int D, int be) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float acc_sm[256];
+  const long long cta = blockIdx.x;
+  int t = 0;
+  if (cta >= job.first_cta[1]) t = 1;
+  if (cta >= job.first_cta[2]) t = 2;
+  const long long local = cta - job.first_cta[t];
+  const int nb = job.nb[t];
+  const int blk = (int)(local % nb);
+  const T* x = reinterpret_cast<const T*>(job.x[t]) + local * (long long)be * D;
+  T* out = reinterpret_cast<T*>(job.out[t]) + local * (long long)D;
+  int size = job.sizes[t][blk];
+  size = size < 0 ? 0 : (size > be ? be : size);
+
+  for (int d = threadIdx.x; d < D; d += blockDim.x) acc_sm[d] = 0.f;
+  __syncthreads();
+
+  const int cpr = D / VEC;                     // 16-byte chunks per row
+  const int rows_per_pass = blockDim.x / cpr;
+  const int chunk = threadIdx.x % cpr;
+  const int rgrp = threadIdx.x / cpr;
+  float part[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) part[i] = 0.f;
+  if (rgrp < rows_per_pass) {
+    for (int r = rgrp; r < size; r += rows_per_pass) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(x + (long long)r * D + chunk * VEC);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(e + i);
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) atomicAdd(&acc_sm[chunk * VEC + i], part[i]);
+  }
+  __syncthreads();
+  const float denom = (float)(size > 1 ? size : 1);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) Elem<T>::st(out + d, acc_sm[d] / denom);
+}
+
+template <typename T>
+static int launch_block_mean(MeanJob job, int ntensors, int64_t BH, int D, int be, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(T);
+  if (D % VEC != 0 || D / VEC > 128 || D > 256)
+    return fail(VSA_ERR_UNSUPPORTED, "block mean: head dim %d must be a multiple of %d and <= 256", D, VEC);
+  long long total = 0;
+  for (int t = 0; t < 3; ++t) {
+    job.first_cta[t] = total;
+    if (t < ntensors) total += BH * job.nb[t];
+  }
+  job.first_cta[3] = total;
+  for (int t = ntensors; t < 3; ++t) job.first_cta[t] = total + 1;  // never matched
+  if (total == 0) return VSA_OK;
+  if (total > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "block mean: too many blocks");
+  block_mean_kernel<T><<<(unsigned)total, 128, 0, st>>>(job, D, be);
+  return check_launch("block_mean_kernel");
+}
+
+int block_mean_fwd(const void* const* x, void* const* out, const int32_t* const* sizes, const int64_t* L,
+                   int ntensors, int64_t BH, int D, int be, int dtype, cudaStream_t st) {
+  MeanJob job{};
+  for (int t = 0; t < ntensors; ++t) {
+    job.x[t] = x[t];
+    job.out[t] = out[t];
+    job.sizes[t] = sizes[t];
+    job.nb[t] = (int)(L[t] / be);
+  }
+  return dtype == VSA_F32 ? launch_block_mean<float>(job, ntensors, BH, D, be, st)
+                          : launch_block_mean<__nv_bfloat16>(job, ntensors, BH, D, be, st);
+}
+
+// Block-mean backward (vsa/fused_common.py:62-103 of the reference).  ACCUM adds into
+// dx on valid rows and leaves padding rows alone; otherwise padding rows are zeroed.
+template <typename T, bool ACCUM>
+__global__ void __launch_bounds__(128) block_mean_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dmean,
+                                                            const int32_t* __restrict__ sizes, int nb, int D, int be) {
+  constexpr int VEC = 16 / sizeof(T);
+  const long long local = blockIdx.x;
+  const int blk = (int)(local % nb);
+  int size = sizes[blk];
+  size = size < 0 ? 0 : (size > be ? be : size);
+  const float inv = 1.f / (float)(size > 1 ? size : 1);
+  T* x = dx + local * (long long)be * D;
+  const T* g = dmean + local * (long long)D;
+  const int cpr = D / VEC;
+  const int rows_per_pass = blockDim.x / cpr;
+  const int chunk = threadIdx.x % cpr;
+  const int rgrp = threadIdx.x / cpr;
+  if (rgrp >= rows_per_pass) return;
+  float gv[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) gv[i] = Elem<T>::ld(g + chunk * VEC + i) * inv;
+  const int last = ACCUM ? size : be;
+  for (int r = rgrp; r < last; r += rows_per_pass) {
+    uint4* p = reinterpret_cast<uint4*>(x + (long long)r * D + chunk * VEC);
+    uint4 raw = ACCUM ? *p : make_uint4(0, 0, 0, 0);
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float base = ACCUM ? Elem<T>::ld(e + i) : 0.f;
+      Elem<T>::st(e + i, r < size ? base + gv[i] : 0.f);
+    }
+    *p = raw;
+  }
+}
+
+int block_mean_bwd(void* dx, const void* dmean, const int32_t* sizes, int64_t BH, int64_t L, int D, int be,
+                   int dtype, bool accumulate, cudaStream_t st) {
+  const int nb = (int)(L / be);
+  const long long total = BH * nb;
+  if (total == 0) return VSA_OK;
+  const int vec = dtype == VSA_F32 ? 4 : 8;
+  if (D % vec != 0 || D / vec > 128)
+    return fail(VSA_ERR_UNSUPPORTED, "block mean backward: head dim %d must be a multiple of %d and <= 256", D, vec);
+#define VSA_LAUNCH_BMB(T, ACC)                                                                        \
+  block_mean_bwd_kernel<T, ACC><<<(unsigned)total, 128, 0, st>>>(reinterpret_cast<T*>(dx),             \
+                                                                reinterpret_cast<const T*>(dmean), sizes, nb, D, be)
+  if (dtype == VSA_F32) {
+    if (accumulate) VSA_LAUNCH_BMB(float, true); else VSA_LAUNCH_BMB(float, false);
+  } else {
+    if (accumulate) VSA_LAUNCH_BMB(__nv_bfloat16, true); else VSA_LAUNCH_BMB(__nv_bfloat16, false);
+  }
+#undef VSA_LAUNCH_BMB
+  return check_launch("block_mean_bwd_kernel");
+}
+
+// =========================================================================================
+// Small batched GEMM with arbitrary strides (the pooled attention and its backward).
+// C[b][m][n] = epilogue(sum_k A[b][m][k] * B[b][k][n]); 64x64 tile, 16-deep, 4x4 per thread.
+// =========================================================================================
+struct EpiScores {   // scores = round(round(acc) * scale)            vsa/common.py:164
+  float scale;
+  template <typename T> __device__ void operator()(T* C, long long idx, long long, int, int, float acc) const {
+    Elem<T>::st(C + idx, Elem<T>::round(acc) * scale);
+  }
+};
+struct EpiStore {    // plain rounding store
+  template <typename T> __device__ void operator()(T* C, long long idx, long long, int, int, float acc) const {
+    Elem<T>::st(C + idx, acc);
+  }
+};
+template <typename T> struct EpiSoftmaxBwd {   // dS = P * (dP - rowdot) * scale
+  const T* probs;
+  const float* rowdot;   // [batch*M]
+  float scale;
+  int M;
+  __device__ void operator()(T* C, long long idx, long long b, int m, int, float acc) const {
+    const float p = Elem<T>::ld(probs + idx);
+    Elem<T>::st(C + idx, p * (acc - rowdot[b * M + m]) * scale);
+  }
+};
+
+template <typename T, typename Epi>
+__global__ void __launch_bounds__(256) gemm_kernel(const T* __restrict__ A, long long a_bs, int a_rs, int a_cs,
+                                                   const T* __restrict__ B, long long b_bs, int b_rs, int b_cs,
+                                                   T* __restrict__ C, long long c_bs, int M, int N, int K, Epi epi) {
+  __shared__ float As[16][68];
+  __shared__ float Bs[16][68];
+  const long long b = blockIdx.z;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  A += b * a_bs;
+  B += b * b_bs;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    // each thread stages 4 elements of A and of B; the fast index follows the unit stride
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = threadIdx.x + i * 256;          // 0..1023
+      int mm, kk;
+      if (a_cs == 1) { kk = e % 16; mm = e / 16; } else { mm = e % 64; kk = e / 64; }
+      float va = 0.f;
+      if (m0 + mm < M && k0 + kk < K) va = Elem<T>::ld(A + (long long)(m0 + mm) * a_rs + (long long)(k0 + kk) * a_cs);
+      As[kk][mm] = va;
+      int nn, kb;
+      if (b_rs == 1) { kb = e % 16; nn = e / 16; } else { nn = e % 64; kb = e / 64; }
+      float vb = 0.f;
+      if (n0 + nn < N && k0 + kb < K) vb = Elem<T>::ld(B + (long long)(k0 + kb) * b_rs + (long long)(n0 + nn) * b_cs);
+      Bs[kb][nn] = vb;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], bb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bb[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) epi(C, b * c_bs + (long long)m * N + n, b, m, n, acc[i][j]);
+    }
+  }
+}
+
+template <typename T, typename Epi>
+static int gemm(const T* A, long long a_bs, int a_rs, int a_cs, const T* B, long long b_bs, int b_rs, int b_cs,
+                T* C, int64_t batch, int M, int N, int K, Epi epi, cudaStream_t st, const char* what) {
+  if (batch == 0 || M == 0 || N == 0) return VSA_OK;
+  if (batch > 65535) return fail(VSA_ERR_UNSUPPORTED, "%s: batch*heads %lld exceeds 65535", what, (long long)batch);
+  dim3 grid((N + 63) / 64, (M + 63) / 64, (unsigned)batch);
+  gemm_kernel<T, Epi><<<grid, 256, 0, st>>>(A, a_bs, a_rs, a_cs, B, b_bs, b_rs, b_cs, C, (long long)M * N, M, N, K, epi);
+  return check_launch(what);
+}
+
+// Row softmax of the pooled scores: probs = round(softmax_fp32(scores)).
+template <typename T>
+__global__ void __launch_bounds__(128) softmax_rows_kernel(const T* __restrict__ scores, T* __restrict__ probs, int n) {
+  __shared__ float red[4];
+  const T* s = scores + (long long)blockIdx.x * n;
+  T* p = probs + (long long)blockIdx.x * n;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, Elem<T>::ld(s + i));
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) sum += expf(Elem<T>::ld(s + i) - mx);
+  sum = warp_sum(sum);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  sum = red[0] + red[1] + red[2] + red[3];
+  const float inv = 1.f / sum;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) Elem<T>::st(p + i, expf(Elem<T>::ld(s + i) - mx) * inv);
+}
+
+// rowdot[r] = sum_d a[r,d] * b[r,d]  (one warp per row)
+template <typename T>
+__global__ void rowdot_kernel(const T* __restrict__ a, const T* __restrict__ b, float* __restrict__ out, long long rows, int D) {
+  const long long r = (long long)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  if (r >= rows) return;
+  float s = 0.f;
+  for (int d = threadIdx.x & 31; d < D; d += 32) s += Elem<T>::ld(a + r * D + d) * Elem<T>::ld(b + r * D + d);
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) out[r] = s;
+}
+
+template <typename T>
+static int coarse_fwd_t(const T* qc, const T* kc, const T* vc, T* scores, T* probs, T* out_c,
+                        int64_t BH, int Qb, int Kb, int D, float scale, cudaStream_t st) {
+  // scores[Qb,Kb] = qc[Qb,D] * kc[Kb,D]^T
+  int rc = gemm<T>(qc, (long long)Qb * D, D, 1, kc, (long long)Kb * D, 1, D, scores, BH, Qb, Kb, D,
+                   EpiScores{scale}, st, "coarse scores");
+  if (rc) return rc;
+  const long long rows = BH * Qb;
+  if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "coarse softmax: too many rows");
+  softmax_rows_kernel<T><<<(unsigned)rows, 128, 0, st>>>(scores, probs, Kb);
+  rc = check_launch("softmax_rows_kernel");
+  if (rc) return rc;
+  // out_c[Qb,D] = probs[Qb,Kb] * vc[Kb,D]
+  return gemm<T>(probs, (long long)Qb * Kb, Kb, 1, vc, (long long)Kb * D, D, 1, out_c, BH, Qb, D, Kb, EpiStore{}, st,
+                 "coarse output");
+}
+
+int coarse_fwd(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
+               int Qb, int Kb, int D, float scale, int dtype, cudaStream_t st) {
+  if (dtype == VSA_F32)
+    return coarse_fwd_t<float>((const float*)qc, (const float*)kc, (const float*)vc, (float*)scores, (float*)probs,
+                               (float*)out_c, BH, Qb, Kb, D, scale, st);
+  using B = __nv_bfloat16;
+  return coarse_fwd_t<B>((const B*)qc, (const B*)kc, (const B*)vc, (B*)scores, (B*)probs, (B*)out_c, BH, Qb, Kb, D,
+                         scale, st);
+}
+
+template <typename T>
+static int coarse_bwd_t(const T* d_out_c, const T* out_c, const T* qc, const T* kc, const T* vc, const T* probs,
+                        T* ds, float* rowdot, T* dqc, T* dkc, T* dvc, int64_t BH, int Qb, int Kb, int D, float scale,
+                        cudaStream_t st) {
+  const long long rows = BH * Qb;
+  if (rows == 0) return VSA_OK;
+  rowdot_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_out_c, out_c, rowdot, rows, D);
+  int rc = check_launch("rowdot_kernel");
+  if (rc) return rc;
+  // dV_c[Kb,D] = probs^T[Kb,Qb] * d_out_c[Qb,D]
+  rc = gemm<T>(probs, (long long)Qb * Kb, 1, Kb, d_out_c, (long long)Qb * D, D, 1, dvc, BH, Kb, D, Qb, EpiStore{}, st,
+               "coarse dV");
+  if (rc) return rc;
+  // dS[Qb,Kb] = probs * (d_out_c[Qb,D] * vc[Kb,D]^T - rowdot) * scale
+  rc = gemm<T>(d_out_c, (long long)Qb * D, D, 1, vc, (long long)Kb * D, 1, D, ds, BH, Qb, Kb, D,
+               EpiSoftmaxBwd<T>{probs, rowdot, scale, Qb}, st, "coarse dS");
+  if (rc) return rc;
+  // dQ_c[Qb,D] = dS[Qb,Kb] * kc[Kb,D]
+  rc = gemm<T>(ds, (long long)Qb * Kb, Kb, 1, kc, (long long)Kb * D, D, 1, dqc, BH, Qb, D, Kb, EpiStore{}, st,
+               "coarse dQ");
+  if (rc) return rc;
+  // dK_c[Kb,D] = dS^T[Kb,Qb] * qc[Qb,D]
+  return gemm<T>(ds, (long long)Qb * Kb, 1, Kb, qc, (long long)Qb * D, D, 1, dkc, BH, Kb, D, Qb, EpiStore{}, st,
+                 "coarse dK");
+}
+
+int coarse_bwd(const void* d_out_c, const void* out_c, const void* qc, const void* kc, const void* vc,
+               const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb, int Kb,
+               int D, float scale, int dtype, cudaStream_t st) {
+  if (dtype == VSA_F32)
+    return coarse_bwd_t<float>((const float*)d_out_c, (const float*)out_c, (const float*)qc, (const float*)kc,
+                               (const float*)vc, (const float*)probs, (float*)ds, rowdot, (float*)dqc, (float*)dkc,
+                               (float*)dvc, BH, Qb, Kb, D, scale, st);
+  using B = __nv_bfloat16;
+  return coarse_bwd_t<B>((const B*)d_out_c, (const B*)out_c, (const B*)qc, (const B*)kc, (const B*)vc,
+                         (const B*)probs, (B*)ds, rowdot, (B*)dqc, (B*)dkc, (B*)dvc, BH, Qb, Kb, D, scale, st);
+}
+
+// =========================================================================================
+// Top-K by radix select (vsa/torch_impl.py:85 of the reference): one CTA per score row.
+// The k-th largest key is found in four 8-bit passes; every id with a larger key, plus
+// the lowest-numbered ids equal to it, are written in ascending id order.
+// =========================================================================================
+constexpr int kTopkThreads = 256;
+constexpr int kTopkMaxCols = 8192;
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads) topk_kernel(const T* __restrict__ scores, int32_t* __restrict__ selected,
+                                                            int n, int topk) {
+  extern __shared__ uint32_t keys[];       // [n]
+  __shared__ int hist[256];
+  __shared__ uint32_t sh_prefix;
+  __shared__ int sh_k;
+  __shared__ int warp_cnt[2][kTopkThreads / 32];
+  const T* s = scores + (long long)blockIdx.x * n;
+  int32_t* out = selected + (long long)blockIdx.x * topk;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int i = tid; i < n; i += kTopkThreads) keys[i] = order_key(Elem<T>::ld(s + i));
+  if (tid == 0) { sh_prefix = 0; sh_k = topk; }
+  __syncthreads();
+
+  for (int pass = 3; pass >= 0; --pass) {
+    hist[tid] = 0;
+    __syncthreads();
+    const uint32_t prefix = sh_prefix;
+    const int k = sh_k;
+    const int shift = pass * 8;
+    const uint32_t hi_mask = pass == 3 ? 0u : (0xffffffffu << (shift + 8));
+    for (int i = tid; i < n; i += kTopkThreads) {
+      const uint32_t key = keys[i];
+      if ((key & hi_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins [255-8l-7, 255-8l]; scan from the top bin down
+      int mine = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mine += hist[255 - 8 * lane - j];
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const int above = incl - mine;                  // elements in bins above this lane's range
+      if (above < k && k <= incl) {
+        int run = above;
+        for (int j = 0; j < 8; ++j) {
+          const int bin = 255 - 8 * lane - j;
+          const int c = hist[bin];
+          if (k <= run + c) {
+            sh_prefix = prefix | ((uint32_t)bin << shift);
+            sh_k = k - run;
+            break;
+          }
+          run += c;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const uint32_t thr = sh_prefix;
+  const int take_eq = sh_k;        // how many ids equal to the threshold are kept (>= 1)
+
+  int eq_seen = 0, written = 0;
+  for (int base = 0; base < n; base += kTopkThreads) {
+    const int i = base + tid;
+    const uint32_t key = i < n ? keys[i] : 0u;
+    const bool gt = i < n && key > thr;
+    const bool eq = i < n && key == thr;
+    const unsigned eq_b = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) warp_cnt[0][warp] = __popc(eq_b);
+    __syncthreads();
+    int eq_before = eq_seen, eq_total = 0;
+#pragma unroll
+    for (int w = 0; w < kTopkThreads / 32; ++w) {
+      const int c = warp_cnt[0][w];
+      if (w < warp) eq_before += c;
+      eq_total += c;
+    }
+    eq_before += __popc(eq_b & ((1u << lane) - 1u));
+    const bool take = gt || (eq && eq_before < take_eq);
+    const unsigned tk_b = __ballot_sync(0xffffffffu, take);
+    if (lane == 0) warp_cnt[1][warp] = __popc(tk_b);
+    __syncthreads();
+    int pos = written, tk_total = 0;
+#pragma unroll
+    for (int w = 0; w < kTopkThreads / 32; ++w) {
+      const int c = warp_cnt[1][w];
+      if (w < warp) pos += c;
+      tk_total += c;
+    }
+    pos += __popc(tk_b & ((1u << lane) - 1u));
+    if (take && pos < topk) out[pos] = i;
+    eq_seen += eq_total;
+    written += tk_total;
+    __syncthreads();
+  }
+}
+
+int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int topk, int dtype, cudaStream_t st) {
+  if (rows == 0) return VSA_OK;
+  if (Kb > kTopkMaxCols) return fail(VSA_ERR_UNSUPPORTED, "topk: %d key blocks exceed the supported %d", Kb, kTopkMaxCols);
+  if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "topk: too many rows");
+  const size_t smem = (size_t)Kb * sizeof(uint32_t);
+  if (dtype == VSA_F32)
+    topk_kernel<float><<<(unsigned)rows, kTopkThreads, smem, st>>>((const float*)scores, selected, Kb, topk);
+  else
+    topk_kernel<__nv_bfloat16><<<(unsigned)rows, kTopkThreads, smem, st>>>((const __nv_bfloat16*)scores, selected, Kb, topk);
+  return check_launch("topk_kernel");
+}
+
+// =========================================================================================
+// Route inversion (vsa/triton_impl.py:476-595 of the reference): count, scan, scatter.
+// =========================================================================================
+__global__ void route_count_kernel(const int32_t* __restrict__ selected, int32_t* __restrict__ counts,
+                                   long long edges_total, int edges_per_bh, int Kb) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= edges_total) return;
+  const long long bh = e / edges_per_bh;
+  const int kv = selected[e];
+  if ((unsigned)kv < (unsigned)Kb) atomicAdd(&counts[bh * Kb + kv], 1);
+}
+
+__global__ void __launch_bounds__(256) route_scan_kernel(const int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                                                         int32_t* __restrict__ cursor, int Kb) {
+  __shared__ int warp_tot[8];
+  __shared__ int carry_sm;
+  const long long bh = blockIdx.x;
+  const int32_t* c = counts + bh * Kb;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_sm = 0;
+  __syncthreads();
+  for (int base = 0; base < Kb; base += 256) {
+    const int i = base + threadIdx.x;
+    const int v = i < Kb ? c[i] : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = carry_sm;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    if (i < Kb) {
+      offsets[bh * Kb + i] = before + incl - v;
+      cursor[bh * Kb + i] = before + incl - v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 255) carry_sm = before + incl;
+    __syncthreads();
+  }
+}
+
+__global__ void route_scatter_kernel(const int32_t* __restrict__ selected, int32_t* __restrict__ cursor,
+                                     int32_t* __restrict__ inverse, long long edges_total, int edges_per_bh, int Kb,
+                                     int topk) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= edges_total) return;
+  const long long bh = e / edges_per_bh;
+  const int within = (int)(e - bh * edges_per_bh);
+  const int kv = selected[e];
+  if ((unsigned)kv >= (unsigned)Kb) return;
+  const int slot = atomicAdd(&cursor[bh * Kb + kv], 1);
+  inverse[bh * edges_per_bh + slot] = within / topk;
+}
+
+int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int32_t* cursor,
+                 int64_t BH, int Qb, int Kb, int topk, cudaStream_t st) {
+  const long long per = (long long)Qb * topk;
+  const long long total = BH * per;
+  if (BH == 0 || Kb == 0) return VSA_OK;
+  if (per > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "route inversion: too many edges per slice");
+  if (cudaMemsetAsync(counts, 0, sizeof(int32_t) * BH * Kb, st) != cudaSuccess)
+    return fail(VSA_ERR_LAUNCH, "route inversion: memset failed: %s", cudaGetErrorString(cudaGetLastError()));
+  if (total > 0) {
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    route_count_kernel<<<blocks, 256, 0, st>>>(selected, counts, total, (int)per, Kb);
+    int rc = check_launch("route_count_kernel");
+    if (rc) return rc;
+  }
+  route_scan_kernel<<<(unsigned)BH, 256, 0, st>>>(counts, offsets, cursor, Kb);
+  int rc = check_launch("route_scan_kernel");
+  if (rc) return rc;
+  if (total > 0) {
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    route_scatter_kernel<<<blocks, 256, 0, st>>>(selected, cursor, inverse, total, (int)per, Kb, topk);
+    rc = check_launch("route_scatter_kernel");
+  }
+  return rc;
+}
+
+// =========================================================================================
+// Gated combine (vsa/fused_common.py:175-256 of the reference).
+// =========================================================================================
+template <typename T, bool GATE>
+__global__ void __launch_bounds__(256) combine_fwd_kernel(const T* __restrict__ out_s, const T* __restrict__ out_c,
+                                                          const T* __restrict__ gate, T* __restrict__ out,
+                                                          long long chunks, int D, int be) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int cpr = D / VEC;
+  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < chunks;
+       c += (long long)gridDim.x * blockDim.x) {
+    const long long row = c / cpr;
+    const int ch = (int)(c - row * cpr);
+    const long long blk = row / be;
+    const uint4 s_raw = *reinterpret_cast<const uint4*>(out_s + c * VEC);
+    const uint4 c_raw = *reinterpret_cast<const uint4*>(out_c + blk * D + ch * VEC);
+    uint4 g_raw = make_uint4(0, 0, 0, 0);
+    if (GATE) g_raw = *reinterpret_cast<const uint4*>(gate + c * VEC);
+    uint4 o_raw;
+    const T* se = reinterpret_cast<const T*>(&s_raw);
+    const T* ce = reinterpret_cast<const T*>(&c_raw);
+    const T* ge = reinterpret_cast<const T*>(&g_raw);
+    T* oe = reinterpret_cast<T*>(&o_raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      float cv = Elem<T>::ld(ce + i);
+      if (GATE) cv *= Elem<T>::ld(ge + i);
+      Elem<T>::st(oe + i, Elem<T>::ld(se + i) + cv);
+    }
+    *reinterpret_cast<uint4*>(out + c * VEC) = o_raw;
+  }
+}
+
+int combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out, int64_t BH, int64_t Lq, int D,
+                int be, int dtype, cudaStream_t st) {
+  const int vec = dtype == VSA_F32 ? 4 : 8;
+  if (D % vec != 0) return fail(VSA_ERR_UNSUPPORTED, "combine: head dim %d must be a multiple of %d", D, vec);
+  const long long chunks = BH * Lq * (D / vec);
+  if (chunks == 0) return VSA_OK;
+  long long blocks = (chunks + 255) / 256;
+  if (blocks > 148LL * 64) blocks = 148LL * 64;
+#define VSA_LAUNCH_CF(T, G)                                                                                   \
+  combine_fwd_kernel<T, G><<<(unsigned)blocks, 256, 0, st>>>((const T*)out_s, (const T*)out_c, (const T*)gate, \
+                                                            (T*)out, chunks, D, be)
+  if (dtype == VSA_F32) {
+    if (gate) VSA_LAUNCH_CF(float, true); else VSA_LAUNCH_CF(float, false);
+  } else {
+    if (gate) VSA_LAUNCH_CF(__nv_bfloat16, true); else VSA_LAUNCH_CF(__nv_bfloat16, false);
+  }
+#undef VSA_LAUNCH_CF
+  return check_launch("combine_fwd_kernel");
+}
+
+// One CTA per (bh, query block): d_out_c = sum over ALL be rows of dout*gate (padded
+// query rows included), dgate = dout * out_c[block], both from a single read of dout.
+template <typename T, bool GATE>
+__global__ void __launch_bounds__(128) combine_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ gate,
+                                                          const T* __restrict__ out_c, T* __restrict__ d_out_c,
+                                                          T* __restrict__ dgate, int D, int be) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float acc_sm[256];
+  const long long blk = blockIdx.x;
+  const T* g_do = dout + blk * (long long)be * D;
+  const T* g_gate = GATE ? gate + blk * (long long)be * D : nullptr;
+  T* g_dgate = (GATE && dgate) ? dgate + blk * (long long)be * D : nullptr;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) acc_sm[d] = 0.f;
+  __syncthreads();
+  const int cpr = D / VEC;
+  const int rows_per_pass = blockDim.x / cpr;
+  const int chunk = threadIdx.x % cpr;
+  const int rgrp = threadIdx.x / cpr;
+  if (rgrp < rows_per_pass) {
+    float cvec[VEC], part[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      cvec[i] = Elem<T>::ld(out_c + blk * D + chunk * VEC + i);
+      part[i] = 0.f;
+    }
+    for (int r = rgrp; r < be; r += rows_per_pass) {
+      const long long off = (long long)r * D + chunk * VEC;
+      const uint4 d_raw = *reinterpret_cast<const uint4*>(g_do + off);
+      const T* de = reinterpret_cast<const T*>(&d_raw);
+      if (GATE) {
+        const uint4 g_raw = *reinterpret_cast<const uint4*>(g_gate + off);
+        const T* ge = reinterpret_cast<const T*>(&g_raw);
+        uint4 o_raw;
+        T* oe = reinterpret_cast<T*>(&o_raw);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const float dv = Elem<T>::ld(de + i);
+          part[i] += dv * Elem<T>::ld(ge + i);
+          Elem<T>::st(oe + i, dv * cvec[i]);
+        }
+        if (g_dgate) *reinterpret_cast<uint4*>(g_dgate + off) = o_raw;
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(de + i);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) atomicAdd(&acc_sm[chunk * VEC + i], part[i]);
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) Elem<T>::st(d_out_c + blk * D + d, acc_sm[d]);
+}
+
+int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,
+                int64_t Lq, int D, int be, int dtype, cudaStream_t st) {
+  const int vec = dtype == VSA_F32 ? 4 : 8;
+  if (D % vec != 0 || D / vec > 128 || D > 256)
+    return fail(VSA_ERR_UNSUPPORTED, "combine backward: head dim %d must be a multiple of %d and <= 256", D, vec);
+  const long long blocks = BH * (Lq / be);
+  if (blocks == 0) return VSA_OK;
+  if (blocks > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "combine backward: too many blocks");
+#define VSA_LAUNCH_CB(T, G)                                                                                    \
+  combine_bwd_kernel<T, G><<<(unsigned)blocks, 128, 0, st>>>((const T*)dout, (const T*)gate, (const T*)out_c,   \
+                                                            (T*)d_out_c, (T*)dgate, D, be)
+  if (dtype == VSA_F32) {
+    if (gate) VSA_LAUNCH_CB(float, true); else VSA_LAUNCH_CB(float, false);
+  } else {
+    if (gate) VSA_LAUNCH_CB(__nv_bfloat16, true); else VSA_LAUNCH_CB(__nv_bfloat16, false);
+  }
+#undef VSA_LAUNCH_CB
+  return check_launch("combine_bwd_kernel");
+}
+
+// =========================================================================================
+// Scalar fine attention (any block volume, any head dim <= 256, bf16 or fp32): one warp
+// per query row (forward, dQ) or per key row (dK/dV).  Lane l holds dims l, l+32, ...
+// =========================================================================================
+constexpr int kMaxDimRegs = 8;    // head dim <= 256
+
+template <typename T>
+__device__ __forceinline__ void load_row(const T* p, int D, int lane, float (&r)[kMaxDimRegs]) {
+#pragma unroll
+  for (int i = 0; i < kMaxDimRegs; ++i) {
+    const int d = lane + 32 * i;
+    r[i] = d < D ? Elem<T>::ld(p + d) : 0.f;
+  }
+}
+__device__ __forceinline__ float dot_regs(const float (&a)[kMaxDimRegs], const float (&b)[kMaxDimRegs]) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxDimRegs; ++i) s = fmaf(a[i], b[i], s);
+  return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sparse_fwd_scalar_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                                const T* __restrict__ v,
+                                                                const int32_t* __restrict__ selected,
+                                                                const int32_t* __restrict__ kv_sizes,
+                                                                T* __restrict__ out, float* __restrict__ lse2,
+                                                                long long Lq, long long Lkv, int D, int be, int topk,
+                                                                float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= Lq) return;
+  const long long bh = blockIdx.y;
+  const int Qb = (int)(Lq / be);
+  const int qb = (int)(row / be);
+  const float c = scale * kLog2e;
+  float qr[kMaxDimRegs], acc[kMaxDimRegs] = {}, kr[kMaxDimRegs], vr[kMaxDimRegs];
+  load_row(q + (bh * Lq + row) * D, D, lane, qr);
+  float m = -INFINITY, l = 0.f;
+  const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
+  for (int s = 0; s < topk; ++s) {
+    const int kvb = sel[s];
+    int size = kv_sizes[kvb];
+    size = size > be ? be : size;
+    const T* kp = k + (bh * Lkv + (long long)kvb * be) * D;
+    const T* vp = v + (bh * Lkv + (long long)kvb * be) * D;
+    for (int j = 0; j < size; ++j) {
+      load_row(kp + (long long)j * D, D, lane, kr);
+      load_row(vp + (long long)j * D, D, lane, vr);
+      const float sc = warp_sum(dot_regs(qr, kr)) * c;
+      const float mn = fmaxf(m, sc);
+      const float alpha = exp2f(m - mn);          // m == -inf on the first token gives 0
+      const float p = exp2f(sc - mn);
+      l = l * alpha + p;
+#pragma unroll
+      for (int i = 0; i < kMaxDimRegs; ++i) acc[i] = fmaf(p, vr[i], acc[i] * alpha);
+      m = mn;
+    }
+  }
+  const float inv = 1.f / l;
+  T* op = out + (bh * Lq + row) * D;
+#pragma unroll
+  for (int i = 0; i < kMaxDimRegs; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) Elem<T>::st(op + d, acc[i] * inv);
+  }
+  if (lse2 && lane == 0) lse2[bh * Lq + row] = m + log2f(l);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sparse_dq_scalar_kernel(const T* __restrict__ dout, const T* __restrict__ q,
+                                                               const T* __restrict__ k, const T* __restrict__ v,
+                                                               const T* __restrict__ out_s, const float* __restrict__ lse2,
+                                                               const int32_t* __restrict__ selected,
+                                                               const int32_t* __restrict__ kv_sizes,
+                                                               float* __restrict__ delta, T* __restrict__ dq,
+                                                               long long Lq, long long Lkv, int D, int be, int topk,
+                                                               float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= Lq) return;
+  const long long bh = blockIdx.y;
+  const int Qb = (int)(Lq / be);
+  const int qb = (int)(row / be);
+  const float c = scale * kLog2e;
+  float qr[kMaxDimRegs], dor[kMaxDimRegs], acc[kMaxDimRegs] = {}, kr[kMaxDimRegs], vr[kMaxDimRegs];
+  load_row(q + (bh * Lq + row) * D, D, lane, qr);
+  load_row(dout + (bh * Lq + row) * D, D, lane, dor);
+  load_row(out_s + (bh * Lq + row) * D, D, lane, kr);
+  const float dl = warp_sum(dot_regs(kr, dor));
+  if (lane == 0) delta[bh * Lq + row] = dl;
+  const float lse = lse2[bh * Lq + row];
+  const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
+  for (int s = 0; s < topk; ++s) {
+    const int kvb = sel[s];
+    int size = kv_sizes[kvb];
+    size = size > be ? be : size;
+    const T* kp = k + (bh * Lkv + (long long)kvb * be) * D;
+    const T* vp = v + (bh * Lkv + (long long)kvb * be) * D;
+    for (int j = 0; j < size; ++j) {
+      load_row(kp + (long long)j * D, D, lane, kr);
+      load_row(vp + (long long)j * D, D, lane, vr);
+      const float sc = warp_sum(dot_regs(qr, kr)) * c;
+      const float dp = warp_sum(dot_regs(dor, vr));
+      const float ds = exp2f(sc - lse) * (dp - dl) * scale;
+#pragma unroll
+      for (int i = 0; i < kMaxDimRegs; ++i) acc[i] = fmaf(ds, kr[i], acc[i]);
+    }
+  }
+  T* op = dq + (bh * Lq + row) * D;
+#pragma unroll
+  for (int i = 0; i < kMaxDimRegs; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) Elem<T>::st(op + d, acc[i]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sparse_dkdv_scalar_kernel(
+    const T* __restrict__ dout, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+    const float* __restrict__ lse2, const float* __restrict__ delta, const int32_t* __restrict__ counts,
+    const int32_t* __restrict__ offsets, const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
+    T* __restrict__ dk, T* __restrict__ dv, long long Lq, long long Lkv, int D, int be, int topk, float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= Lkv) return;
+  const long long bh = blockIdx.y;
+  const int Kb = (int)(Lkv / be), Qb = (int)(Lq / be);
+  const int kvb = (int)(row / be);
+  const int pos = (int)(row - (long long)kvb * be);
+  const float c = scale * kLog2e;
+  float kr[kMaxDimRegs], vr[kMaxDimRegs], dka[kMaxDimRegs] = {}, dva[kMaxDimRegs] = {}, qr[kMaxDimRegs], dor[kMaxDimRegs];
+  if (pos < kv_sizes[kvb]) {
+    load_row(k + (bh * Lkv + row) * D, D, lane, kr);
+    load_row(v + (bh * Lkv + row) * D, D, lane, vr);
+    const int cnt = counts[bh * Kb + kvb];
+    const int32_t* inv = inverse + bh * (long long)Qb * topk + offsets[bh * Kb + kvb];
+    for (int e = 0; e < cnt; ++e) {
+      const long long r0 = (long long)inv[e] * be;
+      for (int r = 0; r < be; ++r) {
+        const long long qi = bh * Lq + r0 + r;
+        load_row(q + qi * D, D, lane, qr);
+        load_row(dout + qi * D, D, lane, dor);
+        const float sc = warp_sum(dot_regs(qr, kr)) * c;
+        const float dp = warp_sum(dot_regs(dor, vr));
+        const float p = exp2f(sc - lse2[qi]);
+        const float ds = p * (dp - delta[qi]);
+#pragma unroll
+        for (int i = 0; i < kMaxDimRegs; ++i) {
+          dka[i] = fmaf(ds, qr[i], dka[i]);
+          dva[i] = fmaf(p, dor[i], dva[i]);
+        }
+      }
+    }
+  }
+  T* dkp = dk + (bh * Lkv + row) * D;
+  T* dvp = dv + (bh * Lkv + row) * D;
+#pragma unroll
+  for (int i = 0; i < kMaxDimRegs; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) {
+      Elem<T>::st(dkp + d, dka[i] * scale);
+      Elem<T>::st(dvp + d, dva[i]);
+    }
+  }
+}
+
+static int check_scalar_shape(int64_t BH, int D, const char* what) {
+  if (D > 32 * kMaxDimRegs) return fail(VSA_ERR_UNSUPPORTED, "%s: head dim %d exceeds 256", what, D);
+  if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "%s: batch*heads %lld exceeds 65535", what, (long long)BH);
+  return VSA_OK;
+}
+
+int sparse_fwd_scalar(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
+                      void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                      float scale, int dtype, cudaStream_t st) {
+  int rc = check_scalar_shape(BH, D, "sparse forward");
+  if (rc) return rc;
+  if (BH == 0 || Lq == 0) return VSA_OK;
+  dim3 grid((unsigned)((Lq + 7) / 8), (unsigned)BH);
+  if (dtype == VSA_F32)
+    sparse_fwd_scalar_kernel<float><<<grid, 256, 0, st>>>((const float*)q, (const float*)k, (const float*)v, selected,
+                                                          kv_sizes, (float*)out, lse2, Lq, Lkv, D, be, topk, scale);
+  else
+    sparse_fwd_scalar_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
+                                                                  (const __nv_bfloat16*)v, selected, kv_sizes,
+                                                                  (__nv_bfloat16*)out, lse2, Lq, Lkv, D, be, topk, scale);
+  return check_launch("sparse_fwd_scalar_kernel");
+}
+
+int sparse_dq_scalar(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
+                     const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
+                     int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale, int dtype,
+                     cudaStream_t st) {
+  int rc = check_scalar_shape(BH, D, "sparse dQ");
+  if (rc) return rc;
+  if (BH == 0 || Lq == 0) return VSA_OK;
+  dim3 grid((unsigned)((Lq + 7) / 8), (unsigned)BH);
+  if (dtype == VSA_F32)
+    sparse_dq_scalar_kernel<float><<<grid, 256, 0, st>>>((const float*)dout, (const float*)q, (const float*)k,
+                                                         (const float*)v, (const float*)out_s, lse2, selected, kv_sizes,
+                                                         delta, (float*)dq, Lq, Lkv, D, be, topk, scale);
+  else
+    sparse_dq_scalar_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+        (const __nv_bfloat16*)out_s, lse2, selected, kv_sizes, delta, (__nv_bfloat16*)dq, Lq, Lkv, D, be, topk, scale);
+  return check_launch("sparse_dq_scalar_kernel");
+}
+
+int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                       const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                       const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
+                       int topk, float scale, int dtype, cudaStream_t st) {
+  int rc = check_scalar_shape(BH, D, "sparse dK/dV");
+  if (rc) return rc;
+  if (BH == 0 || Lkv == 0) return VSA_OK;
+  dim3 grid((unsigned)((Lkv + 7) / 8), (unsigned)BH);
+  if (dtype == VSA_F32)
+    sparse_dkdv_scalar_kernel<float><<<grid, 256, 0, st>>>((const float*)dout, (const float*)q, (const float*)k,
+                                                           (const float*)v, lse2, delta, counts, offsets, inverse,
+                                                           kv_sizes, (float*)dk, (float*)dv, Lq, Lkv, D, be, topk, scale);
+  else
+    sparse_dkdv_scalar_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, lse2,
+        delta, counts, offsets, inverse, kv_sizes, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, Lq, Lkv, D, be, topk, scale);
+  return check_launch("sparse_dkdv_scalar_kernel");
+}
+
+}  // namespace vsa

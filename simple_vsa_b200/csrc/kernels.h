@@ -1,0 +1,50 @@
+// Internal launchers shared between the translation units of the library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vsa {
+
+// ---- scalar kernels (generic_kernels.cu) -------------------------------------------------
+int block_mean_fwd(const void* const* x, void* const* out, const int32_t* const* sizes, const int64_t* L,
+                   int ntensors, int64_t BH, int D, int be, int dtype, cudaStream_t st);
+int block_mean_bwd(void* dx, const void* dmean, const int32_t* sizes, int64_t BH, int64_t L, int D, int be,
+                   int dtype, bool accumulate, cudaStream_t st);
+int coarse_fwd(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
+               int Qb, int Kb, int D, float scale, int dtype, cudaStream_t st);
+int coarse_bwd(const void* d_out_c, const void* out_c, const void* qc, const void* kc, const void* vc,
+               const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb, int Kb,
+               int D, float scale, int dtype, cudaStream_t st);
+int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int topk, int dtype, cudaStream_t st);
+int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int32_t* cursor,
+                 int64_t BH, int Qb, int Kb, int topk, cudaStream_t st);
+int combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out, int64_t BH, int64_t Lq, int D,
+                int be, int dtype, cudaStream_t st);
+int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,
+                int64_t Lq, int D, int be, int dtype, cudaStream_t st);
+int sparse_fwd_scalar(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
+                      void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                      float scale, int dtype, cudaStream_t st);
+int sparse_dq_scalar(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
+                     const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
+                     int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale, int dtype,
+                     cudaStream_t st);
+int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                       const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                       const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
+                       int topk, float scale, int dtype, cudaStream_t st);
+
+// ---- tensor-core kernels, bf16, head dim 128, block volume 64 or 256 (sparse_mma.cu) ------
+bool sparse_tc_eligible(int D, int be, int dtype);
+int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
+                  void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
+                  cudaStream_t st);
+int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
+                 const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
+                 int64_t Lkv, int be, int topk, float scale, cudaStream_t st);
+int sparse_dkdv_tc(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                   const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                   const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
+                   float scale, cudaStream_t st);
+
+}  // namespace vsa

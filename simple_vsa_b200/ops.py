@@ -1,0 +1,327 @@
+"""Host side of the VSA operator: argument checks, buffers, autograd wiring.
+
+Mirrors the reference project's operator layer (``vsa/triton_impl.py:1530-1765``:
+``_TritonSparseAttention``, ``_triton_sparse_attention``,
+``_vsa_with_sparse_executor``) with one difference in structure: the whole
+operator is a single ``autograd.Function`` so that the pooled-branch backward
+runs before the fine backward and the block-mean gradients are accumulated
+straight into dq/dk/dv instead of through three extra full-size tensors.
+
+All compute goes through the C ABI of ``libvsa_b200.so``; torch is used for
+device memory, the current stream and autograd only.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence, Tuple, Union
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import call
+
+BlockSize = Union[int, Sequence[int]]
+
+
+def as_block_elements(block_size: BlockSize) -> int:
+    """An int is a cube edge, a tuple is multiplied out (``vsa/common.py:39-42``)."""
+    if isinstance(block_size, int):
+        return block_size * block_size * block_size
+    return int(math.prod(block_size))
+
+
+def validate_vsa_inputs(q, k, v, variable_block_sizes, q_variable_block_sizes, topk: int, be: int) -> None:
+    """Shape contract of the operator; messages keep the reference's wording (``vsa/common.py:97-134``)."""
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("q, k, and v must have shape [batch, heads, seq_len, dim]")
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    if k.shape[0] != B or v.shape[0] != B or k.shape[1] != H or v.shape[1] != H:
+        raise ValueError("q, k, and v must share batch and head dimensions")
+    if v.shape[2] != Lkv:
+        raise ValueError("k and v must have the same sequence length")
+    if k.shape[-1] != D or v.shape[-1] != D:
+        raise ValueError("q, k, and v must have the same head dimension")
+    if Lq % be or Lkv % be:
+        raise ValueError(f"q/kv sequence lengths must be divisible by block_elements={be}")
+    if variable_block_sizes.numel() != Lkv // be:
+        raise ValueError(
+            f"variable_block_sizes must have length {Lkv // be}, got {variable_block_sizes.numel()}")
+    if q_variable_block_sizes.numel() != Lq // be:
+        raise ValueError(
+            f"q_variable_block_sizes must have length {Lq // be}, got {q_variable_block_sizes.numel()}")
+    if not 1 <= topk <= Lkv // be:
+        raise ValueError(f"topk must be in [1, {Lkv // be}]")
+
+
+def _check_device_dtype(q: Tensor, k: Tensor, v: Tensor) -> int:
+    """Same refusals as the reference launcher (``vsa/triton_impl.py:371-384``)."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("the B200 implementation requires CUDA tensors")
+    if not (q.device == k.device == v.device):
+        raise ValueError("q, k, and v must be on the same CUDA device")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise ValueError("q, k, and v must have the same dtype")
+    if q.dtype == torch.bfloat16:
+        return _lib.VSA_BF16
+    if q.dtype == torch.float32:
+        return _lib.VSA_F32
+    raise ValueError("the B200 path supports bfloat16 and float32 (validation mode)")
+
+
+def _dense(x: Tensor) -> Tensor:
+    """Contiguous and 16-byte aligned (the kernels use 16-byte vector accesses)."""
+    x = x.contiguous()
+    if x.data_ptr() % 16:
+        x = x.clone()
+    return x
+
+
+def _sizes(sizes: Tensor, device) -> Tensor:
+    return sizes.to(device=device, dtype=torch.int32).contiguous()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: Optional[Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+# --------------------------------------------------------------------------------------------
+# thin launch wrappers (no autograd); every tensor is dense and on one device
+# --------------------------------------------------------------------------------------------
+def sparse_forward(q, k, v, selected, kv_sizes, be: int, scale: float, want_lse: bool):
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    dt = _check_device_dtype(q, k, v)
+    out = torch.empty_like(q)
+    lse = torch.empty((B, H, Lq), device=q.device, dtype=torch.float32) if want_lse else None
+    call("vsa_sparse_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), selected.data_ptr(), kv_sizes.data_ptr(),
+         out.data_ptr(), _ptr(lse), B * H, Lq, Lkv, D, be, selected.shape[-1], scale, dt, _stream(q.device))
+    return out, lse
+
+
+def invert_routes(selected: Tensor, key_blocks: int):
+    """CSR of key block -> query blocks: (inverse [B,H,Qb*tk], offsets [B,H,Kb], counts [B,H,Kb]), int32.
+
+    Same triple, in the same order, as the reference's ``_invert_indices`` (``vsa/triton_impl.py:544-595``).
+    """
+    B, H, Qb, tk = selected.shape
+    dev = selected.device
+    counts = torch.empty((B, H, key_blocks), device=dev, dtype=torch.int32)
+    offsets = torch.empty_like(counts)
+    cursor = torch.empty_like(counts)
+    inverse = torch.empty((B, H, Qb * tk), device=dev, dtype=torch.int32)
+    call("vsa_route_invert", selected.data_ptr(), counts.data_ptr(), offsets.data_ptr(), inverse.data_ptr(),
+         cursor.data_ptr(), B * H, Qb, key_blocks, tk, _stream(dev))
+    return inverse, offsets, counts
+
+
+def sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be: int, scale: float):
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    dt = _check_device_dtype(q, k, v)
+    st = _stream(q.device)
+    tk = selected.shape[-1]
+    inverse, offsets, counts = invert_routes(selected, Lkv // be)
+    delta = torch.empty_like(lse)
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    call("vsa_sparse_bwd_dq", dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out_s.data_ptr(),
+         lse.data_ptr(), selected.data_ptr(), kv_sizes.data_ptr(), delta.data_ptr(), dq.data_ptr(),
+         B * H, Lq, Lkv, D, be, tk, scale, dt, st)
+    call("vsa_sparse_bwd_dkdv", dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), lse.data_ptr(),
+         delta.data_ptr(), counts.data_ptr(), offsets.data_ptr(), inverse.data_ptr(), kv_sizes.data_ptr(),
+         dk.data_ptr(), dv.data_ptr(), B * H, Lq, Lkv, D, be, tk, scale, dt, st)
+    return dq, dk, dv
+
+
+def pooled_forward(q, k, v, kv_sizes, q_sizes, be: int, scale: float, topk: int):
+    """Block means, pooled scores/probabilities/output and the Top-K routing table."""
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    Qb, Kb = Lq // be, Lkv // be
+    dt = _check_device_dtype(q, k, v)
+    st = _stream(q.device)
+    dev, ty = q.device, q.dtype
+    qc = torch.empty((B, H, Qb, D), device=dev, dtype=ty)
+    kc = torch.empty((B, H, Kb, D), device=dev, dtype=ty)
+    vc = torch.empty((B, H, Kb, D), device=dev, dtype=ty)
+    call("vsa_block_mean3_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), q_sizes.data_ptr(), kv_sizes.data_ptr(),
+         qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), B * H, Lq, Lkv, D, be, dt, st)
+    scores = torch.empty((B, H, Qb, Kb), device=dev, dtype=ty)
+    probs = torch.empty_like(scores)
+    out_c = torch.empty((B, H, Qb, D), device=dev, dtype=ty)
+    call("vsa_coarse_fwd", qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), scores.data_ptr(), probs.data_ptr(),
+         out_c.data_ptr(), B * H, Qb, Kb, D, scale, dt, st)
+    selected = torch.empty((B, H, Qb, topk), device=dev, dtype=torch.int32)
+    call("vsa_topk", scores.data_ptr(), selected.data_ptr(), B * H * Qb, Kb, topk, dt, st)
+    return qc, kc, vc, scores, probs, out_c, selected
+
+
+class _SparseAttention(torch.autograd.Function):
+    """Route-explicit fine attention (``vsa/triton_impl.py:1530-1580``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, selected, kv_sizes, be, scale):
+        out, lse = sparse_forward(q, k, v, selected, kv_sizes, be, scale, True)
+        ctx.save_for_backward(q, k, v, out, lse, selected, kv_sizes)
+        ctx.be, ctx.scale = be, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, selected, kv_sizes = ctx.saved_tensors
+        with torch.cuda.device(q.device):
+            dq, dk, dv = sparse_backward(_dense(dout), q, k, v, out, lse, selected, kv_sizes, ctx.be, ctx.scale)
+        return dq, dk, dv, None, None, None, None
+
+
+def sparse_attention(q, k, v, selected, variable_block_sizes, *, block_size: BlockSize,
+                     sm_scale: Optional[float] = None) -> Tensor:
+    """Fine attention on caller-supplied routes ``selected [B,H,Qb,topk]`` (``vsa/triton_impl.py:1583-1652``)."""
+    be = as_block_elements(block_size)
+    _check_device_dtype(q, k, v)
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("q, k, and v must have shape [batch, heads, seq_len, dim]")
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    if Lq % be or Lkv % be:
+        raise ValueError(f"q/kv sequence lengths must be divisible by block_elements={be}")
+    if tuple(selected.shape[:3]) != (B, H, Lq // be):
+        raise ValueError("selected must have shape [batch, heads, query_blocks, topk]")
+    tk = selected.shape[-1]
+    if not 1 <= tk <= Lkv // be:
+        raise ValueError(f"selected topk must be in [1, {Lkv // be}]")
+    if variable_block_sizes.numel() != Lkv // be:
+        raise ValueError(
+            f"variable_block_sizes must have {Lkv // be} entries, got {variable_block_sizes.numel()}")
+    scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
+    with torch.cuda.device(q.device):
+        q, k, v = _dense(q), _dense(k), _dense(v)
+        selected = selected.to(device=q.device, dtype=torch.int32).contiguous()
+        sizes = _sizes(variable_block_sizes, q.device)
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+            return _SparseAttention.apply(q, k, v, selected, sizes, be, scale)
+        return sparse_forward(q, k, v, selected, sizes, be, scale, False)[0]
+
+
+class _VideoSparseAttention(torch.autograd.Function):
+    """Whole operator: pooled branch, Top-K, fine branch, gated combine -- and its backward."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, gate, kv_sizes, q_sizes, topk, be, scale, need_grad):
+        B, H, Lq, D = q.shape
+        dt = _check_device_dtype(q, k, v)
+        st = _stream(q.device)
+        qc, kc, vc, scores, probs, out_c, selected = pooled_forward(q, k, v, kv_sizes, q_sizes, be, scale, topk)
+        out_s, lse = sparse_forward(q, k, v, selected, kv_sizes, be, scale, need_grad)
+        out = torch.empty_like(q)
+        call("vsa_combine_fwd", out_s.data_ptr(), out_c.data_ptr(), _ptr(gate), out.data_ptr(), B * H, Lq, D, be,
+             dt, st)
+        if need_grad:
+            saved = [q, k, v, out_s, lse, selected, kv_sizes, q_sizes, qc, kc, vc, probs, out_c]
+            if gate is not None:
+                saved.append(gate)
+            ctx.save_for_backward(*saved)
+            ctx.has_gate = gate is not None
+            ctx.be, ctx.scale = be, scale
+        ctx.mark_non_differentiable(scores, selected, out_c, out_s)
+        return out, scores, selected, out_c, out_s
+
+    @staticmethod
+    def backward(ctx, dout, _dscores, _dselected, _dout_c, _dout_s):
+        saved = ctx.saved_tensors
+        q, k, v, out_s, lse, selected, kv_sizes, q_sizes, qc, kc, vc, probs, out_c = saved[:13]
+        gate = saved[13] if ctx.has_gate else None
+        be, scale = ctx.be, ctx.scale
+        B, H, Lq, D = q.shape
+        Lkv = k.shape[2]
+        Qb, Kb = Lq // be, Lkv // be
+        with torch.cuda.device(q.device):
+            dt = _check_device_dtype(q, k, v)
+            st = _stream(q.device)
+            dout = _dense(dout)
+            d_out_c = torch.empty_like(out_c)
+            dgate = torch.empty_like(gate) if gate is not None else None
+            call("vsa_combine_bwd", dout.data_ptr(), _ptr(gate), out_c.data_ptr(), d_out_c.data_ptr(), _ptr(dgate),
+                 B * H, Lq, D, be, dt, st)
+            ds_ws = torch.empty_like(probs)
+            rowdot = torch.empty((B, H, Qb), device=q.device, dtype=torch.float32)
+            dqc, dkc, dvc = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+            call("vsa_coarse_bwd", d_out_c.data_ptr(), out_c.data_ptr(), qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                 probs.data_ptr(), ds_ws.data_ptr(), rowdot.data_ptr(), dqc.data_ptr(), dkc.data_ptr(),
+                 dvc.data_ptr(), B * H, Qb, Kb, D, scale, dt, st)
+            del ds_ws
+            dq, dk, dv = sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale)
+            call("vsa_block_mean_bwd_accumulate", dq.data_ptr(), dqc.data_ptr(), q_sizes.data_ptr(), B * H, Lq, D,
+                 be, dt, st)
+            call("vsa_block_mean_bwd_accumulate", dk.data_ptr(), dkc.data_ptr(), kv_sizes.data_ptr(), B * H, Lkv, D,
+                 be, dt, st)
+            call("vsa_block_mean_bwd_accumulate", dv.data_ptr(), dvc.data_ptr(), kv_sizes.data_ptr(), B * H, Lkv, D,
+                 be, dt, st)
+        return dq, dk, dv, dgate, None, None, None, None, None, None
+
+
+def vsa_forward_full(q, k, v, variable_block_sizes, q_variable_block_sizes, topk: int, block_size: BlockSize = 64,
+                     compress_attn_weight: Optional[Tensor] = None, sm_scale: Optional[float] = None
+                     ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Run the operator; returns (out, pooled scores, routing table, pooled output, fine output)."""
+    be = as_block_elements(block_size)
+    validate_vsa_inputs(q, k, v, variable_block_sizes, q_variable_block_sizes, topk, be)
+    if compress_attn_weight is not None and compress_attn_weight.shape != q.shape:
+        raise ValueError("compress_attn_weight must have the same shape as q")
+    _check_device_dtype(q, k, v)
+    gate = compress_attn_weight
+    if gate is not None and (gate.device != q.device or gate.dtype != q.dtype):
+        gate = gate.to(device=q.device, dtype=q.dtype)
+    scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    with torch.cuda.device(q.device):
+        q, k, v = _dense(q), _dense(k), _dense(v)
+        gate = _dense(gate) if gate is not None else None
+        kv_sizes = _sizes(variable_block_sizes, q.device)
+        q_sizes = _sizes(q_variable_block_sizes, q.device)
+        need_grad = torch.is_grad_enabled() and any(
+            t is not None and t.requires_grad for t in (q, k, v, gate))
+        return _VideoSparseAttention.apply(q, k, v, gate, kv_sizes, q_sizes, int(topk), be, scale, need_grad)
+
+
+class _BlockMean(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, sizes, be):
+        B, H, L, D = x.shape
+        dt = _lib.VSA_BF16 if x.dtype == torch.bfloat16 else _lib.VSA_F32
+        out = torch.empty((B, H, L // be, D), device=x.device, dtype=x.dtype)
+        call("vsa_block_mean_fwd", x.data_ptr(), sizes.data_ptr(), out.data_ptr(), B * H, L, D, be, dt,
+             _stream(x.device))
+        ctx.save_for_backward(sizes)
+        ctx.shape, ctx.be, ctx.dt = x.shape, be, dt
+        return out
+
+    @staticmethod
+    def backward(ctx, dmean):
+        (sizes,) = ctx.saved_tensors
+        B, H, L, D = ctx.shape
+        with torch.cuda.device(dmean.device):
+            dmean = _dense(dmean)
+            dx = torch.empty(ctx.shape, device=dmean.device, dtype=dmean.dtype)
+            call("vsa_block_mean_bwd", dx.data_ptr(), dmean.data_ptr(), sizes.data_ptr(), B * H, L, D, ctx.be,
+                 ctx.dt, _stream(dmean.device))
+        return dx, None, None
+
+
+def block_mean(x: Tensor, variable_block_sizes: Tensor, block_elements: int) -> Tensor:
+    """Padding-aware block means ``[B,H,L,D] -> [B,H,L/be,D]`` (``vsa/common.py:55-82``), differentiable."""
+    if not x.is_cuda:
+        raise ValueError("the B200 implementation requires CUDA tensors")
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("the B200 path supports bfloat16 and float32 (validation mode)")
+    if x.ndim != 4 or x.shape[2] % block_elements:
+        raise ValueError(f"sequence length must be divisible by block_elements={block_elements}")
+    with torch.cuda.device(x.device):
+        return _BlockMean.apply(_dense(x), _sizes(variable_block_sizes, x.device), int(block_elements))

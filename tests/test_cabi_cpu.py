@@ -1,0 +1,83 @@
+"""CPU-side checks: the C ABI library loads and exports what the header declares; host-side
+argument checks behave like the reference's; nothing here launches a kernel."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "vsa_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(vsa_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    import simple_vsa_b200._lib as L
+    lib = ctypes.CDLL(L.LIB_PATH)
+    names = _declared_symbols()
+    assert len(names) >= 15
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/vsa_b200.h but not exported"
+    for name in list(L.SIGNATURES) + list(L.PLAIN):
+        assert name in names, f"{name} bound in _lib.py but not declared in the header"
+    assert L.lib.vsa_version() >= 100
+    assert L.last_error() == ""
+
+
+def test_bad_arguments_are_refused_before_any_launch():
+    import simple_vsa_b200._lib as L
+    # null pointers and a topk out of range come back as status codes with a message, no CUDA call made
+    rc = L.lib.vsa_topk(None, None, 4, 8, 2, 0, None)
+    assert rc == L.ERR_BAD_ARGUMENT and "null" in L.last_error()
+    rc = L.lib.vsa_topk(1, 1, 4, 8, 9, 0, None)
+    assert rc == L.ERR_BAD_ARGUMENT and "topk" in L.last_error()
+    rc = L.lib.vsa_sparse_fwd(1, 1, 1, 1, 1, 1, None, 1, 100, 128, 128, 64, 1, 0.1, 0, None)
+    assert rc == L.ERR_BAD_ARGUMENT and "divisible" in L.last_error()
+    rc = L.lib.vsa_sparse_fwd(1, 1, 1, 1, 1, 1, None, 1, 128, 128, 128, 64, 1, 0.1, 7, None)
+    assert rc == L.ERR_UNSUPPORTED
+    with pytest.raises(ValueError, match="topk"):
+        L.call("vsa_topk", 1, 1, 4, 8, 0, 0, None)
+
+
+def test_operator_validation_matches_reference_messages():
+    import simple_vsa_b200 as V
+    q = torch.randn(1, 1, 12, 8)
+    s3 = torch.full((3,), 4)
+    with pytest.raises(ValueError, match="divisible"):
+        V.b200_vsa(q[:, :, :10], q[:, :, :10], q[:, :, :10], s3, s3, 1, (1, 1, 4))
+    with pytest.raises(ValueError, match="variable_block_sizes"):
+        V.b200_vsa(q, q, q, s3[:2], s3, 1, (1, 1, 4))
+    with pytest.raises(ValueError, match="topk"):
+        V.b200_vsa(q, q, q, s3, s3, 4, (1, 1, 4))
+    with pytest.raises(ValueError, match="same shape as q"):
+        V.b200_vsa(q, q, q, s3, s3, 1, (1, 1, 4), torch.randn(1, 1, 12, 4))
+    with pytest.raises(ValueError, match="requires CUDA tensors"):
+        V.b200_vsa(q, q, q, s3, s3, 1, (1, 1, 4))
+    with pytest.raises(ValueError, match="requires CUDA tensors"):
+        V.b200_sparse_attention(q, q, q, torch.zeros(1, 1, 3, 1, dtype=torch.int32), s3, block_size=(1, 1, 4))
+    assert V.as_block_elements(2) == 8 and V.as_block_elements((4, 4, 4)) == 64
+    assert V.triton_vsa is V.b200_vsa and V.helion_sparse_attention is V.b200_sparse_attention
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    import importlib
+    import simple_vsa_b200._lib as L
+    monkeypatch.setattr(L, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError, match="no other compute path"):
+        L._load()
+    importlib.reload(L)
+
+
+def test_product_package_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "simple_vsa_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("oracle form", ""), f"{f} mentions the oracle"
