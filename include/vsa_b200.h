@@ -54,6 +54,16 @@ int vsa_version(void);
 /* Number of kernels this library has launched in the process so far (all threads). */
 int64_t vsa_launch_count(void);
 
+/* Device-side status word: 0, or the code of the first bounded wait (mbarrier) that ran out in a
+ * tcgen05 kernel since the last call.  Synchronises the device; clears the word. */
+int vsa_device_status(int* status);
+
+/* Unit check of the tcgen05 building blocks (TMA boxes, shared-memory operand descriptors, tensor
+ * memory read-out): out[128x64] fp32 = A * B for bf16 operands.  mode 0: a is [128 x 128] with the
+ * reduction dim contiguous, b is [64 x 128] likewise (out = a b^T).  mode 1: a is [128 k x 128 m], b is
+ * [128 k x 64 n] (out = a^T b).  No counterpart in the reference; used by the GPU tests. */
+int vsa_selftest_umma(const void* a, const void* b, float* out, int mode, void* stream);
+
 /* Padding-aware block means of q, k and v in ONE pass: fp32 sum of the first
  * sizes[b] tokens / max(sizes[b],1), rounded to dtype.
  * Replaces block_mean / fused_block_mean x3: vsa/common.py:55-82,
@@ -105,8 +115,8 @@ int vsa_coarse_bwd(const void* d_out_c, const void* out_c,
                    int dtype, void* stream);
 
 /* Fine attention of each query block over the valid tokens of its selected key
- * blocks; lse2 (may be NULL) receives row_max + log2(row_sum) of the scores
- * times scale*log2(e).
+ * blocks; lse2 (may be NULL, which selects the warp-level kernel instead of the tcgen05 one)
+ * receives row_max + log2(row_sum) of the scores times scale*log2(e).
  * Replaces _triton_sparse_attention_forward and both forward kernels:
  * vsa/triton_impl.py:39-355,358-473 (oracle form: vsa/torch_impl.py:86-106). */
 int vsa_sparse_fwd(const void* q, const void* k, const void* v,

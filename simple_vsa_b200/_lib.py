@@ -32,6 +32,8 @@ SIGNATURES = {
     "vsa_sparse_bwd_dq": [P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dkdv": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_combine_fwd": [P, P, P, P, L, L, I, I, I, P],
+    "vsa_selftest_umma": [P, P, P, I, P],
+    "vsa_device_status": [P],
     "vsa_combine_bwd": [P, P, P, P, P, L, L, I, I, I, P],
 }
 PLAIN = {"vsa_last_error_string": ([], c_char_p), "vsa_version": ([], c_int),
@@ -60,6 +62,15 @@ def _load() -> ctypes.CDLL:
 
 
 lib = _load()
+
+
+def device_status() -> int:
+    """Fetch and clear the device status word (synchronises): 0 or the code of a timed-out wait."""
+    out = ctypes.c_int(0)
+    rc = lib.vsa_device_status(ctypes.byref(out))
+    if rc:
+        raise VsaError(f"vsa_device_status: {last_error()}")
+    return out.value
 
 
 def last_error() -> str:

@@ -60,7 +60,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
 
     def compile_one(job):
         src, obj = job
-        proc = subprocess.run([nvcc, *NVCC_FLAGS, "-c", src, "-o", obj], capture_output=True, text=True)
+        extra = os.environ.get("VSA_EXTRA_NVCC_FLAGS", "").split()
+        proc = subprocess.run([nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj], capture_output=True, text=True)
         return src, proc
 
     with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, min(8, len(jobs)))) as pool:

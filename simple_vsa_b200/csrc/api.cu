@@ -35,10 +35,15 @@ int check_launch(const char* what) {
   return fail(VSA_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
 }
 
-// VSA_B200_KERNELS=scalar forces the CUDA-core kernels everywhere (for cross-checks).
+// VSA_B200_KERNELS selects the fine-attention kernels (for cross-checks): "scalar" = CUDA cores
+// everywhere, "mma" = warp-level mma.sync kernels, anything else = tcgen05 where available.
 static bool scalar_forced() {
   const char* e = std::getenv("VSA_B200_KERNELS");
   return e && std::strcmp(e, "scalar") == 0;
+}
+static bool mma_forced() {
+  const char* e = std::getenv("VSA_B200_KERNELS");
+  return e && std::strcmp(e, "mma") == 0;
 }
 
 static int check_dtype(int dtype) {
@@ -160,8 +165,17 @@ int vsa_sparse_fwd(const void* q, const void* k, const void* v, const int32_t* s
   int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
   if (rc) return rc;
   VSA_REQUIRE(q && k && v && selected && kv_sizes && out, "sparse forward: null pointer");
-  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
-    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, (cudaStream_t)stream);
+  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype)) {
+    if (lse2 && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk)) {
+      rc = sparse_fwd_umma(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, (cudaStream_t)stream);
+      if (rc) return rc;
+      // exact recomputation of the (normally zero) tiles the fixed-shift softmax marked as out of range
+      return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, true,
+                           (cudaStream_t)stream);
+    }
+    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, false,
+                         (cudaStream_t)stream);
+  }
   return sparse_fwd_scalar(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype,
                            (cudaStream_t)stream);
 }
@@ -200,6 +214,16 @@ int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const vo
                           topk, scale, (cudaStream_t)stream);
   return sparse_dkdv_scalar(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, D, be,
                             topk, scale, dtype, (cudaStream_t)stream);
+}
+
+int vsa_selftest_umma(const void* a, const void* b, float* out, int mode, void* stream) {
+  VSA_REQUIRE(a && b && out && (mode == 0 || mode == 1), "selftest: bad argument");
+  return umma_selftest(a, b, out, mode, (cudaStream_t)stream);
+}
+
+int vsa_device_status(int* status) {
+  VSA_REQUIRE(status, "device status: null pointer");
+  return device_status_fetch_and_clear(status);
 }
 
 int vsa_combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out, int64_t BH, int64_t Lq, int D,

@@ -36,9 +36,11 @@ int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const voi
 
 // ---- tensor-core kernels, bf16, head dim 128, block volume 64 or 256 (sparse_mma.cu) ------
 bool sparse_tc_eligible(int D, int be, int dtype);
+// redo_only: recompute only the 64-row query tiles whose first lse2 entry is NaN (the marker the
+// tcgen05 forward leaves on a tile whose fixed softmax shift ran out of range).
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                  cudaStream_t st);
+                  bool redo_only, cudaStream_t st);
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
                  const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
                  int64_t Lkv, int be, int topk, float scale, cudaStream_t st);
@@ -46,5 +48,13 @@ int sparse_dkdv_tc(const void* dout, const void* q, const void* k, const void* v
                    const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                    const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
                    float scale, cudaStream_t st);
+
+// ---- tcgen05 / TMA kernels (sparse_umma.cu) -----------------------------------------------------
+bool sparse_umma_eligible(int D, int be, int dtype, int topk);
+int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
+                    void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
+                    cudaStream_t st);
+int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st);
+int device_status_fetch_and_clear(int* status);
 
 }  // namespace vsa

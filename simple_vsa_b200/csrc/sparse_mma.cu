@@ -98,8 +98,12 @@ __global__ void __launch_bounds__(kThreads, 2)
 sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
                       bf16* __restrict__ out, float* __restrict__ lse2, long long Lq, long long Lkv, int topk,
-                      float scale) {
+                      float scale, int redo_only) {
   extern __shared__ __align__(128) uint8_t smem[];
+  if (redo_only) {   // only tiles the tcgen05 forward marked with a NaN statistic are recomputed
+    const float mark = lse2[(long long)blockIdx.y * Lq + (long long)blockIdx.x * kTile];
+    if (mark == mark) return;
+  }
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sK = sQ + kTileBytes;          // two stages
   const uint32_t sV = sK + 2 * kTileBytes;      // two stages
@@ -560,7 +564,7 @@ bool sparse_tc_eligible(int D, int be, int dtype) { return dtype == VSA_BF16 && 
 
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                  cudaStream_t st) {
+                  bool redo_only, cudaStream_t st) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
   dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
@@ -568,11 +572,11 @@ int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* se
   if (be == 64) {
     if ((rc = set_smem(sparse_fwd_mma_kernel<1>, kFwdSmem, "sparse forward"))) return rc;
     sparse_fwd_mma_kernel<1><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
-                                                               kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale);
+                                                               kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
   } else {
     if ((rc = set_smem(sparse_fwd_mma_kernel<4>, kFwdSmem, "sparse forward"))) return rc;
     sparse_fwd_mma_kernel<4><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
-                                                               kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale);
+                                                               kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
   }
   return check_launch("sparse_fwd_mma_kernel");
 }

@@ -1,0 +1,573 @@
+// Fine (block-sparse) attention forward on the Blackwell tensor path: TMA tile gathers by
+// block id, tcgen05.mma with accumulators in tensor memory, warp-specialised softmax.
+//
+// Formulation.  A 64-row query tile gives only M = 64 for the usual S = Q K^T product, which
+// runs tcgen05 at half rate.  The kernel therefore computes the TRANSPOSED products on PAIRS of
+// selected key tiles:
+//     S^T [128 key tokens x 64 query rows] = K2 [128 x 128] * Q^T          (M 128, N 64, K 128)
+//     O^T [128 dims       x 64 query rows] += V2^T [128 x 128] * P^T       (M 128, N 64, K 128)
+// K2/V2 are two 64-token tiles stacked in shared memory by four TMA boxes each.  In tensor
+// memory a lane is then a key token and a column a query row, so the softmax statistics run
+// ACROSS lanes.  They are handled without per-tile cross-lane traffic:
+//   * the shift m[q] is the exact column maximum of the FIRST live pair only (one cross-lane
+//     reduction per CTA); softmax is shift-invariant, so any later score simply gives
+//     P = 2^(s-m) > 1, which bf16 and fp32 hold up to 2^127;
+//   * every thread keeps its own partial row sums (64 registers) and they are reduced across
+//     lanes once at the end;
+//   * if a sum or an output leaves the finite range (scores more than ~2^7 apart in log2
+//     units from the first pair's maximum) the tile writes NaN into its log-sum-exp rows and
+//     the exact warp-level kernel recomputes just those tiles in a follow-up launch.
+// P^T is written by its owner thread as one swizzled 128-byte row of shared memory (N-major B
+// operand), so no transposition is ever needed.
+//
+// Roles: warp 0 = K producer, warp 1 = V producer (four lanes, one TMA box each; warp 1 also owns the
+// tensor memory), warp 2 = issuer of the S^T MMAs, warp 3 = issuer of the O^T MMAs, warps 4-11 = softmax (a TMEM lane quarter and half of the
+// query-row columns each).  Every mbarrier wait is bounded; on a time-out the CTA records an error code in a
+// device status word, stops issuing work, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "umma.cuh"
+
+namespace vsa {
+
+__device__ int g_device_status = 0;
+
+// Optional timeline of CTA (0,0), compiled in only with -DVSA_TRACE (a development aid).
+#ifdef VSA_TRACE
+__device__ long long g_trace[16 * 128];
+#define VSA_TRACE_AT(slot, p) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (p) < 128) g_trace[(slot) * 128 + (p)] = clock64(); } while (0)
+#else
+#define VSA_TRACE_AT(slot, p) do { } while (0)
+#endif
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+using namespace umma;
+
+constexpr int kD = 128;
+constexpr int kTile = 64;
+constexpr int kMaxTiles = 1024;        // live 64-token key tiles per query tile the list can hold
+constexpr int kSlab = 64 * 128;        // one TMA box: 64 rows x 128 bytes
+constexpr int kPairHalf = 2 * kSlab;   // 128 rows x 128 bytes (one head-dim half of a stacked pair)
+constexpr int kPairBytes = 2 * kPairHalf;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kSBufs = 4;              // S^T accumulators in flight (64 columns each); O^T sits behind them
+
+// ---- host: tensor maps ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [rows, 128] bf16 row-major, boxes of 64 rows x 64 columns, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int64_t rows, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(VSA_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
+  if (reinterpret_cast<uintptr_t>(ptr) % 16) return fail(VSA_ERR_BAD_ARGUMENT, "%s: pointer is not 16-byte aligned", what);
+  if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "%s: %lld rows exceed the TMA coordinate range", what, (long long)rows);
+  const cuuint64_t gdim[2] = {(cuuint64_t)kD, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)kD * 2};
+  const cuuint32_t box[2] = {64, 64};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(VSA_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with code %d", what, (int)r);
+  return VSA_OK;
+}
+
+__device__ __forceinline__ void report_timeout(int code) { atomicCAS(&g_device_status, 0, code); }
+// all waits of this file poll the status word so that a failure anywhere drains the grid quickly
+#define VSA_WAIT(bar_, parity_) mbar_wait((bar_), (parity_), &g_device_status)
+#define VSA_WARP_WAIT(bar_, parity_) warp_wait((bar_), (parity_), &g_device_status, lane)
+
+// One 64x128 tile = two boxes (head-dim halves); `dst` is the row offset inside a stacked pair.
+__device__ __forceinline__ void load_tile(uint32_t pair_base, int half_rows_off, const CUtensorMap* map, int row,
+                                          uint32_t bar) {
+  tma_load_2d(pair_base + half_rows_off, map, 0, row, bar);
+  tma_load_2d(pair_base + kPairHalf + half_rows_off, map, 64, row, bar);
+}
+
+// ---- descriptor / TMEM self-test ---------------------------------------------------------------------
+// mode 0: D[128x64] = A[128 x 128 (k contiguous)] * B[64 x 128 (k contiguous)]^T
+// mode 1: D[128x64] = A[128 k x 128 m (m contiguous)]^T * B[128 k x 64 n (n contiguous)], B written by threads
+__global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                            const __grid_constant__ CUtensorMap map_b,
+                                                            const bf16* __restrict__ b_raw, float* __restrict__ out,
+                                                            int mode) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sA = base, sB = base + kPairBytes;
+  const uint32_t bar_load = base + kPairBytes + 16384, bar_mma = bar_load + 8, tmem_slot = bar_load + 16;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(bar_load, 1);
+    mbar_init(bar_mma, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(base_ptr + kPairBytes + 16384 + 16);
+  bool ok = true;
+  if (mode == 1) {   // B rows written by their owner thread as swizzled 128-byte rows
+    const uint4* src = reinterpret_cast<const uint4*>(b_raw + tid * 64);
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      *reinterpret_cast<uint4*>(base_ptr + kPairBytes + tid * 128 + ((c ^ (tid & 7)) << 4)) = src[c];
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t bytes = kPairBytes + (mode == 0 ? 2 * kSlab : 0);
+    mbar_arrive_expect_tx(bar_load, bytes);
+    load_tile(sA, 0, &map_a, 0, bar_load);
+    load_tile(sA, kSlab, &map_a, 64, bar_load);
+    if (mode == 0) {
+      tma_load_2d(sB, &map_b, 0, 0, bar_load);
+      tma_load_2d(sB + kSlab, &map_b, 64, 0, bar_load);
+    }
+    ok = VSA_WAIT(bar_load, 0);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        if (mode == 0) {
+          const uint32_t off = (ks >> 2) * kPairHalf + (ks & 3) * 32;
+          const uint32_t offb = (ks >> 2) * kSlab + (ks & 3) * 32;
+          mma_ss(tmem, smem_desc(sA + off, 16, 1024), smem_desc(sB + offb, 16, 1024), instr_desc(128, 64, 0, 0), ks > 0);
+        } else {
+          mma_ss(tmem, smem_desc(sA + ks * 2048, kPairHalf, 1024), smem_desc(sB + ks * 2048, 16, 1024),
+                 instr_desc(128, 64, 1, 1), ks > 0);
+        }
+      }
+      mma_commit(bar_mma);
+    } else {
+      report_timeout(101);
+    }
+  }
+  __syncthreads();
+  if (VSA_WAIT(bar_mma, 0)) {
+    tc_fence_after();
+    uint32_t r[32];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + half * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) out[tid * 64 + half * 32 + j] = __uint_as_float(r[j]);
+    }
+  } else {
+    report_timeout(102);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 64);
+}
+
+// ---- forward -------------------------------------------------------------------------------------------
+struct FwdSmem {
+  static constexpr uint32_t q = 0;                               // 16 KB
+  static constexpr uint32_t k = q + 2 * kSlab;                   // 2 stages x 32 KB
+  static constexpr uint32_t v = k + 2 * kPairBytes;              // 2 stages x 32 KB
+  static constexpr uint32_t p = v + 2 * kPairBytes;              // 2 buffers x 16 KB
+  static constexpr uint32_t tile_row = p + 2 * kPairHalf;        // int32 [kMaxTiles]
+  static constexpr uint32_t tile_valid = tile_row + 4 * kMaxTiles;   // uint8 [kMaxTiles]
+  static constexpr uint32_t m_warp = tile_valid + kMaxTiles;     // float [4 lane quarters][64]
+  static constexpr uint32_t m_col = m_warp + 4 * 64 * 4;         // float [64]
+  static constexpr uint32_t l_col = m_col + 64 * 4;              // float [64]
+  static constexpr uint32_t bars = l_col + 64 * 4;               // 8-byte mbarriers
+  static constexpr uint32_t misc = bars + 32 * 8;                // tmem base, n_live, flags
+  static constexpr uint32_t total = misc + 64;
+};
+constexpr int kFwdThreads = 384;   // K producer, V producer, MMA issuer, TMEM owner, eight softmax warps
+enum FwdBar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, P_FULL = 9, P_EMPTY = 11, O_FULL = 13,
+              S_FULL = 14, S_EMPTY = 14 + kSBufs };
+
+template <int SUB>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const int32_t* __restrict__ selected,
+                       const int32_t* __restrict__ kv_sizes, bf16* __restrict__ out, float* __restrict__ lse2,
+                       long long Lq, long long Lkv, int topk, float scale) {
+  extern __shared__ uint8_t smem_raw[];
+  if (*(volatile int*)&g_device_status != 0) return;   // an earlier wait ran out: drain without touching anything
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qtile = blockIdx.x;
+  const long long bh = blockIdx.y;
+  const int Qb = (int)(Lq / (kTile * SUB));
+  const int qb = qtile / SUB;
+  const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
+  const int n_iter = topk * SUB;
+  const float c = scale * kLog2e;
+
+  int32_t* tile_row = reinterpret_cast<int32_t*>(sm + FwdSmem::tile_row);
+  uint8_t* tile_valid = sm + FwdSmem::tile_valid;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(sm + FwdSmem::misc);
+  auto bar = [&](int i) -> uint32_t { return base + FwdSmem::bars + 8u * i; };
+
+  // ---- set-up: barriers, tensor memory, the list of live key tiles ----
+  if (tid == 0) {
+    mbar_init(bar(Q_FULL), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(K_FULL + i), 4);      // four producer lanes, one TMA box each
+      mbar_init(bar(V_FULL + i), 4);
+      mbar_init(bar(K_EMPTY + i), 1);
+      mbar_init(bar(V_EMPTY + i), 1);
+      mbar_init(bar(P_FULL + i), 8);      // one elected lane per softmax warp
+      mbar_init(bar(P_EMPTY + i), 1);
+    }
+    for (int i = 0; i < kSBufs; ++i) {
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(S_EMPTY + i), 8);
+    }
+    mbar_init(bar(O_FULL), 1);
+    misc[2] = 0u;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  // every thread looks up some of the routed tiles (two dependent global loads, all in flight at once) ...
+  for (int it = tid; it < n_iter; it += kFwdThreads) {
+    const int kvb = sel[it / SUB];
+    const int left = kv_sizes[kvb] - (it % SUB) * kTile;
+    tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
+    tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
+  }
+  __syncthreads();
+  if (warp == 2) {   // ... then one warp squeezes out the empty ones in place, keeping the routing order
+    int n_live = 0;
+    for (int it0 = 0; it0 < n_iter; it0 += 32) {
+      const int it = it0 + lane;
+      const int valid = it < n_iter ? (int)tile_valid[it] : 0;
+      const int row = it < n_iter ? tile_row[it] : 0;
+      const unsigned live = __ballot_sync(0xffffffffu, valid > 0);
+      __syncwarp();
+      if (valid > 0) {
+        const int pos = n_live + __popc(live & ((1u << lane) - 1u));
+        tile_row[pos] = row;
+        tile_valid[pos] = (uint8_t)valid;
+      }
+      n_live += __popc(live);
+      __syncwarp();
+    }
+    if (lane == 0) misc[1] = (uint32_t)n_live;
+  }
+  if (warp == 1) {
+    tmem_alloc(base + FwdSmem::misc, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = misc[0];
+  const int n_live = (int)misc[1];
+  const int n_pairs = (n_live + 1) >> 1;
+  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 64 * kSBufs;   // S^T buffers first, then O^T
+  const long long kv_row_base = bh * Lkv;
+  bool ok = true;
+
+  if (warp == 0 || warp == 1) {
+    // ================= TMA producers: warp 0 streams K pairs, warp 1 streams V pairs =================
+    // Four lanes issue one 64-row x 128-byte box each (tile a/b x head-dim half 0/1), in lock step:
+    // a single thread issuing all the boxes of a pair was the slowest stage of the pipeline.
+    const bool is_k = warp == 0;
+    if (is_k && lane == 0) {
+      mbar_arrive_expect_tx(bar(Q_FULL), 2 * kSlab);
+      const int qrow = (int)(bh * Lq + (long long)qtile * kTile);
+      tma_load_2d(base + FwdSmem::q, &map_q, 0, qrow, bar(Q_FULL));
+      tma_load_2d(base + FwdSmem::q + kSlab, &map_q, 64, qrow, bar(Q_FULL));
+    }
+    {
+      const int which = lane & 1, dhalf = (lane >> 1) & 1;  // tile a or b of the pair; head-dim half
+      const CUtensorMap* map = is_k ? &map_k : &map_v;
+      const int full0 = is_k ? K_FULL : V_FULL, empty0 = is_k ? K_EMPTY : V_EMPTY;
+      const uint32_t ring = base + (is_k ? FwdSmem::k : FwdSmem::v);
+      for (int p = 0; p < n_pairs; ++p) {
+        const int s = p & 1;
+        const uint32_t ph = (p >> 1) & 1;
+        int idx = 2 * p + which;
+        if (idx >= n_live) idx = 2 * p;                     // odd tail: repeat the first tile (masked later)
+        const int row = (int)(kv_row_base + tile_row[idx]);
+        ok = VSA_WARP_WAIT(bar(empty0 + s), ph ^ 1);
+        if (!ok) break;
+        if (lane < 4) {
+          mbar_arrive_expect_tx(bar(full0 + s), kSlab);
+          tma_load_2d(ring + s * kPairBytes + dhalf * kPairHalf + which * kSlab, map, dhalf * 64, row, bar(full0 + s));
+        }
+      }
+      if (!ok && lane == 0) report_timeout(1);
+    }
+  } else if (warp == 2) {
+    // ================= MMA issuer 1: S^T = K2 Q^T, as far ahead as operands and accumulators allow =================
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(128, 64, 0, 0);
+      ok = VSA_WAIT(bar(Q_FULL), 0);
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p & 1, b = p % kSBufs;
+        ok = VSA_WAIT(bar(K_FULL + s), (p >> 1) & 1) && VSA_WAIT(bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
+        if (!ok) break;
+        VSA_TRACE_AT(0, p);
+        tc_fence_after();
+        const uint32_t ka = base + FwdSmem::k + s * kPairBytes, qbs = base + FwdSmem::q;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem_s0 + b * 64, smem_desc(ka + (ks >> 2) * kPairHalf + (ks & 3) * 32, 16, 1024),
+                 smem_desc(qbs + (ks >> 2) * kSlab + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        mma_commit(bar(K_EMPTY + s));
+        mma_commit(bar(S_FULL + b));
+        VSA_TRACE_AT(1, p);
+      }
+      if (!ok) report_timeout(2);
+    }
+  } else if (warp == 3) {
+    // ================= MMA issuer 2: O^T += V2^T P^T =================
+    if (lane == 0) {
+      constexpr uint32_t idesc_o = instr_desc(128, 64, 1, 1);
+      for (int j = 0; j < n_pairs && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = VSA_WAIT(bar(V_FULL + s), ph);
+        VSA_TRACE_AT(2, j);
+        ok = ok && VSA_WAIT(bar(P_FULL + s), ph);
+        if (!ok) break;
+        VSA_TRACE_AT(3, j);
+        tc_fence_after();
+        const uint32_t va = base + FwdSmem::v + s * kPairBytes, pb = base + FwdSmem::p + s * kPairHalf;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem_o, smem_desc(va + ks * 2048, kPairHalf, 1024), smem_desc(pb + ks * 2048, 16, 1024), idesc_o,
+                 (j > 0 || ks > 0) ? 1u : 0u);
+        mma_commit(bar(V_EMPTY + s));
+        mma_commit(bar(P_EMPTY + s));
+        VSA_TRACE_AT(4, j);
+      }
+      if (ok) mma_commit(bar(O_FULL));
+      if (!ok) report_timeout(5);
+    }
+  } else if (warp >= 4) {
+    // ================= softmax warps =================
+    // warp -> (TMEM lane quarter = warp & 3, column half = (warp-2) >> 2): a thread owns one key token of
+    // the stacked pair (lane t) and 32 of the 64 query rows (columns c0..c0+31).
+    const int quarter = warp & 3;
+    const int chalf = (warp - 4) >> 2;
+    const int c0 = chalf * 32;
+    const int t = quarter * 32 + lane;
+    const int half = t >> 6, r = t & 63;
+    const int st = tid - 128;                     // 0..255 among the softmax threads
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    float* m_warp = reinterpret_cast<float*>(sm + FwdSmem::m_warp);
+    float* m_col = reinterpret_cast<float*>(sm + FwdSmem::m_col);
+    float* l_col = reinterpret_cast<float*>(sm + FwdSmem::l_col);
+    float lsum[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) lsum[j] = 0.f;
+
+    for (int p = 0; p < n_pairs && ok; ++p) {
+      const int s = p & 1;
+      const uint32_t ph = (p >> 1) & 1;
+      const int idx = 2 * p + half;
+      const int valid = idx < n_live ? (int)tile_valid[idx] : 0;
+      const bool live = r < valid;
+      const int sb = p % kSBufs;
+      ok = VSA_WARP_WAIT(bar(S_FULL + sb), (p / kSBufs) & 1);
+      if (!ok) break;
+      if (tid == 128) VSA_TRACE_AT(5, p);
+      tc_fence_after();
+      uint32_t sv[32];
+      tmem_ld32(tmem_s0 + sb * 64 + lane_addr + c0, sv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(S_EMPTY + sb));
+      if (tid == 128) VSA_TRACE_AT(6, p);
+
+      if (p == 0) {   // exact column maxima of the first live pair: warp shuffle, then across the lane quarters
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float x = warp_max(live ? __uint_as_float(sv[j]) * c : -INFINITY);
+          if (lane == 0) m_warp[quarter * 64 + c0 + j] = x;
+        }
+        named_barrier(1, 256);
+        if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st]));
+        named_barrier(1, 256);
+      }
+      // padding rows of a ragged tile (and the repeated tile of an odd tail): whatever sits in V there
+      // must not reach the tensor core, where 0 * NaN would poison the sum
+      if (!live && chalf == 0) {
+        ok = VSA_WAIT(bar(V_FULL + s), ph);
+        uint8_t* vrow = sm + FwdSmem::v + s * kPairBytes + t * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          *reinterpret_cast<uint4*>(vrow + ch * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(vrow + kPairHalf + ch * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);     // keep the warp's control flow uniform
+      if (!ok) break;
+      uint32_t packed[16];
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 m4 = *reinterpret_cast<const float4*>(m_col + c0 + 4 * j4);
+        const float p0 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m4.x)) : 0.f;
+        const float p1 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m4.y)) : 0.f;
+        const float p2 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m4.z)) : 0.f;
+        const float p3 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m4.w)) : 0.f;
+        lsum[4 * j4 + 0] += p0; lsum[4 * j4 + 1] += p1; lsum[4 * j4 + 2] += p2; lsum[4 * j4 + 3] += p3;
+        packed[2 * j4] = pack_bf16(p0, p1);
+        packed[2 * j4 + 1] = pack_bf16(p2, p3);
+      }
+      if (tid == 128) VSA_TRACE_AT(7, p);
+      ok = VSA_WARP_WAIT(bar(P_EMPTY + s), ph ^ 1);
+      if (!ok) break;
+      if (tid == 128) VSA_TRACE_AT(8, p);
+      uint8_t* prow = sm + FwdSmem::p + s * kPairHalf + t * 128;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)     // this thread's 32 query rows are chunks 4*chalf .. 4*chalf+3 of row t
+        *reinterpret_cast<uint4*>(prow + (((4 * chalf + ch) ^ (t & 7)) << 4)) =
+            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL + s));
+      if (tid == 128) VSA_TRACE_AT(9, p);
+    }
+    if (!ok) report_timeout(3);
+
+    // ---- epilogue: reduce the row sums across lanes (fixed order), normalise O^T, transpose via shared memory ----
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float x = warp_sum(lsum[j]);
+      if (lane == 0) m_warp[quarter * 64 + c0 + j] = x;       // the maxima scratch is free by now
+    }
+    named_barrier(1, 256);
+    if (st < 64) l_col[st] = (m_warp[st] + m_warp[64 + st]) + (m_warp[128 + st] + m_warp[192 + st]);
+    named_barrier(1, 256);
+    if (ok && n_pairs > 0) ok = VSA_WARP_WAIT(bar(O_FULL), 0);
+    if (!ok) report_timeout(4);
+    tc_fence_after();
+    bool finite = true;
+    bf16* stage = reinterpret_cast<bf16*>(sm + FwdSmem::k);     // [64 query rows][128 dims], all MMAs are done
+    if (ok && n_pairs > 0) {
+      uint32_t ov[32];
+      tmem_ld32(tmem_o + lane_addr + c0, ov);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int qi = c0 + j;
+        const float l = l_col[qi];
+        const float o = __uint_as_float(ov[j]) / l;
+        finite = finite && (fabsf(o) <= 3.0e38f) && (l <= 3.0e38f);
+        stage[qi * kD + t] = __float2bfloat16_rn(o);
+      }
+    } else {
+      for (int j = 0; j < 32; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(n_pairs == 0 ? NAN : 0.f);
+    }
+    // vote across the softmax threads through shared memory
+    volatile uint32_t* flag = misc + 2;
+    if (!finite) *flag = 1u;
+    named_barrier(1, 256);
+    const bool redo = (*flag != 0u) && ok;
+    bf16* og = out + (bh * Lq + (long long)qtile * kTile) * kD;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int cidx = st + 256 * i;                // 1024 chunks of 16 bytes
+      const int row = cidx >> 4, ch = cidx & 15;
+      *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
+    }
+    if (st < 64) {
+      const float l = l_col[st];
+      lse2[bh * Lq + (long long)qtile * kTile + st] = (redo || n_pairs == 0) ? NAN : m_col[st] + log2f(l);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+
+// ---- host entry points ---------------------------------------------------------------------------------------
+bool sparse_umma_eligible(int D, int be, int dtype, int topk) {
+  if (dtype != VSA_BF16 || D != 128) return false;
+  if (be == 64) return topk <= kMaxTiles;
+  if (be == 256) return topk * 4 <= kMaxTiles;
+  return false;
+}
+
+int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
+                    void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
+                    cudaStream_t st) {
+  if (BH == 0 || Lq == 0) return VSA_OK;
+  if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_map(&mq, q, BH * Lq, "sparse forward (q)"))) return rc;
+  if ((rc = make_map(&mk, k, BH * Lkv, "sparse forward (k)"))) return rc;
+  if ((rc = make_map(&mv, v, BH * Lkv, "sparse forward (v)"))) return rc;
+  const int smem = FwdSmem::total + 1024;
+  dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
+  cudaError_t e;
+  if (be == 64) {
+    e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
+    sparse_fwd_umma_kernel<1><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale);
+  } else {
+    e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
+    sparse_fwd_umma_kernel<4><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale);
+  }
+  return check_launch("sparse_fwd_umma_kernel");
+}
+
+int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st) {
+  CUtensorMap ma, mb;
+  int rc;
+  if ((rc = make_map(&ma, a, 128, "selftest (a)"))) return rc;
+  if ((rc = make_map(&mb, mode == 0 ? b : a, mode == 0 ? 64 : 128, "selftest (b)"))) return rc;
+  const int smem = kPairBytes + 16384 + 64 + 1024;
+  const cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "selftest: shared memory: %s", cudaGetErrorString(e));
+  umma_selftest_kernel<<<1, 128, smem, st>>>(ma, mb, (const bf16*)b, out, mode);
+  return check_launch("umma_selftest_kernel");
+}
+
+#ifdef VSA_TRACE
+extern "C" int vsa_debug_trace(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 16 * 128) == cudaSuccess ? 0 : -3;
+}
+#endif
+
+int device_status_fetch_and_clear(int* status) {
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(status, g_device_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+  if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "device status: %s", cudaGetErrorString(e));
+  return VSA_OK;
+}
+
+}  // namespace vsa

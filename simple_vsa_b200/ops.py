@@ -99,10 +99,11 @@ def sparse_forward(q, k, v, selected, kv_sizes, be: int, scale: float, want_lse:
     Lkv = k.shape[2]
     dt = _check_device_dtype(q, k, v)
     out = torch.empty_like(q)
-    lse = torch.empty((B, H, Lq), device=q.device, dtype=torch.float32) if want_lse else None
+    # the statistic buffer is always handed over: the tcgen05 forward needs it as scratch (4 bytes per row)
+    lse = torch.empty((B, H, Lq), device=q.device, dtype=torch.float32)
     call("vsa_sparse_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), selected.data_ptr(), kv_sizes.data_ptr(),
          out.data_ptr(), _ptr(lse), B * H, Lq, Lkv, D, be, selected.shape[-1], scale, dt, _stream(q.device))
-    return out, lse
+    return out, (lse if want_lse else None)
 
 
 def invert_routes(selected: Tensor, key_blocks: int):

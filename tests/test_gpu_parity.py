@@ -40,6 +40,56 @@ def _assert_close(got, want, **tol):
     np.testing.assert_allclose(to_np(got), want if isinstance(want, np.ndarray) else to_np(want), **tol)
 
 
+@pytest.fixture(autouse=True)
+def _no_device_timeouts():
+    """Every test must leave the device status word clear (no bounded wait ran out)."""
+    yield
+    from simple_vsa_b200 import _lib
+    assert _lib.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------
+# tcgen05 building blocks
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode", [0, 1])
+def test_umma_building_blocks(mode):
+    """TMA boxes + shared-memory operand descriptors + tensor-memory read-out give A*B."""
+    from simple_vsa_b200 import _lib
+    torch.manual_seed(60 + mode)
+    a = torch.randn(128, 128, device=DEV).to(torch.bfloat16)
+    if mode == 0:
+        b = torch.randn(64, 128, device=DEV).to(torch.bfloat16)
+        want = a.float() @ b.float().t()
+    else:
+        b = torch.randn(128, 64, device=DEV).to(torch.bfloat16)
+        want = a.float().t() @ b.float()
+    out = torch.full((128, 64), float("nan"), device=DEV)
+    _lib.call("vsa_selftest_umma", a.data_ptr(), b.data_ptr(), out.data_ptr(), mode,
+              torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    torch.testing.assert_close(out, want, atol=1e-3, rtol=1e-3)
+
+
+def test_forward_fixed_shift_out_of_range_is_recomputed_exactly():
+    """Later key blocks score ~200 (log2 units) above the first pair: the tcgen05 forward must hand those
+    tiles to the exact kernel, and the result must still match the oracle."""
+    V = _V()
+    torch.manual_seed(61)
+    be, nb, D = 64, 8, 128
+    q, k, v = (torch.randn(1, 1, be * nb, D).to(torch.bfloat16) for _ in range(3))
+    k[:, :, 5 * be:6 * be] *= 40.0          # block 5 dominates whenever it is selected
+    sizes = torch.full((nb,), be)
+    selected = torch.tensor([[0, 1, 5, 2], [3, 4, 6, 7], [1, 0, 2, 5], [5, 1, 2, 3]] * 2, dtype=torch.int32)[None, None]
+    want, want_lse = O.sparse_attention(q, k, v, selected, sizes, be, return_lse2=True)
+    from simple_vsa_b200 import ops
+    out, lse = ops.sparse_forward(q.to(DEV), k.to(DEV), v.to(DEV), selected.to(DEV), sizes.to(DEV, torch.int32),
+                                  be, 1.0 / math.sqrt(D), True)
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    _assert_close(out, want, atol=2e-2, rtol=2e-2)
+    _assert_close(lse, want_lse, atol=5e-2, rtol=1e-3)
+
+
 # ---------------------------------------------------------------------------------------------
 # bandwidth kernels
 # ---------------------------------------------------------------------------------------------
@@ -155,11 +205,10 @@ def test_topk_kernel_with_ties(dtype):
 # route-explicit fine attention against the reference's vectors
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("name", list(SPARSE_CASES))
-@pytest.mark.parametrize("kernels", ["auto", "scalar"])
+@pytest.mark.parametrize("kernels", ["auto", "mma", "scalar"])
 def test_route_explicit_against_reference_vectors(name, kernels, monkeypatch):
     V = _V()
-    if kernels == "scalar":
-        monkeypatch.setenv("VSA_B200_KERNELS", "scalar")
+    monkeypatch.setenv("VSA_B200_KERNELS", kernels)
     case = SPARSE_CASES[name]
     gold = _load("sparse_" + name)
     q, k, v, dout, sizes, selected = sparse_inputs(case)
@@ -266,7 +315,7 @@ def test_fine_attention_midsize_matches_oracle(be, nb, tk, ragged, monkeypatch):
     want = O.sparse_attention(*ol, selected, sizes, be, q_blocks_per_chunk=8)
     want.backward(dout.float())
     results = {}
-    for mode in ("auto", "scalar"):
+    for mode in ("auto", "mma", "scalar"):
         monkeypatch.setenv("VSA_B200_KERNELS", mode)
         leaves = [t.to(DEV).requires_grad_() for t in (q, k, v)]
         out = V.b200_sparse_attention(*leaves, selected.to(DEV), sizes, block_size=(1, 1, be))
