@@ -194,6 +194,9 @@ int vsa_sparse_bwd_dq(const void* dout, const void* q, const void* k, const void
   int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
   if (rc) return rc;
   VSA_REQUIRE(dout && q && k && v && out_s && lse2 && selected && kv_sizes && delta && dq, "sparse dQ: null pointer");
+  if (!scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk))
+    return sparse_dq_umma(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
+                          (cudaStream_t)stream);
   if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
     return sparse_dq_tc(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
                         (cudaStream_t)stream);
@@ -209,6 +212,9 @@ int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const vo
   if (rc) return rc;
   VSA_REQUIRE(dout && q && k && v && lse2 && delta && counts && offsets && inverse && kv_sizes && dk && dv,
               "sparse dK/dV: null pointer");
+  if (!scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk))
+    return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
+                            topk, scale, (cudaStream_t)stream);
   if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
     return sparse_dkdv_tc(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
                           topk, scale, (cudaStream_t)stream);

@@ -54,6 +54,13 @@ bool sparse_umma_eligible(int D, int be, int dtype, int topk);
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
                     cudaStream_t st);
+int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
+                   const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
+                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st);
+int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                     const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                     const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
+                     float scale, cudaStream_t st);
 int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st);
 int device_status_fetch_and_clear(int* status);
 

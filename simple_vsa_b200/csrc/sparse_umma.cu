@@ -509,6 +509,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
+#include "sparse_umma_bwd.inl"
+
 }  // namespace
 
 // ---- host entry points ---------------------------------------------------------------------------------------
@@ -542,6 +544,64 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
     sparse_fwd_umma_kernel<4><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale);
   }
   return check_launch("sparse_fwd_umma_kernel");
+}
+
+template <typename Kern>
+static int reserve_smem(Kern kern, int bytes, const char* what) {
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "%s: shared memory: %s", what, cudaGetErrorString(e));
+  return VSA_OK;
+}
+
+int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
+                   const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
+                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st) {
+  if (BH == 0 || Lq == 0) return VSA_OK;
+  if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dQ: batch*heads %lld exceeds 65535", (long long)BH);
+  CUtensorMap mq, mdo, mk, mv;
+  int rc;
+  if ((rc = make_map(&mq, q, BH * Lq, "sparse dQ (q)"))) return rc;
+  if ((rc = make_map(&mdo, dout, BH * Lq, "sparse dQ (dout)"))) return rc;
+  if ((rc = make_map(&mk, k, BH * Lkv, "sparse dQ (k)"))) return rc;
+  if ((rc = make_map(&mv, v, BH * Lkv, "sparse dQ (v)"))) return rc;
+  const int smem = DqSmem::total + 1024;
+  dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
+  if (be == 64) {
+    if ((rc = reserve_smem(sparse_dq_umma_kernel<1>, smem, "sparse dQ"))) return rc;
+    sparse_dq_umma_kernel<1><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const bf16*)dout, (const bf16*)out_s, lse2,
+                                                              selected, kv_sizes, delta, (bf16*)dq, Lq, Lkv, topk, scale);
+  } else {
+    if ((rc = reserve_smem(sparse_dq_umma_kernel<4>, smem, "sparse dQ"))) return rc;
+    sparse_dq_umma_kernel<4><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const bf16*)dout, (const bf16*)out_s, lse2,
+                                                              selected, kv_sizes, delta, (bf16*)dq, Lq, Lkv, topk, scale);
+  }
+  return check_launch("sparse_dq_umma_kernel");
+}
+
+int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                     const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                     const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
+                     float scale, cudaStream_t st) {
+  if (BH == 0 || Lkv == 0) return VSA_OK;
+  if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: batch*heads %lld exceeds 65535", (long long)BH);
+  CUtensorMap mq, mdo, mk, mv;
+  int rc;
+  if ((rc = make_map(&mq, q, BH * Lq, "sparse dK/dV (q)"))) return rc;
+  if ((rc = make_map(&mdo, dout, BH * Lq, "sparse dK/dV (dout)"))) return rc;
+  if ((rc = make_map(&mk, k, BH * Lkv, "sparse dK/dV (k)"))) return rc;
+  if ((rc = make_map(&mv, v, BH * Lkv, "sparse dK/dV (v)"))) return rc;
+  const int smem = DkSmem::total + 1024;
+  dim3 grid((unsigned)(Lkv / kTile), (unsigned)BH);
+  if (be == 64) {
+    if ((rc = reserve_smem(sparse_dkdv_umma_kernel<1>, smem, "sparse dK/dV"))) return rc;
+    sparse_dkdv_umma_kernel<1><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse,
+                                                                kv_sizes, (bf16*)dk, (bf16*)dv, Lq, Lkv, topk, scale);
+  } else {
+    if ((rc = reserve_smem(sparse_dkdv_umma_kernel<4>, smem, "sparse dK/dV"))) return rc;
+    sparse_dkdv_umma_kernel<4><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse,
+                                                                kv_sizes, (bf16*)dk, (bf16*)dv, Lq, Lkv, topk, scale);
+  }
+  return check_launch("sparse_dkdv_umma_kernel");
 }
 
 int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st) {

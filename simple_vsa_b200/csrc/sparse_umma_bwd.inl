@@ -1,0 +1,579 @@
+// Backward of the fine attention on the Blackwell tensor path.  Included by sparse_umma.cu (same
+// translation unit: the kernels share its device status word, tensor-map helper and constants).
+//
+// Both passes use the transposed, 128-row formulation of the forward so that every tcgen05.mma has
+// M = 128 although a block holds only 64 tokens, and so that P / dS are produced by the thread that
+// owns their row and are written once, as a swizzled 128-byte shared-memory row (N-major B operand):
+//
+//  query-owned dQ pass, per PAIR of selected key tiles (lanes = 128 key tokens, columns = 64 query rows)
+//      S^T  = K2 Q^T                 dP^T = V2 dO^T
+//      dS^T = 2^(S^T c - lse[q]) * (dP^T - delta[q]) * scale      (elementwise, statistics per COLUMN)
+//      dQ^T [128 dims x 64 rows] += K2^T dS^T
+//
+//  key-owned dK/dV pass, per PAIR of query tiles that selected this key tile (lanes = 128 query rows,
+//  columns = 64 key tokens)
+//      S  = Q2 K^T                   dP = dO2 V^T
+//      P  = 2^(S c - lse[row]),      dS = P * (dP - delta[row])   (elementwise, statistics per LANE)
+//      dV^T [128 dims x 64 keys] += dO2^T P          dK^T += Q2^T dS          (dK^T * scale at the end)
+//
+// Nothing here needs a running maximum (the forward saved the log-sum-exp), so there is no
+// cross-lane traffic at all.  Roles per CTA: warp 0 and 1 = TMA producers (four lanes, one box each),
+// warp 2 = issuer of the score MMAs, warp 3 = issuer of the gradient MMAs, warps 4-11 = elementwise.
+
+// 8 MMAs over the 128-wide reduction, both operands reduction-contiguous ("K-major").
+// a_pair: a stacked pair [2 halves][128 rows][128 B]; b_tile: one tile [2 halves][64 rows][128 B].
+__device__ __forceinline__ void issue_kmajor(uint32_t d_tmem, uint32_t a_pair, uint32_t b_tile) {
+  constexpr uint32_t idesc = instr_desc(128, 64, 0, 0);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    mma_ss(d_tmem, smem_desc(a_pair + (ks >> 2) * kPairHalf + (ks & 3) * 32, 16, 1024),
+           smem_desc(b_tile + (ks >> 2) * kSlab + (ks & 3) * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
+}
+// 8 MMAs over 128 rows of reduction, both operands output-contiguous ("MN-major"):
+// D[128 dims x 64] (+)= a_pair^T [128 dims x 128 rows] * b_rows [128 rows x 64].
+__device__ __forceinline__ void issue_mnmajor(uint32_t d_tmem, uint32_t a_pair, uint32_t b_rows, bool accumulate) {
+  constexpr uint32_t idesc = instr_desc(128, 64, 1, 1);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    mma_ss(d_tmem, smem_desc(a_pair + ks * 2048, kPairHalf, 1024), smem_desc(b_rows + ks * 2048, 16, 1024), idesc,
+           (accumulate || ks > 0) ? 1u : 0u);
+}
+
+constexpr int kBwdThreads = 384;
+
+// ------------------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------------------
+constexpr int kDqBufs = 3;     // (S^T, dP^T) accumulator pairs in flight: 3 x 128 columns, dQ^T behind them
+struct DqSmem {
+  static constexpr uint32_t q = 0;                                // 16 KB
+  static constexpr uint32_t d_o = q + 2 * kSlab;                  // 16 KB
+  static constexpr uint32_t k = d_o + 2 * kSlab;                  // 2 x 32 KB
+  static constexpr uint32_t v = k + 2 * kPairBytes;               // 2 x 32 KB
+  static constexpr uint32_t ds = v + 2 * kPairBytes;              // 2 x 16 KB
+  static constexpr uint32_t tile_row = ds + 2 * kPairHalf;        // int32 [kMaxTiles]
+  static constexpr uint32_t tile_valid = tile_row + 4 * kMaxTiles;
+  static constexpr uint32_t lse = tile_valid + kMaxTiles;         // float [64]
+  static constexpr uint32_t delta = lse + 256;                    // float [64]
+  static constexpr uint32_t bars = delta + 256;
+  static constexpr uint32_t misc = bars + 32 * 8;
+  static constexpr uint32_t total = misc + 64;
+};
+enum DqBar { DQ_QDO_FULL = 0, DQ_K_FULL = 1, DQ_V_FULL = 3, DQ_K_EMPTY = 5, DQ_V_EMPTY = 7, DQ_DS_FULL = 9,
+             DQ_DS_EMPTY = 11, DQ_ACC_FULL = 13, DQ_S_FULL = 14, DQ_S_EMPTY = 14 + kDqBufs };
+
+template <int SUB>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const bf16* __restrict__ dout, const bf16* __restrict__ out_s, const float* __restrict__ lse2,
+                      const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
+                      float* __restrict__ delta, bf16* __restrict__ dq, long long Lq, long long Lkv, int topk,
+                      float scale) {
+  extern __shared__ uint8_t smem_raw[];
+  if (*(volatile int*)&g_device_status != 0) return;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qtile = blockIdx.x;
+  const long long bh = blockIdx.y;
+  const int Qb = (int)(Lq / (kTile * SUB));
+  const int qb = qtile / SUB;
+  const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
+  const int n_iter = topk * SUB;
+  const float c = scale * kLog2e;
+  const long long qrow0 = bh * Lq + (long long)qtile * kTile;
+
+  int32_t* tile_row = reinterpret_cast<int32_t*>(sm + DqSmem::tile_row);
+  uint8_t* tile_valid = sm + DqSmem::tile_valid;
+  float* s_lse = reinterpret_cast<float*>(sm + DqSmem::lse);
+  float* s_delta = reinterpret_cast<float*>(sm + DqSmem::delta);
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(sm + DqSmem::misc);
+  auto bar = [&](int i) -> uint32_t { return base + DqSmem::bars + 8u * i; };
+
+  if (tid == 0) {
+    mbar_init(bar(DQ_QDO_FULL), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(DQ_K_FULL + i), 4);
+      mbar_init(bar(DQ_V_FULL + i), 4);
+      mbar_init(bar(DQ_K_EMPTY + i), 1);
+      mbar_init(bar(DQ_V_EMPTY + i), 1);
+      mbar_init(bar(DQ_DS_FULL + i), 8);
+      mbar_init(bar(DQ_DS_EMPTY + i), 1);
+    }
+    for (int i = 0; i < kDqBufs; ++i) {
+      mbar_init(bar(DQ_S_FULL + i), 1);
+      mbar_init(bar(DQ_S_EMPTY + i), 8);
+    }
+    mbar_init(bar(DQ_ACC_FULL), 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  for (int it = tid; it < n_iter; it += kBwdThreads) {
+    const int kvb = sel[it / SUB];
+    const int left = kv_sizes[kvb] - (it % SUB) * kTile;
+    tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
+    tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
+  }
+  if (warp >= 4) {   // delta = rowsum(out_s * dout) and the saved statistic, four threads per query row
+    const int st = tid - 128;
+    const int row = st >> 2, part = st & 3;
+    const uint4* po = reinterpret_cast<const uint4*>(out_s + (qrow0 + row) * kD + part * 32);
+    const uint4* pd = reinterpret_cast<const uint4*>(dout + (qrow0 + row) * kD + part * 32);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 a = po[i], b = pd[i];
+      const __nv_bfloat162* ea = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* eb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = __bfloat1622float2(ea[j]), fb = __bfloat1622float2(eb[j]);
+        acc = fmaf(fa.x, fb.x, acc);
+        acc = fmaf(fa.y, fb.y, acc);
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (part == 0) {
+      s_delta[row] = acc;
+      delta[qrow0 + row] = acc;
+      s_lse[row] = lse2[qrow0 + row];
+    }
+  }
+  __syncthreads();
+  if (warp == 2) {
+    int n_live = 0;
+    for (int it0 = 0; it0 < n_iter; it0 += 32) {
+      const int it = it0 + lane;
+      const int valid = it < n_iter ? (int)tile_valid[it] : 0;
+      const int row = it < n_iter ? tile_row[it] : 0;
+      const unsigned live = __ballot_sync(0xffffffffu, valid > 0);
+      __syncwarp();
+      if (valid > 0) {
+        const int pos = n_live + __popc(live & ((1u << lane) - 1u));
+        tile_row[pos] = row;
+        tile_valid[pos] = (uint8_t)valid;
+      }
+      n_live += __popc(live);
+      __syncwarp();
+    }
+    if (lane == 0) misc[1] = (uint32_t)n_live;
+  }
+  if (warp == 1) {
+    tmem_alloc(base + DqSmem::misc, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = misc[0];
+  const int n_live = (int)misc[1];
+  const int n_pairs = (n_live + 1) >> 1;
+  const uint32_t tmem_acc = tmem + 128 * kDqBufs;
+  const long long kv_row_base = bh * Lkv;
+  bool ok = true;
+
+  if (warp == 0 || warp == 1) {
+    const bool is_k = warp == 0;
+    if (is_k && lane == 0) {
+      mbar_arrive_expect_tx(bar(DQ_QDO_FULL), 4 * kSlab);
+      tma_load_2d(base + DqSmem::q, &map_q, 0, (int)qrow0, bar(DQ_QDO_FULL));
+      tma_load_2d(base + DqSmem::q + kSlab, &map_q, 64, (int)qrow0, bar(DQ_QDO_FULL));
+      tma_load_2d(base + DqSmem::d_o, &map_do, 0, (int)qrow0, bar(DQ_QDO_FULL));
+      tma_load_2d(base + DqSmem::d_o + kSlab, &map_do, 64, (int)qrow0, bar(DQ_QDO_FULL));
+    }
+    const int which = lane & 1, dhalf = (lane >> 1) & 1;
+    const CUtensorMap* map = is_k ? &map_k : &map_v;
+    const int full0 = is_k ? DQ_K_FULL : DQ_V_FULL, empty0 = is_k ? DQ_K_EMPTY : DQ_V_EMPTY;
+    const uint32_t ring = base + (is_k ? DqSmem::k : DqSmem::v);
+    for (int p = 0; p < n_pairs; ++p) {
+      const int s = p & 1;
+      const uint32_t ph = (p >> 1) & 1;
+      int idx = 2 * p + which;
+      if (idx >= n_live) idx = 2 * p;
+      const int row = (int)(kv_row_base + tile_row[idx]);
+      ok = VSA_WARP_WAIT(bar(empty0 + s), ph ^ 1);
+      if (!ok) break;
+      if (lane < 4) {
+        mbar_arrive_expect_tx(bar(full0 + s), kSlab);
+        tma_load_2d(ring + s * kPairBytes + dhalf * kPairHalf + which * kSlab, map, dhalf * 64, row, bar(full0 + s));
+      }
+    }
+    if (!ok && lane == 0) report_timeout(11);
+  } else if (warp == 2) {
+    if (lane == 0) {   // scores: S^T = K2 Q^T and dP^T = V2 dO^T
+      ok = VSA_WAIT(bar(DQ_QDO_FULL), 0);
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p & 1, b = p % kDqBufs;
+        const uint32_t ph = (p >> 1) & 1;
+        ok = VSA_WAIT(bar(DQ_K_FULL + s), ph) && VSA_WAIT(bar(DQ_V_FULL + s), ph) &&
+             VSA_WAIT(bar(DQ_S_EMPTY + b), ((p / kDqBufs) & 1) ^ 1);
+        if (!ok) break;
+        tc_fence_after();
+        issue_kmajor(tmem + b * 128, base + DqSmem::k + s * kPairBytes, base + DqSmem::q);
+        issue_kmajor(tmem + b * 128 + 64, base + DqSmem::v + s * kPairBytes, base + DqSmem::d_o);
+        mma_commit(bar(DQ_V_EMPTY + s));
+        mma_commit(bar(DQ_S_FULL + b));
+      }
+      if (!ok) report_timeout(12);
+    }
+  } else if (warp == 3) {
+    if (lane == 0) {   // dQ^T += K2^T dS^T
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p & 1;
+        const uint32_t ph = (p >> 1) & 1;
+        ok = VSA_WAIT(bar(DQ_K_FULL + s), ph) && VSA_WAIT(bar(DQ_DS_FULL + s), ph);
+        if (!ok) break;
+        tc_fence_after();
+        issue_mnmajor(tmem_acc, base + DqSmem::k + s * kPairBytes, base + DqSmem::ds + s * kPairHalf, p > 0);
+        mma_commit(bar(DQ_K_EMPTY + s));
+        mma_commit(bar(DQ_DS_EMPTY + s));
+      }
+      if (ok) mma_commit(bar(DQ_ACC_FULL));
+      if (!ok) report_timeout(13);
+    }
+  } else {
+    // elementwise warps: lane t = key token of the pair, 32 of the 64 query rows (columns c0..c0+31)
+    const int quarter = warp & 3;
+    const int chalf = (warp - 4) >> 2;
+    const int c0 = chalf * 32;
+    const int t = quarter * 32 + lane;
+    const int half = t >> 6, r = t & 63;
+    const int st = tid - 128;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    for (int p = 0; p < n_pairs && ok; ++p) {
+      const int s = p & 1, b = p % kDqBufs;
+      const uint32_t ph = (p >> 1) & 1;
+      const int idx = 2 * p + half;
+      const int valid = idx < n_live ? (int)tile_valid[idx] : 0;
+      const bool live = r < valid;
+      ok = VSA_WARP_WAIT(bar(DQ_S_FULL + b), (p / kDqBufs) & 1);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[32], dv[32];
+      tmem_ld32(tmem + b * 128 + lane_addr + c0, sv);
+      tmem_ld32(tmem + b * 128 + 64 + lane_addr + c0, dv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DQ_S_EMPTY + b));
+      // rows of K beyond a ragged tile's size (and the repeated tile of an odd tail) must be finite zeros:
+      // they meet dS = 0 in the dQ product, where 0 * NaN would poison the sum.  S(p) has completed.
+      if (!live && chalf == 0) {
+        uint8_t* krow = sm + DqSmem::k + s * kPairBytes + t * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          *reinterpret_cast<uint4*>(krow + ch * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(krow + kPairHalf + ch * 16) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      uint32_t packed[16];
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c0 + 4 * j4);
+        const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c0 + 4 * j4);
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -l4.x));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -l4.y));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -l4.z));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -l4.w));
+        const float g0 = live ? p0 * (__uint_as_float(dv[4 * j4 + 0]) - d4.x) * scale : 0.f;
+        const float g1 = live ? p1 * (__uint_as_float(dv[4 * j4 + 1]) - d4.y) * scale : 0.f;
+        const float g2 = live ? p2 * (__uint_as_float(dv[4 * j4 + 2]) - d4.z) * scale : 0.f;
+        const float g3 = live ? p3 * (__uint_as_float(dv[4 * j4 + 3]) - d4.w) * scale : 0.f;
+        packed[2 * j4] = pack_bf16(g0, g1);
+        packed[2 * j4 + 1] = pack_bf16(g2, g3);
+      }
+      ok = VSA_WARP_WAIT(bar(DQ_DS_EMPTY + s), ph ^ 1);
+      if (!ok) break;
+      uint8_t* drow = sm + DqSmem::ds + s * kPairHalf + t * 128;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)
+        *reinterpret_cast<uint4*>(drow + (((4 * chalf + ch) ^ (t & 7)) << 4)) =
+            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DQ_DS_FULL + s));
+    }
+    if (!ok && lane == 0) report_timeout(14);
+    if (ok && n_pairs > 0) ok = VSA_WARP_WAIT(bar(DQ_ACC_FULL), 0);
+    if (!ok && lane == 0) report_timeout(15);
+    tc_fence_after();
+    bf16* stage = reinterpret_cast<bf16*>(sm + DqSmem::k);      // [64 query rows][128 dims]; every MMA is done
+    if (ok && n_pairs > 0) {
+      uint32_t av[32];
+      tmem_ld32(tmem_acc + lane_addr + c0, av);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
+    } else {
+      for (int j = 0; j < 32; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
+    }
+    named_barrier(1, 256);
+    bf16* og = dq + qrow0 * kD;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int cidx = st + 256 * i;
+      const int row = cidx >> 4, ch = cidx & 15;
+      *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// dK / dV
+// ------------------------------------------------------------------------------------------------------
+constexpr int kDkBufs = 2;     // (S, dP) accumulator pairs in flight: 2 x 128 columns, then dK^T and dV^T
+struct DkSmem {
+  static constexpr uint32_t k = 0;                                // 16 KB
+  static constexpr uint32_t v = k + 2 * kSlab;                    // 16 KB
+  static constexpr uint32_t q = v + 2 * kSlab;                    // 2 x 32 KB  (pairs of query tiles)
+  static constexpr uint32_t d_o = q + 2 * kPairBytes;             // 2 x 32 KB
+  static constexpr uint32_t p = d_o + 2 * kPairBytes;             // 2 x 16 KB
+  static constexpr uint32_t ds = p + 2 * kPairHalf;               // 2 x 16 KB
+  static constexpr uint32_t bars = ds + 2 * kPairHalf;
+  static constexpr uint32_t misc = bars + 32 * 8;
+  static constexpr uint32_t total = misc + 64;
+};
+enum DkBar { DK_KV_FULL = 0, DK_Q_FULL = 1, DK_DO_FULL = 3, DK_Q_EMPTY = 5, DK_DO_EMPTY = 7, DK_PDS_FULL = 9,
+             DK_PDS_EMPTY = 11, DK_ACC_FULL = 13, DK_S_FULL = 14, DK_S_EMPTY = 14 + kDkBufs };
+
+template <int SUB>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                        const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const float* __restrict__ lse2, const float* __restrict__ delta,
+                        const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
+                        const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
+                        bf16* __restrict__ dk, bf16* __restrict__ dv, long long Lq, long long Lkv, int topk,
+                        float scale) {
+  extern __shared__ uint8_t smem_raw[];
+  if (*(volatile int*)&g_device_status != 0) return;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ktile = blockIdx.x;
+  const long long bh = blockIdx.y;
+  const int Kb = (int)(Lkv / (kTile * SUB)), Qb = (int)(Lq / (kTile * SUB));
+  const int kvb = ktile / SUB, sub = ktile % SUB;
+  int valid = kv_sizes[kvb] - sub * kTile;
+  valid = valid < 0 ? 0 : (valid > kTile ? kTile : valid);
+  const long long krow0 = bh * Lkv + (long long)ktile * kTile;
+  const int cnt = counts[bh * Kb + kvb];
+  const int32_t* inv = inverse + bh * (long long)Qb * topk + offsets[bh * Kb + kvb];
+  const int n_tiles = valid > 0 ? cnt * SUB : 0;
+  const int n_pairs = (n_tiles + 1) >> 1;
+  const float c = scale * kLog2e;
+  const long long q_row_base = bh * Lq;
+
+  if (n_pairs == 0) {   // nobody selected this tile, or it is all padding: zero gradients, no pipeline
+    uint4* gk = reinterpret_cast<uint4*>(dk + krow0 * kD);
+    uint4* gv = reinterpret_cast<uint4*>(dv + krow0 * kD);
+    for (int i = tid; i < 1024; i += kBwdThreads) {
+      gk[i] = make_uint4(0, 0, 0, 0);
+      gv[i] = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(sm + DkSmem::misc);
+  auto bar = [&](int i) -> uint32_t { return base + DkSmem::bars + 8u * i; };
+  // row (inside this batch-head slice) of the i-th query tile that selected this key block
+  auto tile_row = [&](int i) -> int { return inv[i / SUB] * (kTile * SUB) + (i % SUB) * kTile; };
+
+  if (tid == 0) {
+    mbar_init(bar(DK_KV_FULL), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(DK_Q_FULL + i), 4);
+      mbar_init(bar(DK_DO_FULL + i), 4);
+      mbar_init(bar(DK_Q_EMPTY + i), 1);
+      mbar_init(bar(DK_DO_EMPTY + i), 1);
+      mbar_init(bar(DK_PDS_FULL + i), 8);
+      mbar_init(bar(DK_PDS_EMPTY + i), 1);
+    }
+    for (int i = 0; i < kDkBufs; ++i) {
+      mbar_init(bar(DK_S_FULL + i), 1);
+      mbar_init(bar(DK_S_EMPTY + i), 8);
+    }
+    mbar_init(bar(DK_ACC_FULL), 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(base + DkSmem::misc, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = misc[0];
+  const uint32_t tmem_dk = tmem + 128 * kDkBufs, tmem_dv = tmem_dk + 64;
+  bool ok = true;
+
+  if (warp == 0 || warp == 1) {
+    const bool is_q = warp == 0;
+    if (is_q && lane == 0) {
+      mbar_arrive_expect_tx(bar(DK_KV_FULL), 4 * kSlab);
+      tma_load_2d(base + DkSmem::k, &map_k, 0, (int)krow0, bar(DK_KV_FULL));
+      tma_load_2d(base + DkSmem::k + kSlab, &map_k, 64, (int)krow0, bar(DK_KV_FULL));
+      tma_load_2d(base + DkSmem::v, &map_v, 0, (int)krow0, bar(DK_KV_FULL));
+      tma_load_2d(base + DkSmem::v + kSlab, &map_v, 64, (int)krow0, bar(DK_KV_FULL));
+    }
+    const int which = lane & 1, dhalf = (lane >> 1) & 1;
+    const CUtensorMap* map = is_q ? &map_q : &map_do;
+    const int full0 = is_q ? DK_Q_FULL : DK_DO_FULL, empty0 = is_q ? DK_Q_EMPTY : DK_DO_EMPTY;
+    const uint32_t ring = base + (is_q ? DkSmem::q : DkSmem::d_o);
+    for (int p = 0; p < n_pairs; ++p) {
+      const int s = p & 1;
+      const uint32_t ph = (p >> 1) & 1;
+      int idx = 2 * p + which;
+      if (idx >= n_tiles) idx = 2 * p;                  // odd tail: repeat the tile (its rows are masked)
+      const int row = (int)(q_row_base + tile_row(idx));
+      ok = VSA_WARP_WAIT(bar(empty0 + s), ph ^ 1);
+      if (!ok) break;
+      if (lane < 4) {
+        mbar_arrive_expect_tx(bar(full0 + s), kSlab);
+        tma_load_2d(ring + s * kPairBytes + dhalf * kPairHalf + which * kSlab, map, dhalf * 64, row, bar(full0 + s));
+      }
+    }
+    if (!ok && lane == 0) report_timeout(21);
+  } else if (warp == 2) {
+    if (lane == 0) {   // scores: S = Q2 K^T and dP = dO2 V^T
+      ok = VSA_WAIT(bar(DK_KV_FULL), 0);
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p & 1, b = p % kDkBufs;
+        const uint32_t ph = (p >> 1) & 1;
+        ok = VSA_WAIT(bar(DK_Q_FULL + s), ph) && VSA_WAIT(bar(DK_DO_FULL + s), ph) &&
+             VSA_WAIT(bar(DK_S_EMPTY + b), ((p / kDkBufs) & 1) ^ 1);
+        if (!ok) break;
+        tc_fence_after();
+        issue_kmajor(tmem + b * 128, base + DkSmem::q + s * kPairBytes, base + DkSmem::k);
+        issue_kmajor(tmem + b * 128 + 64, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::v);
+        mma_commit(bar(DK_S_FULL + b));
+      }
+      if (!ok) report_timeout(22);
+    }
+  } else if (warp == 3) {
+    if (lane == 0) {   // dV^T += dO2^T P and dK^T += Q2^T dS
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p & 1;
+        const uint32_t ph = (p >> 1) & 1;
+        ok = VSA_WAIT(bar(DK_Q_FULL + s), ph) && VSA_WAIT(bar(DK_DO_FULL + s), ph) && VSA_WAIT(bar(DK_PDS_FULL + s), ph);
+        if (!ok) break;
+        tc_fence_after();
+        issue_mnmajor(tmem_dv, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::p + s * kPairHalf, p > 0);
+        mma_commit(bar(DK_DO_EMPTY + s));
+        issue_mnmajor(tmem_dk, base + DkSmem::q + s * kPairBytes, base + DkSmem::ds + s * kPairHalf, p > 0);
+        mma_commit(bar(DK_Q_EMPTY + s));
+        mma_commit(bar(DK_PDS_EMPTY + s));
+      }
+      if (ok) mma_commit(bar(DK_ACC_FULL));
+      if (!ok) report_timeout(23);
+    }
+  } else {
+    // elementwise warps: lane t = query row of the pair, 32 of the 64 key tokens (columns c0..c0+31)
+    const int quarter = warp & 3;
+    const int chalf = (warp - 4) >> 2;
+    const int c0 = chalf * 32;
+    const int t = quarter * 32 + lane;
+    const int half = t >> 6, r = t & 63;
+    const int st = tid - 128;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    // statistics of this lane's query row, fetched one pair ahead of their use
+    float lse_n = 0.f, dl_n = 0.f;
+    bool live_n = half < n_tiles;
+    if (live_n) {
+      const long long row = q_row_base + tile_row(half) + r;
+      lse_n = lse2[row];
+      dl_n = delta[row];
+    }
+    for (int p = 0; p < n_pairs && ok; ++p) {
+      const int s = p & 1, b = p % kDkBufs;
+      const uint32_t ph = (p >> 1) & 1;
+      const float lse = lse_n, dl = dl_n;
+      const bool live = live_n;
+      {
+        const int nidx = 2 * (p + 1) + half;
+        live_n = nidx < n_tiles;
+        if (live_n) {
+          const long long row = q_row_base + tile_row(nidx) + r;
+          lse_n = lse2[row];
+          dl_n = delta[row];
+        }
+      }
+      ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[32], dvv[32];
+      tmem_ld32(tmem + b * 128 + lane_addr + c0, sv);
+      tmem_ld32(tmem + b * 128 + 64 + lane_addr + c0, dvv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DK_S_EMPTY + b));
+      uint32_t pp[16], pg[16];
+#pragma unroll
+      for (int j2 = 0; j2 < 16; ++j2) {
+        const bool k0 = live && (c0 + 2 * j2) < valid, k1 = live && (c0 + 2 * j2 + 1) < valid;
+        const float p0 = k0 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse)) : 0.f;
+        const float p1 = k1 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse)) : 0.f;
+        const float g0 = k0 ? p0 * (__uint_as_float(dvv[2 * j2]) - dl) : 0.f;
+        const float g1 = k1 ? p1 * (__uint_as_float(dvv[2 * j2 + 1]) - dl) : 0.f;
+        pp[j2] = pack_bf16(p0, p1);
+        pg[j2] = pack_bf16(g0, g1);
+      }
+      ok = VSA_WARP_WAIT(bar(DK_PDS_EMPTY + s), ph ^ 1);
+      if (!ok) break;
+      uint8_t* prow = sm + DkSmem::p + s * kPairHalf + t * 128;
+      uint8_t* grow = sm + DkSmem::ds + s * kPairHalf + t * 128;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        const uint32_t off = (uint32_t)(((4 * chalf + ch) ^ (t & 7)) << 4);
+        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+        *reinterpret_cast<uint4*>(grow + off) = make_uint4(pg[4 * ch], pg[4 * ch + 1], pg[4 * ch + 2], pg[4 * ch + 3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DK_PDS_FULL + s));
+    }
+    if (!ok && lane == 0) report_timeout(24);
+    if (ok) ok = VSA_WARP_WAIT(bar(DK_ACC_FULL), 0);
+    if (!ok && lane == 0) report_timeout(25);
+    tc_fence_after();
+    bf16* stage_k = reinterpret_cast<bf16*>(sm + DkSmem::q);          // [64 key rows][128 dims] each; all MMAs done
+    bf16* stage_v = stage_k + kTile * kD;
+    if (ok) {
+      uint32_t ak[32], av[32];
+      tmem_ld32(tmem_dk + lane_addr + c0, ak);
+      tmem_ld32(tmem_dv + lane_addr + c0, av);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(ak[j]) * scale);
+        stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
+      }
+    } else {
+      for (int j = 0; j < 32; ++j) {
+        stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
+        stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
+      }
+    }
+    named_barrier(1, 256);
+    bf16* gk = dk + krow0 * kD;
+    bf16* gv = dv + krow0 * kD;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int cidx = st + 256 * i;
+      const int row = cidx >> 4, ch = cidx & 15;
+      *reinterpret_cast<uint4*>(gk + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_k + row * kD + ch * 8);
+      *reinterpret_cast<uint4*>(gv + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_v + row * kD + ch * 8);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
