@@ -341,7 +341,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         with open(tpath) as fh:
             tj = json.load(fh)
         if top in tj:
-            traffic = tj[top]["dram_bytes_per_edge"] * edges
+            traffic = tj[top]["dram_bytes_per_tensor_byte"] * count * L * D * 2
     step_total = sum(kv["total_ms"] for kv in kernels.values())
     shares = {n: round(kv["total_ms"] / step_total, 4) for n, kv in sorted(kernels.items())}
 
