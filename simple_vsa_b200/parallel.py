@@ -1,0 +1,91 @@
+"""Multi-GPU layer of the VSA operator (one process per GPU, ``torch.distributed``).
+
+Two modes, neither of which exists in the reference project (its kernels index every
+``(batch, head)`` slice independently, ``vsa/triton_impl.py:83-86``, and it has no collective):
+
+* **head sharding** -- the ``batch*heads`` slices are cut into contiguous ranges, one per rank, and
+  each rank runs the ordinary operator on its range.  No data-path collective.
+* **sequence parallelism** (long sequences) -- each rank owns ``L/W`` query tokens and the matching
+  K/V shard.  K and V are all-gathered into local HBM (NCCL over NVLink), the rank then runs the
+  ordinary operator with its local queries against the full keys (``Lq != Lkv``: pooled scores
+  ``[Qb/W, Kb]``, Top-K and the fine kernels all work on global key-block ids), and the backward
+  reduce-scatters the partial dK/dV to their owners.  Remote data is always copied into the GPU's
+  own memory first; no kernel reads a peer's memory.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+
+def shard_slices(total: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous range ``(first, count)`` of ``total`` slices owned by ``rank`` (remainder to the low ranks)."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world of {world}")
+    per, extra = divmod(total, world)
+    return rank * per + min(rank, extra), per + (1 if rank < extra else 0)
+
+
+def shard_heads(x: Tensor, world: int, rank: int) -> Tensor:
+    """``[B,H,L,D] -> [1, count, L, D]``: this rank's contiguous share of the ``B*H`` slices."""
+    B, H, L, D = x.shape
+    first, count = shard_slices(B * H, world, rank)
+    return x.reshape(1, B * H, L, D)[:, first:first + count]
+
+
+class _GatherSequence(torch.autograd.Function):
+    """all-gather along the sequence axis; the backward reduce-scatters the gradient."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:
+        world = dist.get_world_size(group)
+        ctx.group, ctx.world = group, world
+        x = x.contiguous()
+        B, H, l, D = x.shape
+        gathered = torch.empty((world * B, H, l, D), device=x.device, dtype=x.dtype)   # rank-major concatenation
+        dist.all_gather_into_tensor(gathered, x, group=group)
+        return gathered.view(world, B, H, l, D).permute(1, 2, 0, 3, 4).reshape(B, H, world * l, D)
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        world, group = ctx.world, ctx.group
+        B, H, L, D = grad.shape
+        l = L // world
+        parts = grad.reshape(B, H, world, l, D).permute(2, 0, 1, 3, 4).contiguous()
+        if dist.get_backend(group) == "nccl":
+            out = torch.empty((B, H, l, D), device=grad.device, dtype=grad.dtype)
+            dist.reduce_scatter_tensor(out, parts.view(world * B, H, l, D), op=dist.ReduceOp.SUM, group=group)
+        else:   # backends without reduce-scatter (gloo on CPU): all-reduce, keep the own part
+            dist.all_reduce(parts, op=dist.ReduceOp.SUM, group=group)
+            out = parts[dist.get_rank(group)].contiguous()
+        return out, None
+
+
+def gather_sequence(x: Tensor, group=None) -> Tensor:
+    """Differentiable all-gather of ``[B,H,L/W,D]`` shards into ``[B,H,L,D]`` (rank order = sequence order)."""
+    return _GatherSequence.apply(x, group)
+
+
+def sequence_parallel_vsa(q_local: Tensor, k_local: Tensor, v_local: Tensor, variable_block_sizes: Tensor,
+                          q_variable_block_sizes_local: Tensor, topk: int, block_size=64,
+                          compress_attn_weight_local: Optional[Tensor] = None, *, group=None,
+                          local_op: Optional[Callable] = None) -> Tensor:
+    """VSA with the sequence split over the ranks of ``group``.
+
+    ``q_local/k_local/v_local`` are this rank's ``[B,H,L/W,D]`` shards (rank r holds tokens
+    ``[r*L/W, (r+1)*L/W)``; ``L/W`` must be a multiple of the block volume),
+    ``variable_block_sizes`` lists ALL key blocks, ``q_variable_block_sizes_local`` this rank's query
+    blocks.  Returns the local ``[B,H,L/W,D]`` output; gradients reach the local q/k/v (dK/dV are
+    summed over ranks by the reduce-scatter) and the local gate.  ``local_op`` defaults to the CUDA
+    operator and exists so that the glue can be exercised on CPU ranks with a stand-in.
+    """
+    if local_op is None:
+        from . import b200_vsa as local_op
+    k_full = gather_sequence(k_local, group)
+    v_full = gather_sequence(v_local, group)
+    return local_op(q_local, k_full, v_full, variable_block_sizes, q_variable_block_sizes_local, topk, block_size,
+                    compress_attn_weight_local)
