@@ -133,6 +133,18 @@ int vsa_route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets,
                      int32_t* inverse, int32_t* cursor_ws,
                      int64_t BH, int Qb, int Kb, int topk, void* stream);
 
+/* Same result as vsa_route_invert, for callers that cannot provide the cursor scratch: a host whose
+ * own pool owns all device memory (cudaMalloc fails there) or a loop where allocation is banned
+ * because it synchronises the device.  The cursor lives in a 1 MiB array built into the library
+ * (held by every GPU that loads it, until exit); BH*Kb must not exceed 262,144 or the call is
+ * refused with VSA_ERR_UNSUPPORTED.  The call allocates nothing.  Its first use on a device looks up
+ * the array's device address (cudaGetSymbolAddress), so make that first call before any stream
+ * capture.  All calls share the one array: calls that overlap on the same GPU race and must be
+ * serialised by the caller; no state carries over between calls (every entry used is rewritten).
+ * No counterpart in the reference (it always allocates with torch). */
+int vsa_route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offsets,
+                            int32_t* inverse, int64_t BH, int Qb, int Kb, int topk, void* stream);
+
 /* Query-owned backward: delta = rowsum(out_s * dout) (written to delta, which
  * vsa_sparse_bwd_dkdv reads) and dq = scale * sum_edges dS K.
  * Replaces _delta_kernel/_delta_256_kernel + _vsa_dq_kernel/_vsa_dq_256_kernel:

@@ -29,6 +29,7 @@ SIGNATURES = {
     "vsa_coarse_bwd": [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, F, I, P],
     "vsa_sparse_fwd": [P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_route_invert": [P, P, P, P, P, L, I, I, I, P],
+    "vsa_route_invert_static": [P, P, P, P, L, I, I, I, P],
     "vsa_sparse_bwd_dq": [P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dkdv": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_combine_fwd": [P, P, P, P, L, L, I, I, I, P],

@@ -187,6 +187,13 @@ int vsa_route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets,
   return route_invert(selected, counts, offsets, inverse, cursor_ws, BH, Qb, Kb, topk, (cudaStream_t)stream);
 }
 
+int vsa_route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int64_t BH,
+                            int Qb, int Kb, int topk, void* stream) {
+  VSA_REQUIRE(selected && counts && offsets && inverse, "static route inversion: null pointer");
+  VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && topk >= 1, "static route inversion: bad extents");
+  return route_invert_static(selected, counts, offsets, inverse, BH, Qb, Kb, topk, (cudaStream_t)stream);
+}
+
 int vsa_sparse_bwd_dq(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                       const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
                       int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale, int dtype,

@@ -6,6 +6,8 @@
 // cover (fp32 validation mode, block volumes other than 64/256, head dims
 // other than 128).  Arithmetic follows the reference project's conventions:
 // fp32 accumulation, base-2 log-sum-exp, masks from the per-block sizes.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -540,6 +542,60 @@ int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int
     rc = check_launch("route_scatter_kernel");
   }
   return rc;
+}
+
+// -----------------------------------------------------------------------------------------
+// Route inversion for callers that cannot hand over scratch memory.
+//
+// Some hosts of this library may not allocate device memory at the point where they need the
+// inverse routing: a serving process that gave the whole GPU to its own memory pool at start-up
+// (a later cudaMalloc simply fails), or a latency-critical loop in which cudaMalloc is banned
+// because it synchronises the device.  For them the per-key-block cursor that the scatter step
+// needs lives in the fixed array below instead of a caller-provided buffer.  The array belongs to
+// the library image: every GPU that loads the library holds these 1 MiB until the process exits.
+//
+// In host code the name `g_static_cursor` is only a handle for the symbol, not a device address;
+// the device address is looked up once per device with cudaGetSymbolAddress (with that device
+// current) and that pointer is what the kernels receive.
+// -----------------------------------------------------------------------------------------
+constexpr long long kStaticCursorEntries = 1LL << 18;          // batch*heads*key_blocks <= 262,144
+static __device__ __align__(256) int32_t g_static_cursor[kStaticCursorEntries];
+
+static int32_t* static_cursor_for_current_device(int* rc_out) {
+  constexpr int kMaxDevices = 64;
+  static int32_t* ptrs[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *rc_out = fail(VSA_ERR_LAUNCH, "static route inversion: cannot identify the current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_cursor);
+    if (e != cudaSuccess || !p) {
+      *rc_out = fail(VSA_ERR_LAUNCH, "static route inversion: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<int32_t*>(p);
+  }
+  *rc_out = VSA_OK;
+  return ptrs[dev];
+}
+
+int route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int64_t BH,
+                        int Qb, int Kb, int topk, cudaStream_t st) {
+  if (BH * (long long)Kb > kStaticCursorEntries)
+    return fail(VSA_ERR_UNSUPPORTED,
+                "static route inversion: batch*heads*key_blocks = %lld exceeds the built-in scratch of %lld entries; "
+                "use vsa_route_invert with a caller-provided cursor buffer",
+                (long long)(BH * (long long)Kb), kStaticCursorEntries);
+  int rc = VSA_OK;
+  int32_t* cursor = static_cursor_for_current_device(&rc);
+  if (!cursor) return rc;
+  // the scan step rewrites every cursor entry it will use, so nothing left by an earlier call survives
+  return route_invert(selected, counts, offsets, inverse, cursor, BH, Qb, Kb, topk, st);
 }
 
 // =========================================================================================
