@@ -289,17 +289,13 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     torch.cuda.empty_cache()
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
 
+    from simple_vsa_b200.host import vsa_step_from_host
+
     def e2e_step():
-        dv_ = {n: host_in[n].to(dev, non_blocking=True) for n in names}
-        ql, kl, vl = (dv_[n].requires_grad_() for n in ("q", "k", "v"))
-        g_ = dv_["gate"].requires_grad_() if "gate" in dv_ else None
-        out = fwd_bwd(ql, kl, vl, g_, dv_["dout"])
-        host_out["out"].copy_(out.detach(), non_blocking=True)
-        host_out["dq"].copy_(ql.grad, non_blocking=True)
-        host_out["dk"].copy_(kl.grad, non_blocking=True)
-        host_out["dv"].copy_(vl.grad, non_blocking=True)
-        if g_ is not None:
-            host_out["dgate"].copy_(g_.grad, non_blocking=True)
+        # the public host-resident step: chunks of slices, copies overlapped with the kernels
+        vsa_step_from_host(host_in["q"], host_in["k"], host_in["v"], host_in["dout"], sizes, sizes, tk,
+                           cfg["block_size"], host_in.get("gate"), out=host_out, device=dev,
+                           slices_per_chunk=args.e2e_chunk)
 
     e2e_step()
     barrier()
@@ -395,6 +391,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--e2e-chunk", type=int, default=4, help="(batch,head) slices per pipelined chunk of the host-resident step")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]

@@ -21,7 +21,7 @@
 // operand), so no transposition is ever needed.
 //
 // Roles: warp 0 = K producer, warp 1 = V producer (four lanes, one TMA box each; warp 1 also owns the
-// tensor memory), warp 2 = issuer of the S^T MMAs, warp 3 = issuer of the O^T MMAs, warps 4-11 = softmax (a TMEM lane quarter and half of the
+// tensor memory), warp 2 = issuer of the S^T MMAs, warp 3 = issuer of the O^T MMAs, warps 4-19 = softmax (a TMEM lane quarter and half of the
 // query-row columns each).  Every mbarrier wait is bounded; on a time-out the CTA records an error code in a
 // device status word, stops issuing work, frees its tensor memory and returns.
 #include <cuda.h>
@@ -202,7 +202,10 @@ struct FwdSmem {
   static constexpr uint32_t misc = bars + 32 * 8;                // tmem base, n_live, flags
   static constexpr uint32_t total = misc + 64;
 };
-constexpr int kFwdThreads = 384;   // K producer, V producer, MMA issuer, TMEM owner, eight softmax warps
+constexpr int kEwCols = 16;          // columns of a TMEM tile one elementwise thread owns
+constexpr int kEwWarps = 4 * (64 / kEwCols);   // lane quarters x column groups = 16 warps
+constexpr int kEwThreads = 32 * kEwWarps;
+constexpr int kFwdThreads = 128 + kEwThreads;   // K producer, V producer, two MMA issuers, elementwise warps
 enum FwdBar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, P_FULL = 9, P_EMPTY = 11, O_FULL = 13,
               S_FULL = 14, S_EMPTY = 14 + kSBufs };
 
@@ -238,12 +241,12 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(bar(V_FULL + i), 4);
       mbar_init(bar(K_EMPTY + i), 1);
       mbar_init(bar(V_EMPTY + i), 1);
-      mbar_init(bar(P_FULL + i), 8);      // one elected lane per softmax warp
+      mbar_init(bar(P_FULL + i), kEwWarps);      // one elected lane per softmax warp
       mbar_init(bar(P_EMPTY + i), 1);
     }
     for (int i = 0; i < kSBufs; ++i) {
       mbar_init(bar(S_FULL + i), 1);
-      mbar_init(bar(S_EMPTY + i), 8);
+      mbar_init(bar(S_EMPTY + i), kEwWarps);
     }
     mbar_init(bar(O_FULL), 1);
     misc[2] = 0u;
@@ -372,21 +375,21 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else if (warp >= 4) {
     // ================= softmax warps =================
-    // warp -> (TMEM lane quarter = warp & 3, column half = (warp-2) >> 2): a thread owns one key token of
-    // the stacked pair (lane t) and 32 of the 64 query rows (columns c0..c0+31).
+    // warp -> (TMEM lane quarter = warp & 3, column group = (warp-4) >> 2): a thread owns one key token of
+    // the stacked pair (lane t) and kEwCols of the 64 query rows (columns c0..c0+kEwCols-1).
     const int quarter = warp & 3;
-    const int chalf = (warp - 4) >> 2;
-    const int c0 = chalf * 32;
+    const int cg = (warp - 4) >> 2;
+    const int c0 = cg * kEwCols;
     const int t = quarter * 32 + lane;
     const int half = t >> 6, r = t & 63;
-    const int st = tid - 128;                     // 0..255 among the softmax threads
+    const int st = tid - 128;                     // index among the softmax threads
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     float* m_warp = reinterpret_cast<float*>(sm + FwdSmem::m_warp);
     float* m_col = reinterpret_cast<float*>(sm + FwdSmem::m_col);
     float* l_col = reinterpret_cast<float*>(sm + FwdSmem::l_col);
-    float lsum[32];
+    float lsum[kEwCols];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) lsum[j] = 0.f;
+    for (int j = 0; j < kEwCols; ++j) lsum[j] = 0.f;
 
     for (int p = 0; p < n_pairs && ok; ++p) {
       const int s = p & 1;
@@ -399,8 +402,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
-      uint32_t sv[32];
-      tmem_ld32(tmem_s0 + sb * 64 + lane_addr + c0, sv);
+      uint32_t sv[kEwCols];
+      tmem_ld16(tmem_s0 + sb * 64 + lane_addr + c0, sv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
@@ -409,17 +412,17 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
       if (p == 0) {   // exact column maxima of the first live pair: warp shuffle, then across the lane quarters
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < kEwCols; ++j) {
           const float x = warp_max(live ? __uint_as_float(sv[j]) * c : -INFINITY);
           if (lane == 0) m_warp[quarter * 64 + c0 + j] = x;
         }
-        named_barrier(1, 256);
+        named_barrier(1, kEwThreads);
         if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st]));
-        named_barrier(1, 256);
+        named_barrier(1, kEwThreads);
       }
       // padding rows of a ragged tile (and the repeated tile of an odd tail): whatever sits in V there
       // must not reach the tensor core, where 0 * NaN would poison the sum
-      if (!live && chalf == 0) {
+      if (!live && cg == 0) {
         ok = VSA_WAIT(bar(V_FULL + s), ph);
         uint8_t* vrow = sm + FwdSmem::v + s * kPairBytes + t * 128;
 #pragma unroll
@@ -430,9 +433,9 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       ok = __all_sync(0xffffffffu, ok);     // keep the warp's control flow uniform
       if (!ok) break;
-      uint32_t packed[16];
+      uint32_t packed[kEwCols / 2];
 #pragma unroll
-      for (int j4 = 0; j4 < 8; ++j4) {
+      for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
         const float4 m4 = *reinterpret_cast<const float4*>(m_col + c0 + 4 * j4);
         const float p0 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m4.x)) : 0.f;
         const float p1 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m4.y)) : 0.f;
@@ -448,8 +451,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (tid == 128) VSA_TRACE_AT(8, p);
       uint8_t* prow = sm + FwdSmem::p + s * kPairHalf + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch)     // this thread's 32 query rows are chunks 4*chalf .. 4*chalf+3 of row t
-        *reinterpret_cast<uint4*>(prow + (((4 * chalf + ch) ^ (t & 7)) << 4)) =
+      for (int ch = 0; ch < kEwCols / 8; ++ch)     // this thread's query rows are 16-byte chunks of row t
+        *reinterpret_cast<uint4*>(prow + ((((kEwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
             make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       fence_proxy_async_smem();
       __syncwarp();
@@ -460,24 +463,24 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // ---- epilogue: reduce the row sums across lanes (fixed order), normalise O^T, transpose via shared memory ----
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < kEwCols; ++j) {
       const float x = warp_sum(lsum[j]);
       if (lane == 0) m_warp[quarter * 64 + c0 + j] = x;       // the maxima scratch is free by now
     }
-    named_barrier(1, 256);
+    named_barrier(1, kEwThreads);
     if (st < 64) l_col[st] = (m_warp[st] + m_warp[64 + st]) + (m_warp[128 + st] + m_warp[192 + st]);
-    named_barrier(1, 256);
+    named_barrier(1, kEwThreads);
     if (ok && n_pairs > 0) ok = VSA_WARP_WAIT(bar(O_FULL), 0);
     if (!ok) report_timeout(4);
     tc_fence_after();
     bool finite = true;
     bf16* stage = reinterpret_cast<bf16*>(sm + FwdSmem::k);     // [64 query rows][128 dims], all MMAs are done
     if (ok && n_pairs > 0) {
-      uint32_t ov[32];
-      tmem_ld32(tmem_o + lane_addr + c0, ov);
+      uint32_t ov[kEwCols];
+      tmem_ld16(tmem_o + lane_addr + c0, ov);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < kEwCols; ++j) {
         const int qi = c0 + j;
         const float l = l_col[qi];
         const float o = __uint_as_float(ov[j]) / l;
@@ -485,17 +488,17 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         stage[qi * kD + t] = __float2bfloat16_rn(o);
       }
     } else {
-      for (int j = 0; j < 32; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(n_pairs == 0 ? NAN : 0.f);
+      for (int j = 0; j < kEwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(n_pairs == 0 ? NAN : 0.f);
     }
     // vote across the softmax threads through shared memory
     volatile uint32_t* flag = misc + 2;
     if (!finite) *flag = 1u;
-    named_barrier(1, 256);
+    named_barrier(1, kEwThreads);
     const bool redo = (*flag != 0u) && ok;
     bf16* og = out + (bh * Lq + (long long)qtile * kTile) * kD;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int cidx = st + 256 * i;                // 1024 chunks of 16 bytes
+    for (int i = 0; i < 1024 / kEwThreads; ++i) {
+      const int cidx = st + kEwThreads * i;         // 1024 chunks of 16 bytes
       const int row = cidx >> 4, ch = cidx & 15;
       *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
     }

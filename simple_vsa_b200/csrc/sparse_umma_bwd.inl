@@ -18,7 +18,8 @@
 //
 // Nothing here needs a running maximum (the forward saved the log-sum-exp), so there is no
 // cross-lane traffic at all.  Roles per CTA: warp 0 and 1 = TMA producers (four lanes, one box each),
-// warp 2 = issuer of the score MMAs, warp 3 = issuer of the gradient MMAs, warps 4-11 = elementwise.
+// warp 2 = issuer of the score MMAs, warp 3 = issuer of the gradient MMAs, warps 4-19 = elementwise
+// (a TMEM lane quarter x 16 of the 64 columns each).
 
 // 8 MMAs over the 128-wide reduction, both operands reduction-contiguous ("K-major").
 // a_pair: a stacked pair [2 halves][128 rows][128 B]; b_tile: one tile [2 halves][64 rows][128 B].
@@ -39,7 +40,7 @@ __device__ __forceinline__ void issue_mnmajor(uint32_t d_tmem, uint32_t a_pair, 
            (accumulate || ks > 0) ? 1u : 0u);
 }
 
-constexpr int kBwdThreads = 384;
+constexpr int kBwdThreads = 128 + kEwThreads;
 
 // ------------------------------------------------------------------------------------------------------
 // dQ
@@ -98,12 +99,12 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_init(bar(DQ_V_FULL + i), 4);
       mbar_init(bar(DQ_K_EMPTY + i), 1);
       mbar_init(bar(DQ_V_EMPTY + i), 1);
-      mbar_init(bar(DQ_DS_FULL + i), 8);
+      mbar_init(bar(DQ_DS_FULL + i), kEwWarps);
       mbar_init(bar(DQ_DS_EMPTY + i), 1);
     }
     for (int i = 0; i < kDqBufs; ++i) {
       mbar_init(bar(DQ_S_FULL + i), 1);
-      mbar_init(bar(DQ_S_EMPTY + i), 8);
+      mbar_init(bar(DQ_S_EMPTY + i), kEwWarps);
     }
     mbar_init(bar(DQ_ACC_FULL), 1);
     fence_barrier_init();
@@ -116,14 +117,16 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
     tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
   }
-  if (warp >= 4) {   // delta = rowsum(out_s * dout) and the saved statistic, four threads per query row
+  if (warp >= 4) {   // delta = rowsum(out_s * dout) and the saved statistic, eight threads per query row
+    constexpr int kPer = kEwThreads / 64;            // threads per row
+    constexpr int kDims = kD / kPer;                 // dims per thread
     const int st = tid - 128;
-    const int row = st >> 2, part = st & 3;
-    const uint4* po = reinterpret_cast<const uint4*>(out_s + (qrow0 + row) * kD + part * 32);
-    const uint4* pd = reinterpret_cast<const uint4*>(dout + (qrow0 + row) * kD + part * 32);
+    const int row = st / kPer, part = st % kPer;
+    const uint4* po = reinterpret_cast<const uint4*>(out_s + (qrow0 + row) * kD + part * kDims);
+    const uint4* pd = reinterpret_cast<const uint4*>(dout + (qrow0 + row) * kD + part * kDims);
     float acc = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < kDims / 8; ++i) {
       const uint4 a = po[i], b = pd[i];
       const __nv_bfloat162* ea = reinterpret_cast<const __nv_bfloat162*>(&a);
       const __nv_bfloat162* eb = reinterpret_cast<const __nv_bfloat162*>(&b);
@@ -134,8 +137,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         acc = fmaf(fa.y, fb.y, acc);
       }
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+#pragma unroll
+    for (int o = 1; o < kPer; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (part == 0) {
       s_delta[row] = acc;
       delta[qrow0 + row] = acc;
@@ -235,10 +238,10 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (!ok) report_timeout(13);
     }
   } else {
-    // elementwise warps: lane t = key token of the pair, 32 of the 64 query rows (columns c0..c0+31)
+    // elementwise warps: lane t = key token of the pair, kEwCols of the 64 query rows (columns c0..)
     const int quarter = warp & 3;
-    const int chalf = (warp - 4) >> 2;
-    const int c0 = chalf * 32;
+    const int cg = (warp - 4) >> 2;
+    const int c0 = cg * kEwCols;
     const int t = quarter * 32 + lane;
     const int half = t >> 6, r = t & 63;
     const int st = tid - 128;
@@ -252,16 +255,16 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       ok = VSA_WARP_WAIT(bar(DQ_S_FULL + b), (p / kDqBufs) & 1);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[32], dv[32];
-      tmem_ld32(tmem + b * 128 + lane_addr + c0, sv);
-      tmem_ld32(tmem + b * 128 + 64 + lane_addr + c0, dv);
+      uint32_t sv[kEwCols], dv[kEwCols];
+      tmem_ld16(tmem + b * 128 + lane_addr + c0, sv);
+      tmem_ld16(tmem + b * 128 + 64 + lane_addr + c0, dv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DQ_S_EMPTY + b));
       // rows of K beyond a ragged tile's size (and the repeated tile of an odd tail) must be finite zeros:
       // they meet dS = 0 in the dQ product, where 0 * NaN would poison the sum.  S(p) has completed.
-      if (!live && chalf == 0) {
+      if (!live && cg == 0) {
         uint8_t* krow = sm + DqSmem::k + s * kPairBytes + t * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
@@ -269,9 +272,9 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           *reinterpret_cast<uint4*>(krow + kPairHalf + ch * 16) = make_uint4(0, 0, 0, 0);
         }
       }
-      uint32_t packed[16];
+      uint32_t packed[kEwCols / 2];
 #pragma unroll
-      for (int j4 = 0; j4 < 8; ++j4) {
+      for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
         const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c0 + 4 * j4);
         const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c0 + 4 * j4);
         const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -l4.x));
@@ -289,8 +292,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (!ok) break;
       uint8_t* drow = sm + DqSmem::ds + s * kPairHalf + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch)
-        *reinterpret_cast<uint4*>(drow + (((4 * chalf + ch) ^ (t & 7)) << 4)) =
+      for (int ch = 0; ch < kEwCols / 8; ++ch)
+        *reinterpret_cast<uint4*>(drow + ((((kEwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
             make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       fence_proxy_async_smem();
       __syncwarp();
@@ -302,19 +305,19 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tc_fence_after();
     bf16* stage = reinterpret_cast<bf16*>(sm + DqSmem::k);      // [64 query rows][128 dims]; every MMA is done
     if (ok && n_pairs > 0) {
-      uint32_t av[32];
-      tmem_ld32(tmem_acc + lane_addr + c0, av);
+      uint32_t av[kEwCols];
+      tmem_ld16(tmem_acc + lane_addr + c0, av);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
+      for (int j = 0; j < kEwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
     } else {
-      for (int j = 0; j < 32; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
+      for (int j = 0; j < kEwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
     }
-    named_barrier(1, 256);
+    named_barrier(1, kEwThreads);
     bf16* og = dq + qrow0 * kD;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int cidx = st + 256 * i;
+    for (int i = 0; i < 1024 / kEwThreads; ++i) {
+      const int cidx = st + kEwThreads * i;
       const int row = cidx >> 4, ch = cidx & 15;
       *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
     }
@@ -391,12 +394,12 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(bar(DK_DO_FULL + i), 4);
       mbar_init(bar(DK_Q_EMPTY + i), 1);
       mbar_init(bar(DK_DO_EMPTY + i), 1);
-      mbar_init(bar(DK_PDS_FULL + i), 8);
+      mbar_init(bar(DK_PDS_FULL + i), kEwWarps);
       mbar_init(bar(DK_PDS_EMPTY + i), 1);
     }
     for (int i = 0; i < kDkBufs; ++i) {
       mbar_init(bar(DK_S_FULL + i), 1);
-      mbar_init(bar(DK_S_EMPTY + i), 8);
+      mbar_init(bar(DK_S_EMPTY + i), kEwWarps);
     }
     mbar_init(bar(DK_ACC_FULL), 1);
     fence_barrier_init();
@@ -475,10 +478,10 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (!ok) report_timeout(23);
     }
   } else {
-    // elementwise warps: lane t = query row of the pair, 32 of the 64 key tokens (columns c0..c0+31)
+    // elementwise warps: lane t = query row of the pair, kEwCols of the 64 key tokens (columns c0..)
     const int quarter = warp & 3;
-    const int chalf = (warp - 4) >> 2;
-    const int c0 = chalf * 32;
+    const int cg = (warp - 4) >> 2;
+    const int c0 = cg * kEwCols;
     const int t = quarter * 32 + lane;
     const int half = t >> 6, r = t & 63;
     const int st = tid - 128;
@@ -508,16 +511,16 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[32], dvv[32];
-      tmem_ld32(tmem + b * 128 + lane_addr + c0, sv);
-      tmem_ld32(tmem + b * 128 + 64 + lane_addr + c0, dvv);
+      uint32_t sv[kEwCols], dvv[kEwCols];
+      tmem_ld16(tmem + b * 128 + lane_addr + c0, sv);
+      tmem_ld16(tmem + b * 128 + 64 + lane_addr + c0, dvv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DK_S_EMPTY + b));
-      uint32_t pp[16], pg[16];
+      uint32_t pp[kEwCols / 2], pg[kEwCols / 2];
 #pragma unroll
-      for (int j2 = 0; j2 < 16; ++j2) {
+      for (int j2 = 0; j2 < kEwCols / 2; ++j2) {
         const bool k0 = live && (c0 + 2 * j2) < valid, k1 = live && (c0 + 2 * j2 + 1) < valid;
         const float p0 = k0 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse)) : 0.f;
         const float p1 = k1 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse)) : 0.f;
@@ -531,8 +534,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       uint8_t* prow = sm + DkSmem::p + s * kPairHalf + t * 128;
       uint8_t* grow = sm + DkSmem::ds + s * kPairHalf + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const uint32_t off = (uint32_t)(((4 * chalf + ch) ^ (t & 7)) << 4);
+      for (int ch = 0; ch < kEwCols / 8; ++ch) {
+        const uint32_t off = (uint32_t)((((kEwCols / 8) * cg + ch) ^ (t & 7)) << 4);
         *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
         *reinterpret_cast<uint4*>(grow + off) = make_uint4(pg[4 * ch], pg[4 * ch + 1], pg[4 * ch + 2], pg[4 * ch + 3]);
       }
@@ -547,27 +550,27 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     bf16* stage_k = reinterpret_cast<bf16*>(sm + DkSmem::q);          // [64 key rows][128 dims] each; all MMAs done
     bf16* stage_v = stage_k + kTile * kD;
     if (ok) {
-      uint32_t ak[32], av[32];
-      tmem_ld32(tmem_dk + lane_addr + c0, ak);
-      tmem_ld32(tmem_dv + lane_addr + c0, av);
+      uint32_t ak[kEwCols], av[kEwCols];
+      tmem_ld16(tmem_dk + lane_addr + c0, ak);
+      tmem_ld16(tmem_dv + lane_addr + c0, av);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < kEwCols; ++j) {
         stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(ak[j]) * scale);
         stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
       }
     } else {
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < kEwCols; ++j) {
         stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
         stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
       }
     }
-    named_barrier(1, 256);
+    named_barrier(1, kEwThreads);
     bf16* gk = dk + krow0 * kD;
     bf16* gv = dv + krow0 * kD;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int cidx = st + 256 * i;
+    for (int i = 0; i < 1024 / kEwThreads; ++i) {
+      const int cidx = st + kEwThreads * i;
       const int row = cidx >> 4, ch = cidx & 15;
       *reinterpret_cast<uint4*>(gk + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_k + row * kD + ch * 8);
       *reinterpret_cast<uint4*>(gv + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_v + row * kD + ch * 8);
