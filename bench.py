@@ -42,6 +42,11 @@ WORKLOADS = {
     "c5_92k_be64_tk180": dict(B=2, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False),
     "c2_16k_be64_tk32_gate": dict(B=1, H=12, L=16384, D=128, block_size=(4, 4, 4), topk=32, gate=True),
     "small_8k_be64_tk16": dict(B=1, H=8, L=8192, D=128, block_size=(4, 4, 4), topk=16, gate=False),
+    # logical 256 blocks, 10 % of them ragged (sizes uniform in [1,255], padded rows zeroed)
+    "c3_40k_be256_tk20_ragged": dict(B=1, H=40, L=40960, D=128, block_size=(4, 8, 8), topk=20, gate=False,
+                                     ragged_frac=0.1),
+    # route-explicit executor only: 180 of 1440 key blocks per query block, Zipf(1.1) without replacement
+    "c4_92k_routes_zipf": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="zipf"),
 }
 DEFAULT_WORKLOAD = "c5_92k_be64_tk180"
 SEED = 1234
@@ -234,16 +239,40 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     count = per + (1 if rank < extra else 0)
     first = rank * per + min(rank, extra)
     sizes = torch.full((L // be,), be, dtype=torch.int32, device=dev)
+    nb = L // be
 
     data = make_slices(cfg, first, count, dev)
     q, k, v, dout = data["q"], data["k"], data["v"], data["dout"]
     gate = data.get("gate")
+    if cfg.get("ragged_frac"):
+        g = torch.Generator().manual_seed(SEED)
+        ragged = torch.randperm(nb, generator=g)[:max(1, int(round(nb * cfg["ragged_frac"])))]
+        sizes_h = torch.full((nb,), be, dtype=torch.int32)
+        sizes_h[ragged] = torch.randint(1, be, (ragged.numel(),), generator=g, dtype=torch.int32)
+        sizes = sizes_h.to(dev)
+        pad = (torch.arange(be)[None, :] >= sizes_h[:, None]).reshape(L).to(dev)      # [L] True on padding rows
+        for t in (q, k, v):
+            t[:, :, pad] = 0
+    routes = None
+    if cfg.get("routes") == "zipf":
+        gen = torch.Generator(device=dev)
+        routes = torch.empty((1, count, nb, tk), device=dev, dtype=torch.int32)
+        logw = -1.1 * torch.log(torch.arange(1, nb + 1, device=dev, dtype=torch.float32))
+        for i in range(count):
+            gen.manual_seed(SEED + 7919 * (first + i))
+            perm = torch.randperm(nb, generator=gen, device=dev)
+            u = torch.rand((nb, nb), generator=gen, device=dev).clamp_min(1e-12)
+            routes[0, i] = perm[(logw - torch.log(-torch.log(u))).topk(tk, dim=-1).indices].to(torch.int32)
+        del u
 
     def fwd_bwd(q_, k_, v_, gate_, dout_):
         q_.grad = k_.grad = v_.grad = None
         if gate_ is not None:
             gate_.grad = None
-        out = V.b200_vsa(q_, k_, v_, sizes, sizes, tk, cfg["block_size"], gate_)
+        if routes is not None:
+            out = V.b200_sparse_attention(q_, k_, v_, routes, sizes, block_size=cfg["block_size"])
+        else:
+            out = V.b200_vsa(q_, k_, v_, sizes, sizes, tk, cfg["block_size"], gate_)
         out.backward(dout_)
         return out
 
@@ -292,6 +321,13 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     from simple_vsa_b200.host import vsa_step_from_host
 
     def e2e_step():
+        if routes is not None:     # route-explicit executor: plain copy in / call / copy out
+            dv_ = {n: host_in[n].to(dev, non_blocking=True) for n in names}
+            ql, kl, vl = (dv_[n].requires_grad_() for n in ("q", "k", "v"))
+            out = fwd_bwd(ql, kl, vl, None, dv_["dout"])
+            for n, t in (("out", out.detach()), ("dq", ql.grad), ("dk", kl.grad), ("dv", vl.grad)):
+                host_out[n].copy_(t, non_blocking=True)
+            return
         # the public host-resident step: chunks of slices, copies overlapped with the kernels
         vsa_step_from_host(host_in["q"], host_in["k"], host_in["v"], host_in["dout"], sizes, sizes, tk,
                            cfg["block_size"], host_in.get("gate"), out=host_out, device=dev,
@@ -357,7 +393,8 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         "dtype": "bf16",
         "data": "synthetic N(0,1), seeded per (batch,head) slice; random routes come from the operator's own Top-K",
         "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], L, D], "block_elements": be,
-                   "topk": tk, "gate": cfg["gate"], "slices_per_gpu": count,
+                   "topk": tk, "gate": cfg["gate"], "slices_per_gpu": count, "ragged_frac": cfg.get("ragged_frac", 0),
+                   "routes": cfg.get("routes", "operator Top-K"),
                    "parallelism": f"(batch,head) slices partitioned over {world} GPU(s), no collective",
                    "l2": "inputs per GPU (%.2f GB) are larger than L2; no flush" % (4 * T / 1e9),
                    "useful_flops_per_call": flops_total},

@@ -40,7 +40,12 @@ __device__ __forceinline__ void issue_mnmajor(uint32_t d_tmem, uint32_t a_pair, 
            (accumulate || ks > 0) ? 1u : 0u);
 }
 
-constexpr int kBwdThreads = 128 + kEwThreads;
+// The backward passes are closest to the shared-memory bandwidth limit (every operand byte is read by an
+// MMA once or twice per pair); eight wider elementwise warps disturb that pipe less than sixteen narrow ones.
+constexpr int kBwCols = 32;
+constexpr int kBwWarps = 4 * (64 / kBwCols);
+constexpr int kBwEwThreads = 32 * kBwWarps;
+constexpr int kBwdThreads = 128 + kBwEwThreads;
 
 // ------------------------------------------------------------------------------------------------------
 // dQ
@@ -99,12 +104,12 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_init(bar(DQ_V_FULL + i), 4);
       mbar_init(bar(DQ_K_EMPTY + i), 1);
       mbar_init(bar(DQ_V_EMPTY + i), 1);
-      mbar_init(bar(DQ_DS_FULL + i), kEwWarps);
+      mbar_init(bar(DQ_DS_FULL + i), kBwWarps);
       mbar_init(bar(DQ_DS_EMPTY + i), 1);
     }
     for (int i = 0; i < kDqBufs; ++i) {
       mbar_init(bar(DQ_S_FULL + i), 1);
-      mbar_init(bar(DQ_S_EMPTY + i), kEwWarps);
+      mbar_init(bar(DQ_S_EMPTY + i), kBwWarps);
     }
     mbar_init(bar(DQ_ACC_FULL), 1);
     fence_barrier_init();
@@ -118,7 +123,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
   }
   if (warp >= 4) {   // delta = rowsum(out_s * dout) and the saved statistic, eight threads per query row
-    constexpr int kPer = kEwThreads / 64;            // threads per row
+    constexpr int kPer = kBwEwThreads / 64;            // threads per row
     constexpr int kDims = kD / kPer;                 // dims per thread
     const int st = tid - 128;
     const int row = st / kPer, part = st % kPer;
@@ -238,10 +243,10 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (!ok) report_timeout(13);
     }
   } else {
-    // elementwise warps: lane t = key token of the pair, kEwCols of the 64 query rows (columns c0..)
+    // elementwise warps: lane t = key token of the pair, kBwCols of the 64 query rows (columns c0..)
     const int quarter = warp & 3;
     const int cg = (warp - 4) >> 2;
-    const int c0 = cg * kEwCols;
+    const int c0 = cg * kBwCols;
     const int t = quarter * 32 + lane;
     const int half = t >> 6, r = t & 63;
     const int st = tid - 128;
@@ -255,9 +260,9 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       ok = VSA_WARP_WAIT(bar(DQ_S_FULL + b), (p / kDqBufs) & 1);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[kEwCols], dv[kEwCols];
-      tmem_ld16(tmem + b * 128 + lane_addr + c0, sv);
-      tmem_ld16(tmem + b * 128 + 64 + lane_addr + c0, dv);
+      uint32_t sv[kBwCols], dv[kBwCols];
+      tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
+      tmem_ld(tmem + b * 128 + 64 + lane_addr + c0, dv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
@@ -272,9 +277,9 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           *reinterpret_cast<uint4*>(krow + kPairHalf + ch * 16) = make_uint4(0, 0, 0, 0);
         }
       }
-      uint32_t packed[kEwCols / 2];
+      uint32_t packed[kBwCols / 2];
 #pragma unroll
-      for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
+      for (int j4 = 0; j4 < kBwCols / 4; ++j4) {
         const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c0 + 4 * j4);
         const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c0 + 4 * j4);
         const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -l4.x));
@@ -292,8 +297,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (!ok) break;
       uint8_t* drow = sm + DqSmem::ds + s * kPairHalf + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < kEwCols / 8; ++ch)
-        *reinterpret_cast<uint4*>(drow + ((((kEwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
+      for (int ch = 0; ch < kBwCols / 8; ++ch)
+        *reinterpret_cast<uint4*>(drow + ((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
             make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       fence_proxy_async_smem();
       __syncwarp();
@@ -305,19 +310,19 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tc_fence_after();
     bf16* stage = reinterpret_cast<bf16*>(sm + DqSmem::k);      // [64 query rows][128 dims]; every MMA is done
     if (ok && n_pairs > 0) {
-      uint32_t av[kEwCols];
-      tmem_ld16(tmem_acc + lane_addr + c0, av);
+      uint32_t av[kBwCols];
+      tmem_ld(tmem_acc + lane_addr + c0, av);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < kEwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
+      for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
     } else {
-      for (int j = 0; j < kEwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
+      for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
     }
-    named_barrier(1, kEwThreads);
+    named_barrier(1, kBwEwThreads);
     bf16* og = dq + qrow0 * kD;
 #pragma unroll
-    for (int i = 0; i < 1024 / kEwThreads; ++i) {
-      const int cidx = st + kEwThreads * i;
+    for (int i = 0; i < 1024 / kBwEwThreads; ++i) {
+      const int cidx = st + kBwEwThreads * i;
       const int row = cidx >> 4, ch = cidx & 15;
       *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
     }
@@ -394,12 +399,12 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(bar(DK_DO_FULL + i), 4);
       mbar_init(bar(DK_Q_EMPTY + i), 1);
       mbar_init(bar(DK_DO_EMPTY + i), 1);
-      mbar_init(bar(DK_PDS_FULL + i), kEwWarps);
+      mbar_init(bar(DK_PDS_FULL + i), kBwWarps);
       mbar_init(bar(DK_PDS_EMPTY + i), 1);
     }
     for (int i = 0; i < kDkBufs; ++i) {
       mbar_init(bar(DK_S_FULL + i), 1);
-      mbar_init(bar(DK_S_EMPTY + i), kEwWarps);
+      mbar_init(bar(DK_S_EMPTY + i), kBwWarps);
     }
     mbar_init(bar(DK_ACC_FULL), 1);
     fence_barrier_init();
@@ -478,10 +483,10 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (!ok) report_timeout(23);
     }
   } else {
-    // elementwise warps: lane t = query row of the pair, kEwCols of the 64 key tokens (columns c0..)
+    // elementwise warps: lane t = query row of the pair, kBwCols of the 64 key tokens (columns c0..)
     const int quarter = warp & 3;
     const int cg = (warp - 4) >> 2;
-    const int c0 = cg * kEwCols;
+    const int c0 = cg * kBwCols;
     const int t = quarter * 32 + lane;
     const int half = t >> 6, r = t & 63;
     const int st = tid - 128;
@@ -511,16 +516,16 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[kEwCols], dvv[kEwCols];
-      tmem_ld16(tmem + b * 128 + lane_addr + c0, sv);
-      tmem_ld16(tmem + b * 128 + 64 + lane_addr + c0, dvv);
+      uint32_t sv[kBwCols], dvv[kBwCols];
+      tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
+      tmem_ld(tmem + b * 128 + 64 + lane_addr + c0, dvv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DK_S_EMPTY + b));
-      uint32_t pp[kEwCols / 2], pg[kEwCols / 2];
+      uint32_t pp[kBwCols / 2], pg[kBwCols / 2];
 #pragma unroll
-      for (int j2 = 0; j2 < kEwCols / 2; ++j2) {
+      for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
         const bool k0 = live && (c0 + 2 * j2) < valid, k1 = live && (c0 + 2 * j2 + 1) < valid;
         const float p0 = k0 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse)) : 0.f;
         const float p1 = k1 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse)) : 0.f;
@@ -534,8 +539,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       uint8_t* prow = sm + DkSmem::p + s * kPairHalf + t * 128;
       uint8_t* grow = sm + DkSmem::ds + s * kPairHalf + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < kEwCols / 8; ++ch) {
-        const uint32_t off = (uint32_t)((((kEwCols / 8) * cg + ch) ^ (t & 7)) << 4);
+      for (int ch = 0; ch < kBwCols / 8; ++ch) {
+        const uint32_t off = (uint32_t)((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4);
         *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
         *reinterpret_cast<uint4*>(grow + off) = make_uint4(pg[4 * ch], pg[4 * ch + 1], pg[4 * ch + 2], pg[4 * ch + 3]);
       }
@@ -550,27 +555,27 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     bf16* stage_k = reinterpret_cast<bf16*>(sm + DkSmem::q);          // [64 key rows][128 dims] each; all MMAs done
     bf16* stage_v = stage_k + kTile * kD;
     if (ok) {
-      uint32_t ak[kEwCols], av[kEwCols];
-      tmem_ld16(tmem_dk + lane_addr + c0, ak);
-      tmem_ld16(tmem_dv + lane_addr + c0, av);
+      uint32_t ak[kBwCols], av[kBwCols];
+      tmem_ld(tmem_dk + lane_addr + c0, ak);
+      tmem_ld(tmem_dv + lane_addr + c0, av);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < kEwCols; ++j) {
+      for (int j = 0; j < kBwCols; ++j) {
         stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(ak[j]) * scale);
         stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
       }
     } else {
-      for (int j = 0; j < kEwCols; ++j) {
+      for (int j = 0; j < kBwCols; ++j) {
         stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
         stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
       }
     }
-    named_barrier(1, kEwThreads);
+    named_barrier(1, kBwEwThreads);
     bf16* gk = dk + krow0 * kD;
     bf16* gv = dv + krow0 * kD;
 #pragma unroll
-    for (int i = 0; i < 1024 / kEwThreads; ++i) {
-      const int cidx = st + kEwThreads * i;
+    for (int i = 0; i < 1024 / kBwEwThreads; ++i) {
+      const int cidx = st + kBwEwThreads * i;
       const int row = cidx >> 4, ch = cidx & 15;
       *reinterpret_cast<uint4*>(gk + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_k + row * kD + ch * 8);
       *reinterpret_cast<uint4*>(gv + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_v + row * kD + ch * 8);
