@@ -45,6 +45,10 @@ WORKLOADS = {
     # logical 256 blocks, 10 % of them ragged (sizes uniform in [1,255], padded rows zeroed)
     "c3_40k_be256_tk20_ragged": dict(B=1, H=40, L=40960, D=128, block_size=(4, 8, 8), topk=20, gate=False,
                                      ragged_frac=0.1),
+    # sequence-parallel long-sequence run: every rank owns L/W query tokens and the matching K/V shard,
+    # K/V are all-gathered over NCCL, dK/dV reduce-scattered (weak in L per rank is NOT assumed: L is fixed)
+    "c5sp_184k_be64_tk360": dict(B=2, H=40, L=184320, D=128, block_size=(4, 4, 4), topk=360, gate=False, sp=True),
+    "sp_small_32k_be64_tk64": dict(B=1, H=8, L=32768, D=128, block_size=(4, 4, 4), topk=64, gate=False, sp=True),
     # route-explicit executor only: 180 of 1440 key blocks per query block, Zipf(1.1) without replacement
     "c4_92k_routes_zipf": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="zipf"),
 }
@@ -178,15 +182,15 @@ def run_cpu(cfg, steps: int, warmup: int, q_blocks: int = 64):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
-def make_slices(cfg, first: int, count: int, device):
-    """q, k, v, dout (and gate) for ``count`` (batch, head) slices starting at ``first``: [1, count, L, D]."""
+def make_slices(cfg, first: int, count: int, device, rows=None, salt: int = 0):
+    """q, k, v, dout (and gate) for ``count`` (batch, head) slices starting at ``first``: [1, count, rows, D]."""
     import torch
-    L, D = cfg["L"], cfg["D"]
+    L, D = (rows or cfg["L"]), cfg["D"]
     names = ["q", "k", "v", "dout"] + (["gate"] if cfg["gate"] else [])
     out = {n: torch.empty((1, count, L, D), device=device, dtype=torch.bfloat16) for n in names}
     gen = torch.Generator(device=device)
     for i in range(count):
-        gen.manual_seed(SEED + first + i)
+        gen.manual_seed(SEED + first + i + 1000003 * salt)
         for n in names:
             x = torch.randn((L, D), generator=gen, device=device, dtype=torch.float32)
             if n == "gate":
@@ -226,6 +230,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
 
     import simple_vsa_b200 as V
     from simple_vsa_b200 import _lib
+    from simple_vsa_b200.parallel import sequence_parallel_vsa
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -234,14 +239,20 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     be = V.as_block_elements(cfg["block_size"])
     L, D, tk = cfg["L"], cfg["D"], cfg["topk"]
     total_slices = cfg["B"] * cfg["H"]
+    sp = bool(cfg.get("sp"))
     per = total_slices // world
     extra = total_slices % world
     count = per + (1 if rank < extra else 0)
     first = rank * per + min(rank, extra)
     sizes = torch.full((L // be,), be, dtype=torch.int32, device=dev)
     nb = L // be
+    if sp:      # every rank holds all slices but only L/W tokens (its query blocks and its K/V shard)
+        if L % (world * be):
+            raise SystemExit(f"sequence-parallel workload needs L divisible by world*block ({world}*{be})")
+        count, first = total_slices, 0
+    l_loc = L // world if sp else L
 
-    data = make_slices(cfg, first, count, dev)
+    data = make_slices(cfg, first, count, dev, rows=l_loc, salt=rank if sp else 0)
     q, k, v, dout = data["q"], data["k"], data["v"], data["dout"]
     gate = data.get("gate")
     if cfg.get("ragged_frac"):
@@ -269,7 +280,9 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         q_.grad = k_.grad = v_.grad = None
         if gate_ is not None:
             gate_.grad = None
-        if routes is not None:
+        if sp:
+            out = sequence_parallel_vsa(q_, k_, v_, sizes, sizes[:l_loc // be], tk, cfg["block_size"], gate_)
+        elif routes is not None:
             out = V.b200_sparse_attention(q_, k_, v_, routes, sizes, block_size=cfg["block_size"])
         else:
             out = V.b200_vsa(q_, k_, v_, sizes, sizes, tk, cfg["block_size"], gate_)
@@ -321,7 +334,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     from simple_vsa_b200.host import vsa_step_from_host
 
     def e2e_step():
-        if routes is not None:     # route-explicit executor: plain copy in / call / copy out
+        if routes is not None or sp:     # route-explicit executor / sequence-parallel: plain copy in / call / copy out
             dv_ = {n: host_in[n].to(dev, non_blocking=True) for n in names}
             ql, kl, vl = (dv_[n].requires_grad_() for n in ("q", "k", "v"))
             out = fwd_bwd(ql, kl, vl, None, dv_["dout"])
@@ -364,7 +377,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     top = max(fine, key=lambda n: fine[n]["total_ms"])
     # GEMM FLOPs the kernel's algorithm performs per edge: forward S,O = 4; dQ pass S,dP,dQ = 6; dK/dV pass S,dP,dK,dV = 8
     per_edge = {"vsa_sparse_fwd": 4, "vsa_sparse_bwd_dq": 6, "vsa_sparse_bwd_dkdv": 8}[top]
-    edges = count * (L // be) * tk
+    edges = count * (l_loc // be) * tk
     flops_launch = per_edge * float(be) * be * D * edges
     achieved = flops_launch / (fine[top]["avg_ms"] * 1e-3) / 1e12
     traffic = None
@@ -378,7 +391,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     shares = {n: round(kv["total_ms"] / step_total, 4) for n, kv in sorted(kernels.items())}
 
     cpu = run_cpu(cfg, steps=args.cpu_steps, warmup=1) if world == 1 and not args.no_cpu else None
-    T = count * L * D * 2
+    T = count * l_loc * D * 2
     n_in, n_out = len(names), len(out_names)
     line = {
         "metric": "VSA fwd+bwd useful TFLOPS, 92k tok blk64 bf16" if args.workload == DEFAULT_WORKLOAD
@@ -392,10 +405,12 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic N(0,1), seeded per (batch,head) slice; random routes come from the operator's own Top-K",
+        "collectives": ("all-gather K,V + reduce-scatter dK,dV over NCCL (sequence parallel)" if sp else "none"),
         "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], L, D], "block_elements": be,
                    "topk": tk, "gate": cfg["gate"], "slices_per_gpu": count, "ragged_frac": cfg.get("ragged_frac", 0),
                    "routes": cfg.get("routes", "operator Top-K"),
-                   "parallelism": f"(batch,head) slices partitioned over {world} GPU(s), no collective",
+                   "parallelism": (f"sequence split over {world} GPU(s): L/W = {l_loc} tokens per rank" if sp else
+                                   f"(batch,head) slices partitioned over {world} GPU(s), no collective"),
                    "l2": "inputs per GPU (%.2f GB) are larger than L2; no flush" % (4 * T / 1e9),
                    "useful_flops_per_call": flops_total},
         "impl": "b200",
