@@ -166,6 +166,13 @@ int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const vo
                         int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                         float scale, int dtype, void* stream);
 
+/* dst[b, r, :] = map[r] >= 0 ? src[b, map[r], :] : 0 for rows of row_bytes bytes (even; 16-byte
+ * multiples take the vector path).  With the maps of the tiling metadata this is the raster ->
+ * zero-padded tile layout move and its inverse.
+ * Replaces tile / untile: vsa/fastvideo_tiling.py:128-145. */
+int vsa_gather_rows(const void* src, const int32_t* map, void* dst,
+                    int64_t batch, int64_t src_rows, int64_t dst_rows, int64_t row_bytes, void* stream);
+
 /* out = out_s + out_c[block] * gate (gate may be NULL) in fp32, one rounding.
  * Replaces _combine_forward_kernel: vsa/fused_common.py:175-199,259-295. */
 int vsa_combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out,

@@ -22,6 +22,7 @@ import torch
 from torch import Tensor, nn
 
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is absent)
+from .tiling import build_vsa_metadata, tile, tile_with, untile, untile_with
 from .ops import (
     BlockSize,
     as_block_elements,
@@ -37,6 +38,7 @@ __all__ = [
     "b200_sparse_attention", "triton_sparse_attention", "helion_sparse_attention",
     "block_mean", "topk_block_mask", "CompressionGate", "invert_routes",
     "as_block_elements", "validate_vsa_inputs",
+    "build_vsa_metadata", "tile", "untile", "tile_with", "untile_with",
 ]
 
 

@@ -33,6 +33,7 @@ SIGNATURES = {
     "vsa_sparse_bwd_dq": [P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dkdv": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_combine_fwd": [P, P, P, P, L, L, I, I, I, P],
+    "vsa_gather_rows": [P, P, P, L, L, L, L, P],
     "vsa_selftest_umma": [P, P, P, I, P],
     "vsa_device_status": [P],
     "vsa_combine_bwd": [P, P, P, P, P, L, L, I, I, I, P],

@@ -229,6 +229,13 @@ int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const vo
                             topk, scale, dtype, (cudaStream_t)stream);
 }
 
+int vsa_gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
+                    int64_t row_bytes, void* stream) {
+  VSA_REQUIRE(src && map && dst, "gather rows: null pointer");
+  VSA_REQUIRE(batch >= 0 && src_rows >= 0 && dst_rows >= 0 && row_bytes >= 0, "gather rows: negative extent");
+  return gather_rows(src, map, dst, batch, src_rows, dst_rows, row_bytes, (cudaStream_t)stream);
+}
+
 int vsa_selftest_umma(const void* a, const void* b, float* out, int mode, void* stream) {
   VSA_REQUIRE(a && b && out && (mode == 0 || mode == 1), "selftest: bad argument");
   return umma_selftest(a, b, out, mode, (cudaStream_t)stream);

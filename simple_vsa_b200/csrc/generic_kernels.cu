@@ -725,6 +725,50 @@ int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_o
 }
 
 // =========================================================================================
+// Row gather with zero fill: dst[b, r, :] = map[r] >= 0 ? src[b, map[r], :] : 0.
+// One kernel serves both directions of the 3-D tiling front end (vsa/fastvideo_tiling.py:128-145 of
+// the reference): raster -> zero-padded tile-contiguous layout, and back.  Pure HBM traffic:
+// every byte is read once and written once.
+// =========================================================================================
+template <typename W>
+__global__ void __launch_bounds__(256) gather_rows_kernel(const W* __restrict__ src, const int32_t* __restrict__ map,
+                                                          W* __restrict__ dst, long long src_rows, long long dst_rows,
+                                                          int words_per_row, long long total_words) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_words;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row_all = i / words_per_row;
+    const int w = (int)(i - row_all * words_per_row);
+    const long long b = row_all / dst_rows;
+    const long long r = row_all - b * dst_rows;
+    const int m = map[r];
+    W val{};
+    if (m >= 0) val = src[(b * src_rows + m) * words_per_row + w];
+    dst[i] = val;
+  }
+}
+
+int gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
+                int64_t row_bytes, cudaStream_t st) {
+  if (batch == 0 || dst_rows == 0 || row_bytes == 0) return VSA_OK;
+  const bool wide = row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+  if (!wide && row_bytes % 2 != 0) return fail(VSA_ERR_UNSUPPORTED, "gather rows: row size %lld bytes is odd", (long long)row_bytes);
+  const int unit = wide ? 16 : (row_bytes % 4 == 0 ? 4 : 2);
+  const long long wpr = row_bytes / unit;
+  if (wpr > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "gather rows: row too long");
+  const long long total = batch * dst_rows * wpr;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (unit == 16)
+    gather_rows_kernel<uint4><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)src, map, (uint4*)dst, src_rows, dst_rows, (int)wpr, total);
+  else if (unit == 4)
+    gather_rows_kernel<uint32_t><<<(unsigned)blocks, 256, 0, st>>>((const uint32_t*)src, map, (uint32_t*)dst, src_rows, dst_rows, (int)wpr, total);
+  else
+    gather_rows_kernel<uint16_t><<<(unsigned)blocks, 256, 0, st>>>((const uint16_t*)src, map, (uint16_t*)dst, src_rows, dst_rows, (int)wpr, total);
+  return check_launch("gather_rows_kernel");
+}
+
+// =========================================================================================
 // Scalar fine attention (any block volume, any head dim <= 256, bf16 or fp32): one warp
 // per query row (forward, dQ) or per key row (dK/dV).  Lane l holds dims l, l+32, ...
 // =========================================================================================

@@ -20,6 +20,8 @@ int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int
                  int64_t BH, int Qb, int Kb, int topk, cudaStream_t st);
 int route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int64_t BH,
                         int Qb, int Kb, int topk, cudaStream_t st);
+int gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
+                int64_t row_bytes, cudaStream_t st);
 int combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out, int64_t BH, int64_t Lq, int D,
                 int be, int dtype, cudaStream_t st);
 int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,

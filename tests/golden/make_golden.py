@@ -111,10 +111,34 @@ def make_block_mean():
     print("wrote block_mean")
 
 
-if __name__ == "__main__":
+if __name__ == "__main__" and "--tiling-only" not in sys.argv:
     torch.set_num_threads(8)
     for n, c in VSA_CASES.items():
         make_vsa(n, c)
     for n, c in SPARSE_CASES.items():
         make_sparse(n, c)
     make_block_mean()
+
+
+def make_tiling():
+    from vsa import build_vsa_metadata, tile as ref_tile, untile as ref_untile
+    for shape, tsz in (((3, 5, 5), (2, 4, 4)), ((2, 6, 6), (2, 3, 3)), ((5, 9, 7), (4, 4, 4))):
+        meta = build_vsa_metadata(shape, tile_size=tsz, device="cpu")
+        seq = math.prod(shape)
+        x = torch.arange(2 * seq * 3, dtype=torch.float32).reshape(2, seq, 3)
+        nb = math.prod(meta["num_tiles"])
+        tiled = ref_tile(x, meta["tile_partition_indices"], meta["non_pad_index"], nb, meta["max_block_size"])
+        back = ref_untile(tiled, meta["non_pad_index"], meta["reverse_tile_partition_indices"])
+        name = "tiling_%dx%dx%d_%dx%dx%d.npz" % (shape + tsz)
+        np.savez_compressed(os.path.join(HERE, name),
+                            tile_partition_indices=meta["tile_partition_indices"].numpy(),
+                            reverse_tile_partition_indices=meta["reverse_tile_partition_indices"].numpy(),
+                            variable_block_sizes=meta["variable_block_sizes"].numpy(),
+                            non_pad_index=meta["non_pad_index"].numpy(),
+                            num_tiles=np.array(meta["num_tiles"]), max_block_size=np.int64(meta["max_block_size"]),
+                            tiled=tiled.numpy(), untiled=back.numpy())
+        print("wrote", name)
+
+
+if __name__ == "__main__":
+    make_tiling()
