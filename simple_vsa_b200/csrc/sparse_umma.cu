@@ -56,6 +56,8 @@ constexpr int kSlab = 64 * 128;        // one TMA box: 64 rows x 128 bytes
 constexpr int kPairHalf = 2 * kSlab;   // 128 rows x 128 bytes (one head-dim half of a stacked pair)
 constexpr int kPairBytes = 2 * kPairHalf;
 constexpr uint32_t kTmemCols = 512;
+// K pairs in flight: a reload from L2 takes ~2000 cycles, two stages left the S^T issuer waiting for it
+constexpr int kFwdKStages = 3;
 constexpr int kSBufs = 4;              // S^T accumulators in flight (64 columns each); O^T sits behind them
 
 // ---- host: tensor maps ---------------------------------------------------------------------------
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
 struct FwdSmem {
   static constexpr uint32_t q = 0;                               // 16 KB
   static constexpr uint32_t k = q + 2 * kSlab;                   // 2 stages x 32 KB
-  static constexpr uint32_t v = k + 2 * kPairBytes;              // 2 stages x 32 KB
+  static constexpr uint32_t v = k + kFwdKStages * kPairBytes;    // 2 stages x 32 KB (K above: 3 stages)
   static constexpr uint32_t p = v + 2 * kPairBytes;              // 2 buffers x 16 KB
   static constexpr uint32_t tile_row = p + 2 * kPairHalf;        // int32 [kMaxTiles]
   static constexpr uint32_t tile_valid = tile_row + 4 * kMaxTiles;   // uint8 [kMaxTiles]
@@ -206,8 +208,8 @@ constexpr int kEwCols = 16;          // columns of a TMEM tile one elementwise t
 constexpr int kEwWarps = 4 * (64 / kEwCols);   // lane quarters x column groups = 16 warps
 constexpr int kEwThreads = 32 * kEwWarps;
 constexpr int kFwdThreads = 128 + kEwThreads;   // K producer, V producer, two MMA issuers, elementwise warps
-enum FwdBar { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, P_FULL = 9, P_EMPTY = 11, O_FULL = 13,
-              S_FULL = 14, S_EMPTY = 14 + kSBufs };
+enum FwdBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, P_FULL = 11, P_EMPTY = 13, O_FULL = 15,
+              S_FULL = 16, S_EMPTY = 16 + kSBufs };
 
 template <int SUB>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -236,10 +238,12 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // ---- set-up: barriers, tensor memory, the list of live key tiles ----
   if (tid == 0) {
     mbar_init(bar(Q_FULL), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kFwdKStages; ++i) {
       mbar_init(bar(K_FULL + i), 4);      // four producer lanes, one TMA box each
-      mbar_init(bar(V_FULL + i), 4);
       mbar_init(bar(K_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(V_FULL + i), 4);
       mbar_init(bar(V_EMPTY + i), 1);
       mbar_init(bar(P_FULL + i), kEwWarps);      // one elected lane per softmax warp
       mbar_init(bar(P_EMPTY + i), 1);
@@ -311,9 +315,10 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const CUtensorMap* map = is_k ? &map_k : &map_v;
       const int full0 = is_k ? K_FULL : V_FULL, empty0 = is_k ? K_EMPTY : V_EMPTY;
       const uint32_t ring = base + (is_k ? FwdSmem::k : FwdSmem::v);
+      const int depth = is_k ? kFwdKStages : 2;
       for (int p = 0; p < n_pairs; ++p) {
-        const int s = p & 1;
-        const uint32_t ph = (p >> 1) & 1;
+        const int s = p % depth;
+        const uint32_t ph = (p / depth) & 1;
         int idx = 2 * p + which;
         if (idx >= n_live) idx = 2 * p;                     // odd tail: repeat the first tile (masked later)
         const int row = (int)(kv_row_base + tile_row[idx]);
@@ -332,8 +337,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       constexpr uint32_t idesc_s = instr_desc(128, 64, 0, 0);
       ok = VSA_WAIT(bar(Q_FULL), 0);
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int s = p & 1, b = p % kSBufs;
-        ok = VSA_WAIT(bar(K_FULL + s), (p >> 1) & 1) && VSA_WAIT(bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
+        const int s = p % kFwdKStages, b = p % kSBufs;
+        ok = VSA_WAIT(bar(K_FULL + s), (p / kFwdKStages) & 1) && VSA_WAIT(bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
         if (!ok) break;
         VSA_TRACE_AT(0, p);
         tc_fence_after();

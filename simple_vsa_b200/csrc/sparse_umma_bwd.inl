@@ -51,13 +51,17 @@ constexpr int kBwdThreads = 128 + kBwEwThreads;
 // dQ
 // ------------------------------------------------------------------------------------------------------
 constexpr int kDqBufs = 3;     // (S^T, dP^T) accumulator pairs in flight: 3 x 128 columns, dQ^T behind them
+// A K pair stays in shared memory from its score MMA until its dQ MMA, i.e. across the whole elementwise
+// stage plus a ~2000-cycle reload; with two stages that chain was the throughput limit, so K gets three
+// (V is released right after dP^T and keeps two; dS^T makes do with one buffer to pay for it).
+constexpr int kDqKStages = 3;
 struct DqSmem {
   static constexpr uint32_t q = 0;                                // 16 KB
   static constexpr uint32_t d_o = q + 2 * kSlab;                  // 16 KB
-  static constexpr uint32_t k = d_o + 2 * kSlab;                  // 2 x 32 KB
-  static constexpr uint32_t v = k + 2 * kPairBytes;               // 2 x 32 KB
-  static constexpr uint32_t ds = v + 2 * kPairBytes;              // 2 x 16 KB
-  static constexpr uint32_t tile_row = ds + 2 * kPairHalf;        // int32 [kMaxTiles]
+  static constexpr uint32_t k = d_o + 2 * kSlab;                  // 3 x 32 KB
+  static constexpr uint32_t v = k + kDqKStages * kPairBytes;      // 2 x 32 KB
+  static constexpr uint32_t ds = v + 2 * kPairBytes;              // 1 x 16 KB
+  static constexpr uint32_t tile_row = ds + kPairHalf;            // int32 [kMaxTiles]
   static constexpr uint32_t tile_valid = tile_row + 4 * kMaxTiles;
   static constexpr uint32_t lse = tile_valid + kMaxTiles;         // float [64]
   static constexpr uint32_t delta = lse + 256;                    // float [64]
@@ -65,8 +69,8 @@ struct DqSmem {
   static constexpr uint32_t misc = bars + 32 * 8;
   static constexpr uint32_t total = misc + 64;
 };
-enum DqBar { DQ_QDO_FULL = 0, DQ_K_FULL = 1, DQ_V_FULL = 3, DQ_K_EMPTY = 5, DQ_V_EMPTY = 7, DQ_DS_FULL = 9,
-             DQ_DS_EMPTY = 11, DQ_ACC_FULL = 13, DQ_S_FULL = 14, DQ_S_EMPTY = 14 + kDqBufs };
+enum DqBar { DQ_QDO_FULL = 0, DQ_K_FULL = 1, DQ_K_EMPTY = 4, DQ_V_FULL = 7, DQ_V_EMPTY = 9, DQ_DS_FULL = 11,
+             DQ_DS_EMPTY = 12, DQ_ACC_FULL = 13, DQ_S_FULL = 14, DQ_S_EMPTY = 14 + kDqBufs };
 
 template <int SUB>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -99,14 +103,16 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   if (tid == 0) {
     mbar_init(bar(DQ_QDO_FULL), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kDqKStages; ++i) {
       mbar_init(bar(DQ_K_FULL + i), 4);
-      mbar_init(bar(DQ_V_FULL + i), 4);
       mbar_init(bar(DQ_K_EMPTY + i), 1);
-      mbar_init(bar(DQ_V_EMPTY + i), 1);
-      mbar_init(bar(DQ_DS_FULL + i), kBwWarps);
-      mbar_init(bar(DQ_DS_EMPTY + i), 1);
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(DQ_V_FULL + i), 4);
+      mbar_init(bar(DQ_V_EMPTY + i), 1);
+    }
+    mbar_init(bar(DQ_DS_FULL), kBwWarps);
+    mbar_init(bar(DQ_DS_EMPTY), 1);
     for (int i = 0; i < kDqBufs; ++i) {
       mbar_init(bar(DQ_S_FULL + i), 1);
       mbar_init(bar(DQ_S_EMPTY + i), kBwWarps);
@@ -196,9 +202,10 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const CUtensorMap* map = is_k ? &map_k : &map_v;
     const int full0 = is_k ? DQ_K_FULL : DQ_V_FULL, empty0 = is_k ? DQ_K_EMPTY : DQ_V_EMPTY;
     const uint32_t ring = base + (is_k ? DqSmem::k : DqSmem::v);
+    const int depth = is_k ? kDqKStages : 2;
     for (int p = 0; p < n_pairs; ++p) {
-      const int s = p & 1;
-      const uint32_t ph = (p >> 1) & 1;
+      const int s = p % depth;
+      const uint32_t ph = (p / depth) & 1;
       int idx = 2 * p + which;
       if (idx >= n_live) idx = 2 * p;
       const int row = (int)(kv_row_base + tile_row[idx]);
@@ -214,30 +221,34 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (lane == 0) {   // scores: S^T = K2 Q^T and dP^T = V2 dO^T
       ok = VSA_WAIT(bar(DQ_QDO_FULL), 0);
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int s = p & 1, b = p % kDqBufs;
+        const int ks = p % kDqKStages, s = p & 1, b = p % kDqBufs;
         const uint32_t ph = (p >> 1) & 1;
-        ok = VSA_WAIT(bar(DQ_K_FULL + s), ph) && VSA_WAIT(bar(DQ_V_FULL + s), ph) &&
+        ok = VSA_WAIT(bar(DQ_K_FULL + ks), (p / kDqKStages) & 1) && VSA_WAIT(bar(DQ_V_FULL + s), ph) &&
              VSA_WAIT(bar(DQ_S_EMPTY + b), ((p / kDqBufs) & 1) ^ 1);
         if (!ok) break;
+        VSA_TRACE_AT(0, p);
         tc_fence_after();
-        issue_kmajor(tmem + b * 128, base + DqSmem::k + s * kPairBytes, base + DqSmem::q);
+        // dP^T first: its commit hands the V stage back to the producer ~8 MMAs earlier (V has two stages only)
         issue_kmajor(tmem + b * 128 + 64, base + DqSmem::v + s * kPairBytes, base + DqSmem::d_o);
         mma_commit(bar(DQ_V_EMPTY + s));
+        issue_kmajor(tmem + b * 128, base + DqSmem::k + ks * kPairBytes, base + DqSmem::q);
         mma_commit(bar(DQ_S_FULL + b));
+        VSA_TRACE_AT(1, p);
       }
       if (!ok) report_timeout(12);
     }
   } else if (warp == 3) {
     if (lane == 0) {   // dQ^T += K2^T dS^T
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int s = p & 1;
-        const uint32_t ph = (p >> 1) & 1;
-        ok = VSA_WAIT(bar(DQ_K_FULL + s), ph) && VSA_WAIT(bar(DQ_DS_FULL + s), ph);
+        const int ks = p % kDqKStages;
+        ok = VSA_WAIT(bar(DQ_K_FULL + ks), (p / kDqKStages) & 1) && VSA_WAIT(bar(DQ_DS_FULL), p & 1);
         if (!ok) break;
+        VSA_TRACE_AT(3, p);
         tc_fence_after();
-        issue_mnmajor(tmem_acc, base + DqSmem::k + s * kPairBytes, base + DqSmem::ds + s * kPairHalf, p > 0);
-        mma_commit(bar(DQ_K_EMPTY + s));
-        mma_commit(bar(DQ_DS_EMPTY + s));
+        issue_mnmajor(tmem_acc, base + DqSmem::k + ks * kPairBytes, base + DqSmem::ds, p > 0);
+        mma_commit(bar(DQ_K_EMPTY + ks));
+        mma_commit(bar(DQ_DS_EMPTY));
+        VSA_TRACE_AT(4, p);
       }
       if (ok) mma_commit(bar(DQ_ACC_FULL));
       if (!ok) report_timeout(13);
@@ -259,6 +270,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const bool live = r < valid;
       ok = VSA_WARP_WAIT(bar(DQ_S_FULL + b), (p / kDqBufs) & 1);
       if (!ok) break;
+      if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
       uint32_t sv[kBwCols], dv[kBwCols];
       tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
@@ -267,10 +279,11 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DQ_S_EMPTY + b));
+      if (tid == 128) VSA_TRACE_AT(6, p);
       // rows of K beyond a ragged tile's size (and the repeated tile of an odd tail) must be finite zeros:
       // they meet dS = 0 in the dQ product, where 0 * NaN would poison the sum.  S(p) has completed.
       if (!live && cg == 0) {
-        uint8_t* krow = sm + DqSmem::k + s * kPairBytes + t * 128;
+        uint8_t* krow = sm + DqSmem::k + (p % kDqKStages) * kPairBytes + t * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
           *reinterpret_cast<uint4*>(krow + ch * 16) = make_uint4(0, 0, 0, 0);
@@ -293,16 +306,19 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         packed[2 * j4] = pack_bf16(g0, g1);
         packed[2 * j4 + 1] = pack_bf16(g2, g3);
       }
-      ok = VSA_WARP_WAIT(bar(DQ_DS_EMPTY + s), ph ^ 1);
+      if (tid == 128) VSA_TRACE_AT(7, p);
+      ok = VSA_WARP_WAIT(bar(DQ_DS_EMPTY), (p & 1) ^ 1);
       if (!ok) break;
-      uint8_t* drow = sm + DqSmem::ds + s * kPairHalf + t * 128;
+      if (tid == 128) VSA_TRACE_AT(8, p);
+      uint8_t* drow = sm + DqSmem::ds + t * 128;
 #pragma unroll
       for (int ch = 0; ch < kBwCols / 8; ++ch)
         *reinterpret_cast<uint4*>(drow + ((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
             make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(DQ_DS_FULL + s));
+      if (lane == 0) mbar_arrive(bar(DQ_DS_FULL));
+      if (tid == 128) VSA_TRACE_AT(9, p);
     }
     if (!ok && lane == 0) report_timeout(14);
     if (ok && n_pairs > 0) ok = VSA_WARP_WAIT(bar(DQ_ACC_FULL), 0);
@@ -458,10 +474,12 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         ok = VSA_WAIT(bar(DK_Q_FULL + s), ph) && VSA_WAIT(bar(DK_DO_FULL + s), ph) &&
              VSA_WAIT(bar(DK_S_EMPTY + b), ((p / kDkBufs) & 1) ^ 1);
         if (!ok) break;
+        VSA_TRACE_AT(0, p);
         tc_fence_after();
         issue_kmajor(tmem + b * 128, base + DkSmem::q + s * kPairBytes, base + DkSmem::k);
         issue_kmajor(tmem + b * 128 + 64, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::v);
         mma_commit(bar(DK_S_FULL + b));
+        VSA_TRACE_AT(1, p);
       }
       if (!ok) report_timeout(22);
     }
@@ -472,12 +490,14 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t ph = (p >> 1) & 1;
         ok = VSA_WAIT(bar(DK_Q_FULL + s), ph) && VSA_WAIT(bar(DK_DO_FULL + s), ph) && VSA_WAIT(bar(DK_PDS_FULL + s), ph);
         if (!ok) break;
+        VSA_TRACE_AT(3, p);
         tc_fence_after();
         issue_mnmajor(tmem_dv, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::p + s * kPairHalf, p > 0);
         mma_commit(bar(DK_DO_EMPTY + s));
         issue_mnmajor(tmem_dk, base + DkSmem::q + s * kPairBytes, base + DkSmem::ds + s * kPairHalf, p > 0);
         mma_commit(bar(DK_Q_EMPTY + s));
         mma_commit(bar(DK_PDS_EMPTY + s));
+        VSA_TRACE_AT(4, p);
       }
       if (ok) mma_commit(bar(DK_ACC_FULL));
       if (!ok) report_timeout(23);
@@ -515,6 +535,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
       if (!ok) break;
+      if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
       uint32_t sv[kBwCols], dvv[kBwCols];
       tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
@@ -523,6 +544,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DK_S_EMPTY + b));
+      if (tid == 128) VSA_TRACE_AT(6, p);
       uint32_t pp[kBwCols / 2], pg[kBwCols / 2];
 #pragma unroll
       for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
@@ -534,8 +556,10 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         pp[j2] = pack_bf16(p0, p1);
         pg[j2] = pack_bf16(g0, g1);
       }
+      if (tid == 128) VSA_TRACE_AT(7, p);
       ok = VSA_WARP_WAIT(bar(DK_PDS_EMPTY + s), ph ^ 1);
       if (!ok) break;
+      if (tid == 128) VSA_TRACE_AT(8, p);
       uint8_t* prow = sm + DkSmem::p + s * kPairHalf + t * 128;
       uint8_t* grow = sm + DkSmem::ds + s * kPairHalf + t * 128;
 #pragma unroll
@@ -547,6 +571,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DK_PDS_FULL + s));
+      if (tid == 128) VSA_TRACE_AT(9, p);
     }
     if (!ok && lane == 0) report_timeout(24);
     if (ok) ok = VSA_WARP_WAIT(bar(DK_ACC_FULL), 0);
