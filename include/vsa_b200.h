@@ -20,7 +20,8 @@
  *   inverse                         [BH, Qb*topk]    int32 query-block ids grouped by key block
  *
  * dtype: VSA_BF16 (tensor-core kernels for D = 128 and be = 64 or 256, scalar
- * kernels otherwise) or VSA_F32 (scalar kernels, the fp32 validation mode).
+ * kernels otherwise), VSA_F32 (scalar kernels, the fp32 validation mode) or VSA_F16
+ * (scalar kernels; the reference accepts fp16 too).
  *
  * Each comment names the function of the reference project (path inside that
  * project : lines) whose work the entry point replaces.
@@ -43,7 +44,7 @@ typedef enum vsa_status {
   VSA_ERR_DEVICE_TIMEOUT = -4  /* a bounded device-side wait ran out */
 } vsa_status;
 
-typedef enum vsa_dtype { VSA_BF16 = 0, VSA_F32 = 1 } vsa_dtype;
+typedef enum vsa_dtype { VSA_BF16 = 0, VSA_F32 = 1, VSA_F16 = 2 } vsa_dtype;
 
 /* Text of the last error on the calling thread ("" if none). */
 const char* vsa_last_error_string(void);

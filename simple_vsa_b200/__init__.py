@@ -92,13 +92,13 @@ def topk_block_mask(scores: Tensor, topk: int) -> Tensor:
     kb = scores.shape[-1]
     topk = min(int(topk), kb)
     flat = scores.contiguous()
-    if flat.dtype not in (torch.bfloat16, torch.float32):
+    if flat.dtype not in (torch.bfloat16, torch.float32, torch.float16):
         flat = flat.float()
     rows = flat.numel() // kb
     sel = torch.empty((rows, topk), device=scores.device, dtype=torch.int32)
     with torch.cuda.device(scores.device):
         _lib.call("vsa_topk", flat.data_ptr(), sel.data_ptr(), rows, kb, topk,
-                  _lib.VSA_BF16 if flat.dtype == torch.bfloat16 else _lib.VSA_F32,
+                  {torch.bfloat16: _lib.VSA_BF16, torch.float32: _lib.VSA_F32, torch.float16: _lib.VSA_F16}[flat.dtype],
                   torch.cuda.current_stream(scores.device).cuda_stream)
     mask = torch.zeros((rows, kb), device=scores.device, dtype=torch.bool).scatter_(-1, sel.long(), True)
     return mask.view(scores.shape)

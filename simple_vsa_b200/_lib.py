@@ -13,7 +13,7 @@ from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libvsa_b200.so")
 
-VSA_BF16, VSA_F32 = 0, 1
+VSA_BF16, VSA_F32, VSA_F16 = 0, 1, 2
 ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_DEVICE_TIMEOUT = -1, -2, -3, -4
 
 P, I, L, F = c_void_p, c_int, c_int64, c_float

@@ -47,7 +47,8 @@ static bool mma_forced() {
 }
 
 static int check_dtype(int dtype) {
-  if (dtype != VSA_BF16 && dtype != VSA_F32) return fail(VSA_ERR_UNSUPPORTED, "dtype %d is not bf16 (0) or fp32 (1)", dtype);
+  if (dtype != VSA_BF16 && dtype != VSA_F32 && dtype != VSA_F16)
+    return fail(VSA_ERR_UNSUPPORTED, "dtype %d is not bf16 (0), fp32 (1) or fp16 (2)", dtype);
   return VSA_OK;
 }
 

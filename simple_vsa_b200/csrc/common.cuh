@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -36,6 +37,12 @@ template <> struct Elem<__nv_bfloat16> {
   __device__ __forceinline__ static float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   __device__ __forceinline__ static void st(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
   __device__ __forceinline__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+};
+
+template <> struct Elem<__half> {
+  __device__ __forceinline__ static float ld(const __half* p) { return __half2float(*p); }
+  __device__ __forceinline__ static void st(__half* p, float x) { *p = __float2half_rn(x); }
+  __device__ __forceinline__ static float round(float x) { return __half2float(__float2half_rn(x)); }
 };
 
 // ---- warp helpers -----------------------------------------------------------------------

@@ -6,12 +6,27 @@
 // cover (fp32 validation mode, block volumes other than 64/256, head dims
 // other than 128).  Arithmetic follows the reference project's conventions:
 // fp32 accumulation, base-2 log-sum-exp, masks from the per-block sizes.
+#include <cuda_fp16.h>
+
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "kernels.h"
 
 namespace vsa {
+
+// Run `f` with a null pointer of the element type that `dtype` names (bf16, fp32 or fp16).
+template <typename F>
+static int dispatch_dtype(int dtype, F&& f) {
+  switch (dtype) {
+    case VSA_F32: return f(static_cast<float*>(nullptr));
+    case VSA_F16: return f(static_cast<__half*>(nullptr));
+    default: return f(static_cast<__nv_bfloat16*>(nullptr));
+  }
+}
+#define VSA_TAG_TYPE(tag) typename std::remove_pointer<decltype(tag)>::type
+static inline int elems_per_16_bytes(int dtype) { return dtype == VSA_F32 ? 4 : 8; }
 
 // =========================================================================================
 // Block means (vsa/common.py:55-82 of the reference): one CTA per (tensor, bh, block).
@@ -93,8 +108,10 @@ int block_mean_fwd(const void* const* x, void* const* out, const int32_t* const*
     job.sizes[t] = sizes[t];
     job.nb[t] = (int)(L[t] / be);
   }
-  return dtype == VSA_F32 ? launch_block_mean<float>(job, ntensors, BH, D, be, st)
-                          : launch_block_mean<__nv_bfloat16>(job, ntensors, BH, D, be, st);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    return launch_block_mean<T>(job, ntensors, BH, D, be, st);
+  });
 }
 
 // Block-mean backward (vsa/fused_common.py:62-103 of the reference).  ACCUM adds into
@@ -137,19 +154,17 @@ int block_mean_bwd(void* dx, const void* dmean, const int32_t* sizes, int64_t BH
   const int nb = (int)(L / be);
   const long long total = BH * nb;
   if (total == 0) return VSA_OK;
-  const int vec = dtype == VSA_F32 ? 4 : 8;
+  const int vec = elems_per_16_bytes(dtype);
   if (D % vec != 0 || D / vec > 128)
     return fail(VSA_ERR_UNSUPPORTED, "block mean backward: head dim %d must be a multiple of %d and <= 256", D, vec);
-#define VSA_LAUNCH_BMB(T, ACC)                                                                        \
-  block_mean_bwd_kernel<T, ACC><<<(unsigned)total, 128, 0, st>>>(reinterpret_cast<T*>(dx),             \
-                                                                reinterpret_cast<const T*>(dmean), sizes, nb, D, be)
-  if (dtype == VSA_F32) {
-    if (accumulate) VSA_LAUNCH_BMB(float, true); else VSA_LAUNCH_BMB(float, false);
-  } else {
-    if (accumulate) VSA_LAUNCH_BMB(__nv_bfloat16, true); else VSA_LAUNCH_BMB(__nv_bfloat16, false);
-  }
-#undef VSA_LAUNCH_BMB
-  return check_launch("block_mean_bwd_kernel");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    if (accumulate)
+      block_mean_bwd_kernel<T, true><<<(unsigned)total, 128, 0, st>>>((T*)dx, (const T*)dmean, sizes, nb, D, be);
+    else
+      block_mean_bwd_kernel<T, false><<<(unsigned)total, 128, 0, st>>>((T*)dx, (const T*)dmean, sizes, nb, D, be);
+    return check_launch("block_mean_bwd_kernel");
+  });
 }
 
 // =========================================================================================
@@ -296,12 +311,11 @@ static int coarse_fwd_t(const T* qc, const T* kc, const T* vc, T* scores, T* pro
 
 int coarse_fwd(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
                int Qb, int Kb, int D, float scale, int dtype, cudaStream_t st) {
-  if (dtype == VSA_F32)
-    return coarse_fwd_t<float>((const float*)qc, (const float*)kc, (const float*)vc, (float*)scores, (float*)probs,
-                               (float*)out_c, BH, Qb, Kb, D, scale, st);
-  using B = __nv_bfloat16;
-  return coarse_fwd_t<B>((const B*)qc, (const B*)kc, (const B*)vc, (B*)scores, (B*)probs, (B*)out_c, BH, Qb, Kb, D,
-                         scale, st);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    return coarse_fwd_t<T>((const T*)qc, (const T*)kc, (const T*)vc, (T*)scores, (T*)probs, (T*)out_c, BH, Qb, Kb, D,
+                           scale, st);
+  });
 }
 
 template <typename T>
@@ -333,13 +347,11 @@ static int coarse_bwd_t(const T* d_out_c, const T* out_c, const T* qc, const T* 
 int coarse_bwd(const void* d_out_c, const void* out_c, const void* qc, const void* kc, const void* vc,
                const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb, int Kb,
                int D, float scale, int dtype, cudaStream_t st) {
-  if (dtype == VSA_F32)
-    return coarse_bwd_t<float>((const float*)d_out_c, (const float*)out_c, (const float*)qc, (const float*)kc,
-                               (const float*)vc, (const float*)probs, (float*)ds, rowdot, (float*)dqc, (float*)dkc,
-                               (float*)dvc, BH, Qb, Kb, D, scale, st);
-  using B = __nv_bfloat16;
-  return coarse_bwd_t<B>((const B*)d_out_c, (const B*)out_c, (const B*)qc, (const B*)kc, (const B*)vc,
-                         (const B*)probs, (B*)ds, rowdot, (B*)dqc, (B*)dkc, (B*)dvc, BH, Qb, Kb, D, scale, st);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    return coarse_bwd_t<T>((const T*)d_out_c, (const T*)out_c, (const T*)qc, (const T*)kc, (const T*)vc,
+                           (const T*)probs, (T*)ds, rowdot, (T*)dqc, (T*)dkc, (T*)dvc, BH, Qb, Kb, D, scale, st);
+  });
 }
 
 // =========================================================================================
@@ -455,11 +467,11 @@ int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int
   if (Kb > kTopkMaxCols) return fail(VSA_ERR_UNSUPPORTED, "topk: %d key blocks exceed the supported %d", Kb, kTopkMaxCols);
   if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "topk: too many rows");
   const size_t smem = (size_t)Kb * sizeof(uint32_t);
-  if (dtype == VSA_F32)
-    topk_kernel<float><<<(unsigned)rows, kTopkThreads, smem, st>>>((const float*)scores, selected, Kb, topk);
-  else
-    topk_kernel<__nv_bfloat16><<<(unsigned)rows, kTopkThreads, smem, st>>>((const __nv_bfloat16*)scores, selected, Kb, topk);
-  return check_launch("topk_kernel");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    topk_kernel<T><<<(unsigned)rows, kTopkThreads, smem, st>>>((const T*)scores, selected, Kb, topk);
+    return check_launch("topk_kernel");
+  });
 }
 
 // =========================================================================================
@@ -633,22 +645,22 @@ __global__ void __launch_bounds__(256) combine_fwd_kernel(const T* __restrict__ 
 
 int combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out, int64_t BH, int64_t Lq, int D,
                 int be, int dtype, cudaStream_t st) {
-  const int vec = dtype == VSA_F32 ? 4 : 8;
+  const int vec = elems_per_16_bytes(dtype);
   if (D % vec != 0) return fail(VSA_ERR_UNSUPPORTED, "combine: head dim %d must be a multiple of %d", D, vec);
   const long long chunks = BH * Lq * (D / vec);
   if (chunks == 0) return VSA_OK;
   long long blocks = (chunks + 255) / 256;
   if (blocks > 148LL * 64) blocks = 148LL * 64;
-#define VSA_LAUNCH_CF(T, G)                                                                                   \
-  combine_fwd_kernel<T, G><<<(unsigned)blocks, 256, 0, st>>>((const T*)out_s, (const T*)out_c, (const T*)gate, \
-                                                            (T*)out, chunks, D, be)
-  if (dtype == VSA_F32) {
-    if (gate) VSA_LAUNCH_CF(float, true); else VSA_LAUNCH_CF(float, false);
-  } else {
-    if (gate) VSA_LAUNCH_CF(__nv_bfloat16, true); else VSA_LAUNCH_CF(__nv_bfloat16, false);
-  }
-#undef VSA_LAUNCH_CF
-  return check_launch("combine_fwd_kernel");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    if (gate)
+      combine_fwd_kernel<T, true><<<(unsigned)blocks, 256, 0, st>>>((const T*)out_s, (const T*)out_c, (const T*)gate,
+                                                                   (T*)out, chunks, D, be);
+    else
+      combine_fwd_kernel<T, false><<<(unsigned)blocks, 256, 0, st>>>((const T*)out_s, (const T*)out_c, (const T*)gate,
+                                                                    (T*)out, chunks, D, be);
+    return check_launch("combine_fwd_kernel");
+  });
 }
 
 // One CTA per (bh, query block): d_out_c = sum over ALL be rows of dout*gate (padded
@@ -706,22 +718,22 @@ __global__ void __launch_bounds__(128) combine_bwd_kernel(const T* __restrict__ 
 
 int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,
                 int64_t Lq, int D, int be, int dtype, cudaStream_t st) {
-  const int vec = dtype == VSA_F32 ? 4 : 8;
+  const int vec = elems_per_16_bytes(dtype);
   if (D % vec != 0 || D / vec > 128 || D > 256)
     return fail(VSA_ERR_UNSUPPORTED, "combine backward: head dim %d must be a multiple of %d and <= 256", D, vec);
   const long long blocks = BH * (Lq / be);
   if (blocks == 0) return VSA_OK;
   if (blocks > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "combine backward: too many blocks");
-#define VSA_LAUNCH_CB(T, G)                                                                                    \
-  combine_bwd_kernel<T, G><<<(unsigned)blocks, 128, 0, st>>>((const T*)dout, (const T*)gate, (const T*)out_c,   \
-                                                            (T*)d_out_c, (T*)dgate, D, be)
-  if (dtype == VSA_F32) {
-    if (gate) VSA_LAUNCH_CB(float, true); else VSA_LAUNCH_CB(float, false);
-  } else {
-    if (gate) VSA_LAUNCH_CB(__nv_bfloat16, true); else VSA_LAUNCH_CB(__nv_bfloat16, false);
-  }
-#undef VSA_LAUNCH_CB
-  return check_launch("combine_bwd_kernel");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    if (gate)
+      combine_bwd_kernel<T, true><<<(unsigned)blocks, 128, 0, st>>>((const T*)dout, (const T*)gate, (const T*)out_c,
+                                                                   (T*)d_out_c, (T*)dgate, D, be);
+    else
+      combine_bwd_kernel<T, false><<<(unsigned)blocks, 128, 0, st>>>((const T*)dout, (const T*)gate, (const T*)out_c,
+                                                                    (T*)d_out_c, (T*)dgate, D, be);
+    return check_launch("combine_bwd_kernel");
+  });
 }
 
 // =========================================================================================
@@ -948,14 +960,12 @@ int sparse_fwd_scalar(const void* q, const void* k, const void* v, const int32_t
   if (rc) return rc;
   if (BH == 0 || Lq == 0) return VSA_OK;
   dim3 grid((unsigned)((Lq + 7) / 8), (unsigned)BH);
-  if (dtype == VSA_F32)
-    sparse_fwd_scalar_kernel<float><<<grid, 256, 0, st>>>((const float*)q, (const float*)k, (const float*)v, selected,
-                                                          kv_sizes, (float*)out, lse2, Lq, Lkv, D, be, topk, scale);
-  else
-    sparse_fwd_scalar_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
-                                                                  (const __nv_bfloat16*)v, selected, kv_sizes,
-                                                                  (__nv_bfloat16*)out, lse2, Lq, Lkv, D, be, topk, scale);
-  return check_launch("sparse_fwd_scalar_kernel");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    sparse_fwd_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, (const T*)v, selected, kv_sizes, (T*)out,
+                                                      lse2, Lq, Lkv, D, be, topk, scale);
+    return check_launch("sparse_fwd_scalar_kernel");
+  });
 }
 
 int sparse_dq_scalar(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
@@ -966,15 +976,13 @@ int sparse_dq_scalar(const void* dout, const void* q, const void* k, const void*
   if (rc) return rc;
   if (BH == 0 || Lq == 0) return VSA_OK;
   dim3 grid((unsigned)((Lq + 7) / 8), (unsigned)BH);
-  if (dtype == VSA_F32)
-    sparse_dq_scalar_kernel<float><<<grid, 256, 0, st>>>((const float*)dout, (const float*)q, (const float*)k,
-                                                         (const float*)v, (const float*)out_s, lse2, selected, kv_sizes,
-                                                         delta, (float*)dq, Lq, Lkv, D, be, topk, scale);
-  else
-    sparse_dq_scalar_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
-        (const __nv_bfloat16*)out_s, lse2, selected, kv_sizes, delta, (__nv_bfloat16*)dq, Lq, Lkv, D, be, topk, scale);
-  return check_launch("sparse_dq_scalar_kernel");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    sparse_dq_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)dout, (const T*)q, (const T*)k, (const T*)v,
+                                                     (const T*)out_s, lse2, selected, kv_sizes, delta, (T*)dq, Lq, Lkv,
+                                                     D, be, topk, scale);
+    return check_launch("sparse_dq_scalar_kernel");
+  });
 }
 
 int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
@@ -985,15 +993,13 @@ int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const voi
   if (rc) return rc;
   if (BH == 0 || Lkv == 0) return VSA_OK;
   dim3 grid((unsigned)((Lkv + 7) / 8), (unsigned)BH);
-  if (dtype == VSA_F32)
-    sparse_dkdv_scalar_kernel<float><<<grid, 256, 0, st>>>((const float*)dout, (const float*)q, (const float*)k,
-                                                           (const float*)v, lse2, delta, counts, offsets, inverse,
-                                                           kv_sizes, (float*)dk, (float*)dv, Lq, Lkv, D, be, topk, scale);
-  else
-    sparse_dkdv_scalar_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, lse2,
-        delta, counts, offsets, inverse, kv_sizes, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, Lq, Lkv, D, be, topk, scale);
-  return check_launch("sparse_dkdv_scalar_kernel");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    sparse_dkdv_scalar_kernel<T><<<grid, 256, 0, st>>>((const T*)dout, (const T*)q, (const T*)k, (const T*)v, lse2, delta,
+                                                       counts, offsets, inverse, kv_sizes, (T*)dk, (T*)dv, Lq, Lkv, D, be,
+                                                       topk, scale);
+    return check_launch("sparse_dkdv_scalar_kernel");
+  });
 }
 
 }  // namespace vsa

@@ -57,7 +57,7 @@ constexpr int kPairHalf = 2 * kSlab;   // 128 rows x 128 bytes (one head-dim hal
 constexpr int kPairBytes = 2 * kPairHalf;
 constexpr uint32_t kTmemCols = 512;
 // K pairs in flight: a reload from L2 takes ~2000 cycles, two stages left the S^T issuer waiting for it
-constexpr int kFwdKStages = 3;
+constexpr int kFwdKStages = 2;
 constexpr int kSBufs = 4;              // S^T accumulators in flight (64 columns each); O^T sits behind them
 
 // ---- host: tensor maps ---------------------------------------------------------------------------
@@ -187,6 +187,31 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 64);
+}
+
+// 8 MMAs over the 128-wide reduction, both operands reduction-contiguous ("K-major").
+// a_pair: a stacked pair [2 halves][128 rows][128 B]; b_tile: one tile [2 halves][64 rows][128 B].
+// Descriptors are advanced with one 32-bit add each (offsets in 16-byte units are compile-time constants).
+__device__ __forceinline__ void issue_kmajor(uint32_t d_tmem, uint32_t a_pair, uint32_t b_tile) {
+  constexpr uint32_t idesc = instr_desc(128, 64, 0, 0);
+  constexpr uint32_t hi = desc_hi(1024);
+  const uint32_t a0 = desc_lo(a_pair, 16), b0 = desc_lo(b_tile, 16);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    mma_ss(d_tmem, desc_pack(a0 + (uint32_t)(((ks >> 2) * kPairHalf + (ks & 3) * 32) >> 4), hi),
+           desc_pack(b0 + (uint32_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4), hi), idesc, ks > 0 ? 1u : 0u);
+}
+// 8 MMAs over 128 rows of reduction, both operands output-contiguous ("MN-major"):
+// D[128 dims x 64] (+)= a_pair^T [128 dims x 128 rows] * b_rows [128 rows x 64].
+__device__ __forceinline__ void issue_mnmajor(uint32_t d_tmem, uint32_t a_pair, uint32_t b_rows, bool accumulate) {
+  constexpr uint32_t idesc = instr_desc(128, 64, 1, 1);
+  constexpr uint32_t hi = desc_hi(1024);
+  const uint32_t a0 = desc_lo(a_pair, kPairHalf), b0 = desc_lo(b_rows, 16);
+  const uint32_t acc0 = accumulate ? 1u : 0u;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+    mma_ss(d_tmem, desc_pack(a0 + (uint32_t)(ks * 128), hi), desc_pack(b0 + (uint32_t)(ks * 128), hi), idesc,
+           ks > 0 ? 1u : acc0);
 }
 
 // ---- forward -------------------------------------------------------------------------------------------
@@ -334,7 +359,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   } else if (warp == 2) {
     // ================= MMA issuer 1: S^T = K2 Q^T, as far ahead as operands and accumulators allow =================
     if (lane == 0) {
-      constexpr uint32_t idesc_s = instr_desc(128, 64, 0, 0);
       ok = VSA_WAIT(bar(Q_FULL), 0);
       for (int p = 0; p < n_pairs && ok; ++p) {
         const int s = p % kFwdKStages, b = p % kSBufs;
@@ -342,11 +366,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!ok) break;
         VSA_TRACE_AT(0, p);
         tc_fence_after();
-        const uint32_t ka = base + FwdSmem::k + s * kPairBytes, qbs = base + FwdSmem::q;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem_s0 + b * 64, smem_desc(ka + (ks >> 2) * kPairHalf + (ks & 3) * 32, 16, 1024),
-                 smem_desc(qbs + (ks >> 2) * kSlab + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        issue_kmajor(tmem_s0 + b * 64, base + FwdSmem::k + s * kPairBytes, base + FwdSmem::q);
         mma_commit(bar(K_EMPTY + s));
         mma_commit(bar(S_FULL + b));
         VSA_TRACE_AT(1, p);
@@ -356,7 +376,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   } else if (warp == 3) {
     // ================= MMA issuer 2: O^T += V2^T P^T =================
     if (lane == 0) {
-      constexpr uint32_t idesc_o = instr_desc(128, 64, 1, 1);
       for (int j = 0; j < n_pairs && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -366,11 +385,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!ok) break;
         VSA_TRACE_AT(3, j);
         tc_fence_after();
-        const uint32_t va = base + FwdSmem::v + s * kPairBytes, pb = base + FwdSmem::p + s * kPairHalf;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem_o, smem_desc(va + ks * 2048, kPairHalf, 1024), smem_desc(pb + ks * 2048, 16, 1024), idesc_o,
-                 (j > 0 || ks > 0) ? 1u : 0u);
+        issue_mnmajor(tmem_o, base + FwdSmem::v + s * kPairBytes, base + FwdSmem::p + s * kPairHalf, j > 0);
         mma_commit(bar(V_EMPTY + s));
         mma_commit(bar(P_EMPTY + s));
         VSA_TRACE_AT(4, j);

@@ -21,25 +21,6 @@
 // warp 2 = issuer of the score MMAs, warp 3 = issuer of the gradient MMAs, warps 4-19 = elementwise
 // (a TMEM lane quarter x 16 of the 64 columns each).
 
-// 8 MMAs over the 128-wide reduction, both operands reduction-contiguous ("K-major").
-// a_pair: a stacked pair [2 halves][128 rows][128 B]; b_tile: one tile [2 halves][64 rows][128 B].
-__device__ __forceinline__ void issue_kmajor(uint32_t d_tmem, uint32_t a_pair, uint32_t b_tile) {
-  constexpr uint32_t idesc = instr_desc(128, 64, 0, 0);
-#pragma unroll
-  for (int ks = 0; ks < 8; ++ks)
-    mma_ss(d_tmem, smem_desc(a_pair + (ks >> 2) * kPairHalf + (ks & 3) * 32, 16, 1024),
-           smem_desc(b_tile + (ks >> 2) * kSlab + (ks & 3) * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
-}
-// 8 MMAs over 128 rows of reduction, both operands output-contiguous ("MN-major"):
-// D[128 dims x 64] (+)= a_pair^T [128 dims x 128 rows] * b_rows [128 rows x 64].
-__device__ __forceinline__ void issue_mnmajor(uint32_t d_tmem, uint32_t a_pair, uint32_t b_rows, bool accumulate) {
-  constexpr uint32_t idesc = instr_desc(128, 64, 1, 1);
-#pragma unroll
-  for (int ks = 0; ks < 8; ++ks)
-    mma_ss(d_tmem, smem_desc(a_pair + ks * 2048, kPairHalf, 1024), smem_desc(b_rows + ks * 2048, 16, 1024), idesc,
-           (accumulate || ks > 0) ? 1u : 0u);
-}
-
 // The backward passes are closest to the shared-memory bandwidth limit (every operand byte is read by an
 // MMA once or twice per pair); eight wider elementwise warps disturb that pipe less than sixteen narrow ones.
 constexpr int kBwCols = 32;

@@ -68,7 +68,9 @@ def _check_device_dtype(q: Tensor, k: Tensor, v: Tensor) -> int:
         return _lib.VSA_BF16
     if q.dtype == torch.float32:
         return _lib.VSA_F32
-    raise ValueError("the B200 path supports bfloat16 and float32 (validation mode)")
+    if q.dtype == torch.float16:
+        return _lib.VSA_F16
+    raise ValueError("the B200 path supports bfloat16, float16 and float32")
 
 
 def _dense(x: Tensor) -> Tensor:
@@ -296,7 +298,7 @@ class _BlockMean(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, sizes, be):
         B, H, L, D = x.shape
-        dt = _lib.VSA_BF16 if x.dtype == torch.bfloat16 else _lib.VSA_F32
+        dt = {torch.bfloat16: _lib.VSA_BF16, torch.float32: _lib.VSA_F32, torch.float16: _lib.VSA_F16}[x.dtype]
         out = torch.empty((B, H, L // be, D), device=x.device, dtype=x.dtype)
         call("vsa_block_mean_fwd", x.data_ptr(), sizes.data_ptr(), out.data_ptr(), B * H, L, D, be, dt,
              _stream(x.device))
@@ -320,8 +322,8 @@ def block_mean(x: Tensor, variable_block_sizes: Tensor, block_elements: int) -> 
     """Padding-aware block means ``[B,H,L,D] -> [B,H,L/be,D]`` (``vsa/common.py:55-82``), differentiable."""
     if not x.is_cuda:
         raise ValueError("the B200 implementation requires CUDA tensors")
-    if x.dtype not in (torch.bfloat16, torch.float32):
-        raise ValueError("the B200 path supports bfloat16 and float32 (validation mode)")
+    if x.dtype not in (torch.bfloat16, torch.float32, torch.float16):
+        raise ValueError("the B200 path supports bfloat16, float16 and float32")
     if x.ndim != 4 or x.shape[2] % block_elements:
         raise ValueError(f"sequence length must be divisible by block_elements={block_elements}")
     with torch.cuda.device(x.device):

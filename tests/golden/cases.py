@@ -26,6 +26,8 @@ VSA_CASES = {
     "bf16_be64_ragged_gate": dict(seed=21, shape=(1, 2, 256, 128), dtype="bf16", block_size=(1, 1, 64), sizes=[64, 41, 64, 19], topk=2, gate=True, grad=True),
     # bf16, logical block 256, ragged, forward + backward
     "bf16_be256_ragged": dict(seed=23, shape=(1, 1, 768, 128), dtype="bf16", block_size=(4, 8, 8), sizes=[256, 191, 73], topk=2, gate=False, grad=True),
+    # fp16, tiny blocks of 8, head dim 64, ragged, gate: the shape of the reference's own fp16 GPU tests
+    "f16_be8_ragged_gate": dict(seed=37, shape=(1, 2, 48, 64), dtype="f16", block_size=2, sizes=[8, 5, 8, 3, 8, 8], topk=2, gate=True, grad=True),
     # fp32 with head dim 128 and a gate, for the fp32 validation mode of the kernels
     "f32_be64_gate":  dict(seed=29, shape=(1, 1, 512, 128), dtype="f32", block_size=(4, 4, 4), sizes=[64, 64, 17, 64, 1, 64, 40, 64], topk=3, gate=True, grad=True),
 }
