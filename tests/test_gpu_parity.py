@@ -452,3 +452,27 @@ def test_host_resident_step_equals_one_big_call():
     # dK/dV sum over in-edges whose order inside a CSR row is not fixed: equal up to fp32 summation order
     for n, leaf in zip(("dk", "dv"), leaves[1:]):
         torch.testing.assert_close(out[n].float(), leaf.grad.cpu().float(), atol=2e-2, rtol=2e-2)
+
+
+def test_more_tiles_than_the_tcgen05_list_holds_uses_the_warp_level_kernels():
+    """topk above 1024 tiles is outside the tcgen05 kernels' tile list: the dispatcher must fall back to the
+    warp-level kernels and stay correct (checked against dense attention with every block selected)."""
+    V = _V()
+    torch.manual_seed(53)
+    be, nb, D = 64, 1040, 128
+    q, k, v = (torch.randn(1, 1, be * nb, D, device=DEV, dtype=torch.bfloat16) for _ in range(3))
+    sizes = torch.full((nb,), be)
+    # 8 query blocks only (Lq != Lkv), each attending to all 1040 key blocks
+    ql = q[:, :, :8 * be].contiguous().requires_grad_()
+    kl, vl = k.clone().requires_grad_(), v.clone().requires_grad_()
+    every = torch.arange(nb, dtype=torch.int32, device=DEV).expand(1, 1, 8, nb).contiguous()
+    got = V.b200_sparse_attention(ql, kl, vl, every, sizes, block_size=(4, 4, 4))
+    dout = torch.randn_like(got)
+    got.backward(dout)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (ql, kl, vl))
+    want = torch.nn.functional.scaled_dot_product_attention(qr, kr, vr)
+    want.backward(dout.float())
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(ql.grad.float(), qr.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(kl.grad.float(), kr.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(vl.grad.float(), vr.grad, atol=3e-2, rtol=3e-2)
