@@ -126,6 +126,8 @@ int vsa_coarse_fwd(const void* q_mean, const void* k_mean, const void* v_mean, v
   if (rc) return rc;
   VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && D >= 1, "coarse forward: bad extents");
   VSA_REQUIRE(q_mean && k_mean && v_mean && scores && probs && out_c, "coarse forward: null pointer");
+  if (!scalar_forced() && coarse_umma_eligible(Qb, Kb, D, dtype))
+    return coarse_fwd_umma(q_mean, k_mean, v_mean, scores, probs, out_c, BH, Qb, Kb, D, scale, (cudaStream_t)stream);
   return coarse_fwd(q_mean, k_mean, v_mean, scores, probs, out_c, BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
 }
 
@@ -146,6 +148,9 @@ int vsa_coarse_bwd(const void* d_out_c, const void* out_c, const void* q_mean, c
   VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && D >= 1, "coarse backward: bad extents");
   VSA_REQUIRE(d_out_c && out_c && q_mean && k_mean && v_mean && probs && dscores_ws && rowdot_ws && dq_mean &&
                   dk_mean && dv_mean, "coarse backward: null pointer");
+  if (!scalar_forced() && coarse_umma_eligible(Qb, Kb, D, dtype))
+    return coarse_bwd_umma(d_out_c, out_c, q_mean, k_mean, v_mean, probs, dscores_ws, rowdot_ws, dq_mean, dk_mean,
+                           dv_mean, BH, Qb, Kb, D, scale, (cudaStream_t)stream);
   return coarse_bwd(d_out_c, out_c, q_mean, k_mean, v_mean, probs, dscores_ws, rowdot_ws, dq_mean, dk_mean, dv_mean,
                     BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
 }

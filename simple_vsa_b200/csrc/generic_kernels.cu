@@ -67,7 +67,20 @@ __global__ void __launch_bounds__(128) block_mean_kernel(MeanJob job, int D, int
 #pragma unroll
   for (int i = 0; i < VEC; ++i) part[i] = 0.f;
   if (rgrp < rows_per_pass) {
-    for (int r = rgrp; r < size; r += rows_per_pass) {
+    int r = rgrp;
+    for (; r + 3 * rows_per_pass < size; r += 4 * rows_per_pass) {   // four independent 16-byte loads in flight
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        raw[u] = *reinterpret_cast<const uint4*>(x + (long long)(r + u * rows_per_pass) * D + chunk * VEC);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(e + i);
+      }
+    }
+    for (; r < size; r += rows_per_pass) {
       const uint4 raw = *reinterpret_cast<const uint4*>(x + (long long)r * D + chunk * VEC);
       const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
@@ -290,6 +303,25 @@ __global__ void rowdot_kernel(const T* __restrict__ a, const T* __restrict__ b, 
   for (int d = threadIdx.x & 31; d < D; d += 32) s += Elem<T>::ld(a + r * D + d) * Elem<T>::ld(b + r * D + d);
   s = warp_sum(s);
   if ((threadIdx.x & 31) == 0) out[r] = s;
+}
+
+int softmax_rows(const void* scores, void* probs, int64_t rows, int n, int dtype, cudaStream_t st) {
+  if (rows == 0) return VSA_OK;
+  if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "pooled softmax: too many rows");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    softmax_rows_kernel<T><<<(unsigned)rows, 128, 0, st>>>((const T*)scores, (T*)probs, n);
+    return check_launch("softmax_rows_kernel");
+  });
+}
+
+int rowdot_rows(const void* a, const void* b, float* out, int64_t rows, int D, int dtype, cudaStream_t st) {
+  if (rows == 0) return VSA_OK;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    rowdot_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const T*)a, (const T*)b, out, rows, D);
+    return check_launch("rowdot_kernel");
+  });
 }
 
 template <typename T>
@@ -688,6 +720,7 @@ __global__ void __launch_bounds__(128) combine_bwd_kernel(const T* __restrict__ 
       cvec[i] = Elem<T>::ld(out_c + blk * D + chunk * VEC + i);
       part[i] = 0.f;
     }
+#pragma unroll 4
     for (int r = rgrp; r < be; r += rows_per_pass) {
       const long long off = (long long)r * D + chunk * VEC;
       const uint4 d_raw = *reinterpret_cast<const uint4*>(g_do + off);

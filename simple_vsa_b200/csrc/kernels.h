@@ -15,6 +15,8 @@ int coarse_fwd(const void* qc, const void* kc, const void* vc, void* scores, voi
 int coarse_bwd(const void* d_out_c, const void* out_c, const void* qc, const void* kc, const void* vc,
                const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb, int Kb,
                int D, float scale, int dtype, cudaStream_t st);
+int softmax_rows(const void* scores, void* probs, int64_t rows, int n, int dtype, cudaStream_t st);
+int rowdot_rows(const void* a, const void* b, float* out, int64_t rows, int D, int dtype, cudaStream_t st);
 int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int topk, int dtype, cudaStream_t st);
 int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int32_t* cursor,
                  int64_t BH, int Qb, int Kb, int topk, cudaStream_t st);
@@ -65,6 +67,12 @@ int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void*
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
                      float scale, cudaStream_t st);
+bool coarse_umma_eligible(int Qb, int Kb, int D, int dtype);
+int coarse_fwd_umma(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
+                    int Qb, int Kb, int D, float scale, cudaStream_t st);
+int coarse_bwd_umma(const void* d_out_c, const void* out_c, const void* qc, const void* kc, const void* vc,
+                    const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb,
+                    int Kb, int D, float scale, cudaStream_t st);
 int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st);
 int device_status_fetch_and_clear(int* status);
 

@@ -99,6 +99,7 @@ __device__ __forceinline__ void report_timeout(int code) { atomicCAS(&g_device_s
 // all waits of this file poll the status word so that a failure anywhere drains the grid quickly
 #define VSA_WAIT(bar_, parity_) mbar_wait((bar_), (parity_), &g_device_status)
 #define VSA_WARP_WAIT(bar_, parity_) warp_wait((bar_), (parity_), &g_device_status, lane)
+#define VSA_WARP_WAIT2(a_, pa_, b_, pb_) warp_wait2((a_), (pa_), (b_), (pb_), &g_device_status, lane)
 
 // One 64x128 tile = two boxes (head-dim halves); `dst` is the row offset inside a stacked pair.
 __device__ __forceinline__ void load_tile(uint32_t pair_base, int half_rows_off, const CUtensorMap* map, int row,
@@ -418,7 +419,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int valid = idx < n_live ? (int)tile_valid[idx] : 0;
       const bool live = r < valid;
       const int sb = p % kSBufs;
-      ok = VSA_WARP_WAIT(bar(S_FULL + sb), (p / kSBufs) & 1);
+      // the score accumulator and the free P buffer (released by the O^T MMA two pairs back) in one round trip
+      ok = VSA_WARP_WAIT2(bar(S_FULL + sb), (p / kSBufs) & 1, bar(P_EMPTY + s), ph ^ 1);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
@@ -466,8 +468,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         packed[2 * j4 + 1] = pack_bf16(p2, p3);
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
-      ok = VSA_WARP_WAIT(bar(P_EMPTY + s), ph ^ 1);
-      if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(8, p);
       uint8_t* prow = sm + FwdSmem::p + s * kPairHalf + t * 128;
 #pragma unroll
@@ -533,6 +533,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 #include "sparse_umma_bwd.inl"
+#include "coarse_umma.inl"
 
 }  // namespace
 
@@ -625,6 +626,81 @@ int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void*
                                                                 kv_sizes, (bf16*)dk, (bf16*)dv, Lq, Lkv, topk, scale);
   }
   return check_launch("sparse_dkdv_umma_kernel");
+}
+
+// ---- pooled attention on tcgen05 ---------------------------------------------------------------------------
+namespace {
+// [batch, rows, cols] bf16 row-major; boxes of 64 columns x box_rows rows of one batch slice, 128-byte swizzle.
+int make_map3d(CUtensorMap* map, const void* ptr, int64_t batch, int64_t rows, int64_t cols, int box_rows,
+               const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(VSA_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
+  if (reinterpret_cast<uintptr_t>(ptr) % 16 || (cols * 2) % 16)
+    return fail(VSA_ERR_BAD_ARGUMENT, "%s: pointer or row pitch is not 16-byte aligned", what);
+  const cuuint64_t gdim[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  const cuuint64_t gstride[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * cols * 2};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(VSA_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with code %d", what, (int)r);
+  return VSA_OK;
+}
+
+// C[batch, M, N] = A * B.  a_rows/a_cols and b_rows/b_cols describe the operands as stored in memory.
+template <int A_MN, int B_MN, int EPI>
+int launch_gemm(const void* A, int64_t a_rows, int64_t a_cols, const void* B, int64_t b_rows, int64_t b_cols, void* C,
+                int64_t batch, int M, int N, int K, float scale, const void* probs, const float* rowdot,
+                cudaStream_t st, const char* what) {
+  if (batch == 0 || M == 0 || N == 0) return VSA_OK;
+  if (batch > 65535) return fail(VSA_ERR_UNSUPPORTED, "%s: batch*heads %lld exceeds 65535", what, (long long)batch);
+  CUtensorMap ma, mb;
+  int rc;
+  if ((rc = make_map3d(&ma, A, batch, a_rows, a_cols, A_MN ? 64 : 128, what))) return rc;
+  if ((rc = make_map3d(&mb, B, batch, b_rows, b_cols, B_MN ? 64 : 128, what))) return rc;
+  const int smem = GemmSmem::total + 1024;
+  auto kern = coarse_gemm_umma_kernel<A_MN, B_MN, EPI>;
+  if ((rc = reserve_smem(kern, smem, what))) return rc;
+  dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128), (unsigned)batch);
+  kern<<<grid, 192, smem, st>>>(ma, mb, (bf16*)C, M, N, K, scale, (const bf16*)probs, rowdot);
+  return check_launch(what);
+}
+}  // namespace
+
+bool coarse_umma_eligible(int Qb, int Kb, int D, int dtype) {
+  return dtype == VSA_BF16 && D == 128 && Qb % 8 == 0 && Kb % 8 == 0;
+}
+
+int coarse_fwd_umma(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
+                    int Qb, int Kb, int D, float scale, cudaStream_t st) {
+  int rc = launch_gemm<0, 0, kEpiScores>(qc, Qb, D, kc, Kb, D, scores, BH, Qb, Kb, D, scale, nullptr, nullptr, st,
+                                         "pooled scores");
+  if (rc) return rc;
+  if ((rc = softmax_rows(scores, probs, BH * Qb, Kb, VSA_BF16, st))) return rc;
+  return launch_gemm<0, 1, kEpiStore>(probs, Qb, Kb, vc, Kb, D, out_c, BH, Qb, D, Kb, 1.f, nullptr, nullptr, st,
+                                      "pooled output");
+}
+
+int coarse_bwd_umma(const void* d_out_c, const void* out_c, const void* qc, const void* kc, const void* vc,
+                    const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb,
+                    int Kb, int D, float scale, cudaStream_t st) {
+  int rc = rowdot_rows(d_out_c, out_c, rowdot, BH * Qb, D, VSA_BF16, st);
+  if (rc) return rc;
+  // dV_c[Kb,D] = P^T dO_c : A = P stored [Qb rows (reduction), Kb cols (M)], B = dO_c stored [Qb rows, D cols]
+  if ((rc = launch_gemm<1, 1, kEpiStore>(probs, Qb, Kb, d_out_c, Qb, D, dvc, BH, Kb, D, Qb, 1.f, nullptr, nullptr, st,
+                                         "pooled dV")))
+    return rc;
+  // dS[Qb,Kb] = P * (dO_c v_c^T - rowdot) * scale
+  if ((rc = launch_gemm<0, 0, kEpiSoftmaxBwd>(d_out_c, Qb, D, vc, Kb, D, ds, BH, Qb, Kb, D, scale, probs, rowdot, st,
+                                              "pooled dS")))
+    return rc;
+  // dQ_c[Qb,D] = dS k_c
+  if ((rc = launch_gemm<0, 1, kEpiStore>(ds, Qb, Kb, kc, Kb, D, dqc, BH, Qb, D, Kb, 1.f, nullptr, nullptr, st,
+                                         "pooled dQ")))
+    return rc;
+  // dK_c[Kb,D] = dS^T q_c
+  return launch_gemm<1, 1, kEpiStore>(ds, Qb, Kb, qc, Qb, D, dkc, BH, Kb, D, Qb, 1.f, nullptr, nullptr, st, "pooled dK");
 }
 
 int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st) {

@@ -514,7 +514,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           dl_n = delta[row];
         }
       }
-      ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
+      // the score accumulators and the free P/dS buffers (released by the gradient MMAs two pairs back) together
+      ok = VSA_WARP_WAIT2(bar(DK_S_FULL + b), (p / kDkBufs) & 1, bar(DK_PDS_EMPTY + s), ph ^ 1);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
@@ -538,8 +539,6 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         pg[j2] = pack_bf16(g0, g1);
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
-      ok = VSA_WARP_WAIT(bar(DK_PDS_EMPTY + s), ph ^ 1);
-      if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(8, p);
       uint8_t* prow = sm + DkSmem::p + s * kPairHalf + t * 128;
       uint8_t* grow = sm + DkSmem::ds + s * kPairHalf + t * 128;

@@ -63,14 +63,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const v
     else if (now - t0 > kWaitLimitNs) return false;
   }
 }
-// Whole-warp wait: lane 0 polls (one try first: the common case is a barrier that has already flipped),
-// the result and the acquired data are shared through the warp shuffle / barrier.
+// Whole-warp wait: lane 0 polls (one try first: the common case is a barrier that has already flipped);
+// the warp barrier orders the acquired data for the other lanes, the vote shares the result.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag, int lane) {
   int ok = 1;
   if (lane == 0) {
     if (!mbar_try_wait(bar, parity)) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
   }
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  __syncwarp();
+  return __all_sync(0xffffffffu, ok) != 0;
+}
+// Two barriers at once: lane 0 polls the first, lane 1 the second, in the same instruction stream, so the
+// pair costs one shared-memory round trip instead of two back to back (each is ~180 cycles even when the
+// barrier has long flipped, and the elementwise warps pay it once per pair of tiles).
+__device__ __forceinline__ bool warp_wait2(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b,
+                                           const volatile int* abort_flag, int lane) {
+  int ok = 1;
+  if (lane < 2) {
+    const uint32_t bar = lane == 0 ? bar_a : bar_b;
+    const uint32_t parity = lane == 0 ? parity_a : parity_b;
+    if (!mbar_try_wait(bar, parity)) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  }
+  __syncwarp();
+  return __all_sync(0xffffffffu, ok) != 0;
 }
 
 // ---- fences ----------------------------------------------------------------------------------

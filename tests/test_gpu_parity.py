@@ -476,3 +476,46 @@ def test_more_tiles_than_the_tcgen05_list_holds_uses_the_warp_level_kernels():
     torch.testing.assert_close(ql.grad.float(), qr.grad, atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(kl.grad.float(), kr.grad, atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(vl.grad.float(), vr.grad, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("Qb,Kb", [(200, 136), (8, 8), (264, 1448)])
+def test_pooled_attention_tensor_core_path_matches_scalar_path(Qb, Kb, monkeypatch):
+    """The tcgen05 pooled GEMMs (ragged M/N/K edges filled by TMA) against the CUDA-core GEMMs and torch."""
+    from simple_vsa_b200 import _lib
+    torch.manual_seed(55)
+    BH, D = 3, 128
+    scale = D ** -0.5
+    qc, kc, vc, dco = (torch.randn(n, device=DEV).to(torch.bfloat16) for n in
+                       ((BH, Qb, D), (BH, Kb, D), (BH, Kb, D), (BH, Qb, D)))
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        scores = torch.empty(BH, Qb, Kb, device=DEV, dtype=torch.bfloat16)
+        probs, ds = torch.empty_like(scores), torch.empty_like(scores)
+        out_c = torch.empty(BH, Qb, D, device=DEV, dtype=torch.bfloat16)
+        _lib.call("vsa_coarse_fwd", qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), scores.data_ptr(), probs.data_ptr(),
+                  out_c.data_ptr(), BH, Qb, Kb, D, scale, 0, st)
+        rowdot = torch.empty(BH, Qb, device=DEV)
+        dq, dk, dv = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+        _lib.call("vsa_coarse_bwd", dco.data_ptr(), out_c.data_ptr(), qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                  probs.data_ptr(), ds.data_ptr(), rowdot.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                  BH, Qb, Kb, D, scale, 0, st)
+        torch.cuda.synchronize()
+        return scores, probs, out_c, dq, dk, dv
+
+    fast = run()
+    monkeypatch.setenv("VSA_B200_KERNELS", "scalar")
+    slow = run()
+    # scores: identical roundings, fp32 sums in a different order -> at most one bf16 unit apart
+    assert (fast[0].float() - slow[0].float()).abs().max() <= 2 ** -7 * slow[0].float().abs().max()
+    for a, b in zip(fast[1:], slow[1:]):
+        torch.testing.assert_close(a.float(), b.float(), atol=2e-2, rtol=2e-2)
+    # and against torch on the same roundings
+    want_scores = (torch.matmul(qc.float(), kc.float().transpose(-2, -1)).to(torch.bfloat16).float() * scale)
+    assert (fast[0].float() - want_scores).abs().max() <= 2 ** -6 * want_scores.abs().max()
+    ql, kl, vl = (t.float().requires_grad_() for t in (qc, kc, vc))
+    ref = torch.softmax(torch.matmul(ql, kl.transpose(-2, -1)) * scale, -1) @ vl
+    ref.backward(dco.float())
+    torch.testing.assert_close(fast[2].float(), ref, atol=2e-2, rtol=2e-2)
+    for got, leaf in zip(fast[3:], (ql, kl, vl)):
+        torch.testing.assert_close(got.float(), leaf.grad, atol=3e-2, rtol=3e-2)
