@@ -41,6 +41,8 @@ WORKLOADS = {
     # name: (B, H, L, D, block_size, topk, gate, ragged)
     "c5_92k_be64_tk180": dict(B=2, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False),
     "c2_16k_be64_tk32_gate": dict(B=1, H=12, L=16384, D=128, block_size=(4, 4, 4), topk=32, gate=True),
+    # one tenth of the headline slices, with a gate: the profiling case (2.8 GB on the device, tensors > L2)
+    "mid_92k_h8_tk180_gate": dict(B=1, H=8, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=True),
     "small_8k_be64_tk16": dict(B=1, H=8, L=8192, D=128, block_size=(4, 4, 4), topk=16, gate=False),
     # logical 256 blocks, 10 % of them ragged (sizes uniform in [1,255], padded rows zeroed)
     "c3_40k_be256_tk20_ragged": dict(B=1, H=40, L=40960, D=128, block_size=(4, 8, 8), topk=20, gate=False,
