@@ -43,7 +43,7 @@ struct MeanJob {
 template <typename T>
 __global__ void __launch_bounds__(128) block_mean_kernel(MeanJob job, int D, int be) {
   constexpr int VEC = 16 / sizeof(T);
-  __shared__ float acc_sm[256];
+  __shared__ __align__(16) float part_sm[128 * VEC];     // [row group][D] partial sums
   const long long cta = blockIdx.x;
   int t = 0;
   if (cta >= job.first_cta[1]) t = 1;
@@ -55,9 +55,6 @@ __global__ void __launch_bounds__(128) block_mean_kernel(MeanJob job, int D, int
   T* out = reinterpret_cast<T*>(job.out[t]) + local * (long long)D;
   int size = job.sizes[t][blk];
   size = size < 0 ? 0 : (size > be ? be : size);
-
-  for (int d = threadIdx.x; d < D; d += blockDim.x) acc_sm[d] = 0.f;
-  __syncthreads();
 
   const int cpr = D / VEC;                     // 16-byte chunks per row
   const int rows_per_pass = blockDim.x / cpr;
@@ -86,12 +83,17 @@ __global__ void __launch_bounds__(128) block_mean_kernel(MeanJob job, int D, int
 #pragma unroll
       for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(e + i);
     }
+    float* dst = part_sm + rgrp * D + chunk * VEC;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) atomicAdd(&acc_sm[chunk * VEC + i], part[i]);
+    for (int i = 0; i < VEC; ++i) dst[i] = part[i];
   }
   __syncthreads();
   const float denom = (float)(size > 1 ? size : 1);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) Elem<T>::st(out + d, acc_sm[d] / denom);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float sum = 0.f;
+    for (int g = 0; g < rows_per_pass; ++g) sum += part_sm[g * D + d];     // fixed order: deterministic
+    Elem<T>::st(out + d, sum / denom);
+  }
 }
 
 template <typename T>
@@ -702,13 +704,11 @@ __global__ void __launch_bounds__(128) combine_bwd_kernel(const T* __restrict__ 
                                                           const T* __restrict__ out_c, T* __restrict__ d_out_c,
                                                           T* __restrict__ dgate, int D, int be) {
   constexpr int VEC = 16 / sizeof(T);
-  __shared__ float acc_sm[256];
+  __shared__ __align__(16) float part_sm[128 * VEC];     // [row group][D] partial sums
   const long long blk = blockIdx.x;
   const T* g_do = dout + blk * (long long)be * D;
   const T* g_gate = GATE ? gate + blk * (long long)be * D : nullptr;
   T* g_dgate = (GATE && dgate) ? dgate + blk * (long long)be * D : nullptr;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) acc_sm[d] = 0.f;
-  __syncthreads();
   const int cpr = D / VEC;
   const int rows_per_pass = blockDim.x / cpr;
   const int chunk = threadIdx.x % cpr;
@@ -742,11 +742,16 @@ __global__ void __launch_bounds__(128) combine_bwd_kernel(const T* __restrict__ 
         for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(de + i);
       }
     }
+    float* dst = part_sm + rgrp * D + chunk * VEC;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) atomicAdd(&acc_sm[chunk * VEC + i], part[i]);
+    for (int i = 0; i < VEC; ++i) dst[i] = part[i];
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < D; d += blockDim.x) Elem<T>::st(d_out_c + blk * D + d, acc_sm[d]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float sum = 0.f;
+    for (int g = 0; g < rows_per_pass; ++g) sum += part_sm[g * D + d];     // fixed order: deterministic
+    Elem<T>::st(d_out_c + blk * D + d, sum);
+  }
 }
 
 int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,
