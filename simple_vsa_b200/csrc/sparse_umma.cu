@@ -9,19 +9,21 @@
 // K2/V2 are two 64-token tiles stacked in shared memory by four TMA boxes each.  In tensor
 // memory a lane is then a key token and a column a query row, so the softmax statistics run
 // ACROSS lanes.  They are handled without per-tile cross-lane traffic:
-//   * the shift m[q] is the exact column maximum of the FIRST live pair only (one cross-lane
-//     reduction per CTA); softmax is shift-invariant, so any later score simply gives
-//     P = 2^(s-m) > 1, which bf16 and fp32 hold up to 2^127;
+//   * the shift m is ONE value per query tile: the largest score of the first live pair (one
+//     cross-lane reduction per CTA).  Softmax is shift-invariant, so any other score simply gives
+//     P = 2^(s-m) somewhere in the range of fp32/bf16 (2^-126 .. 2^127); a scalar shift lives in a
+//     register, where per-row shifts cost every thread sixteen shared-memory reads per pair on the
+//     pipe that also feeds the tensor core its operands (measured: the busiest unit of this kernel);
 //   * every thread keeps its own partial row sums (64 registers) and they are reduced across
 //     lanes once at the end;
-//   * if a sum or an output leaves the finite range (scores more than ~2^7 apart in log2
-//     units from the first pair's maximum) the tile writes NaN into its log-sum-exp rows and
+//   * if a sum or an output leaves the finite range, or a row underflows to a zero sum (scores more
+//     than ~2^7 apart in log2 units from the shift), the tile writes NaN into its log-sum-exp rows and
 //     the exact warp-level kernel recomputes just those tiles in a follow-up launch.
 // P^T is written by its owner thread as one swizzled 128-byte row of shared memory (N-major B
 // operand), so no transposition is ever needed.
 //
 // Roles: warp 0 = K producer, warp 1 = V producer (four lanes, one TMA box each; warp 1 also owns the
-// tensor memory), warp 2 = issuer of the S^T MMAs, warp 3 = issuer of the O^T MMAs, warps 4-19 = softmax (a TMEM lane quarter and half of the
+// tensor memory), warp 2 = issuer of the S^T MMAs, warp 3 = issuer of the O^T MMAs, warps 4-19 = softmax (a TMEM lane quarter and sixteen of the
 // query-row columns each).  Every mbarrier wait is bounded; on a time-out the CTA records an error code in a
 // device status word, stops issuing work, frees its tensor memory and returns.
 #include <cuda.h>
@@ -36,10 +38,15 @@ namespace vsa {
 
 __device__ int g_device_status = 0;
 
-// Optional timeline of CTA (0,0), compiled in only with -DVSA_TRACE (a development aid).
+// Optional timeline of the CTA in the middle of the grid, compiled in only with -DVSA_TRACE (a development
+// aid).  Slots 0-13 hold clock64, slots 14/15 the global nanosecond timer at the points of slots 0/9, which
+// gives the SM clock the kernel really ran at.
 #ifdef VSA_TRACE
 __device__ long long g_trace[16 * 128];
-#define VSA_TRACE_AT(slot, p) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (p) < 128) g_trace[(slot) * 128 + (p)] = clock64(); } while (0)
+#define VSA_TRACE_AT(slot, p) do { if (blockIdx.x == gridDim.x / 2 && blockIdx.y == gridDim.y / 2 && (p) < 128) { \
+    g_trace[(slot) * 128 + (p)] = clock64(); \
+    if ((slot) == 0) g_trace[14 * 128 + (p)] = (long long)umma::global_ns(); \
+    if ((slot) == 9) g_trace[15 * 128 + (p)] = (long long)umma::global_ns(); } } while (0)
 #else
 #define VSA_TRACE_AT(slot, p) do { } while (0)
 #endif
@@ -58,6 +65,7 @@ constexpr int kPairBytes = 2 * kPairHalf;
 constexpr uint32_t kTmemCols = 512;
 // K pairs in flight: a reload from L2 takes ~2000 cycles, two stages left the S^T issuer waiting for it
 constexpr int kFwdKStages = 2;
+constexpr int kPBufs = 2;              // P^T buffers in shared memory (16 KB each); four measured no faster
 constexpr int kSBufs = 4;              // S^T accumulators in flight (64 columns each); O^T sits behind them
 
 // ---- host: tensor maps ---------------------------------------------------------------------------
@@ -221,11 +229,10 @@ struct FwdSmem {
   static constexpr uint32_t k = q + 2 * kSlab;                   // 2 stages x 32 KB
   static constexpr uint32_t v = k + kFwdKStages * kPairBytes;    // 2 stages x 32 KB (K above: 3 stages)
   static constexpr uint32_t p = v + 2 * kPairBytes;              // 2 buffers x 16 KB
-  static constexpr uint32_t tile_row = p + 2 * kPairHalf;        // int32 [kMaxTiles]
+  static constexpr uint32_t tile_row = p + kPBufs * kPairHalf;        // int32 [kMaxTiles]
   static constexpr uint32_t tile_valid = tile_row + 4 * kMaxTiles;   // uint8 [kMaxTiles]
   static constexpr uint32_t m_warp = tile_valid + kMaxTiles;     // float [4 lane quarters][64]
-  static constexpr uint32_t m_col = m_warp + 4 * 64 * 4;         // float [64]
-  static constexpr uint32_t l_col = m_col + 64 * 4;              // float [64]
+  static constexpr uint32_t l_col = m_warp + 4 * 64 * 4;         // float [64]
   static constexpr uint32_t bars = l_col + 64 * 4;               // 8-byte mbarriers
   static constexpr uint32_t misc = bars + 32 * 8;                // tmem base, n_live, flags
   static constexpr uint32_t total = misc + 64;
@@ -234,8 +241,8 @@ constexpr int kEwCols = 16;          // columns of a TMEM tile one elementwise t
 constexpr int kEwWarps = 4 * (64 / kEwCols);   // lane quarters x column groups = 16 warps
 constexpr int kEwThreads = 32 * kEwWarps;
 constexpr int kFwdThreads = 128 + kEwThreads;   // K producer, V producer, two MMA issuers, elementwise warps
-enum FwdBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, P_FULL = 11, P_EMPTY = 13, O_FULL = 15,
-              S_FULL = 16, S_EMPTY = 16 + kSBufs };
+enum FwdBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, P_FULL = 11, P_EMPTY = 15, O_FULL = 19,
+              S_FULL = 20, S_EMPTY = 20 + kSBufs };
 
 template <int SUB>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -271,6 +278,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(V_FULL + i), 4);
       mbar_init(bar(V_EMPTY + i), 1);
+    }
+    for (int i = 0; i < kPBufs; ++i) {
       mbar_init(bar(P_FULL + i), kEwWarps);      // one elected lane per softmax warp
       mbar_init(bar(P_EMPTY + i), 1);
     }
@@ -359,40 +368,41 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else if (warp == 2) {
     // ================= MMA issuer 1: S^T = K2 Q^T, as far ahead as operands and accumulators allow =================
-    if (lane == 0) {
-      ok = VSA_WAIT(bar(Q_FULL), 0);
-      for (int p = 0; p < n_pairs && ok; ++p) {
-        const int s = p % kFwdKStages, b = p % kSBufs;
-        ok = VSA_WAIT(bar(K_FULL + s), (p / kFwdKStages) & 1) && VSA_WAIT(bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
-        if (!ok) break;
-        VSA_TRACE_AT(0, p);
-        tc_fence_after();
+    ok = VSA_WARP_WAIT(bar(Q_FULL), 0);
+    for (int p = 0; p < n_pairs && ok; ++p) {
+      const int s = p % kFwdKStages, b = p % kSBufs;
+      ok = VSA_WARP_WAIT2(bar(K_FULL + s), (p / kFwdKStages) & 1, bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
+      if (!ok) break;
+      if (lane == 0) VSA_TRACE_AT(0, p);
+      tc_fence_after();
+      if (elect_one()) {
         issue_kmajor(tmem_s0 + b * 64, base + FwdSmem::k + s * kPairBytes, base + FwdSmem::q);
         mma_commit(bar(K_EMPTY + s));
         mma_commit(bar(S_FULL + b));
-        VSA_TRACE_AT(1, p);
       }
-      if (!ok) report_timeout(2);
+      __syncwarp();
+      if (lane == 0) VSA_TRACE_AT(1, p);
     }
+    if (!ok && lane == 0) report_timeout(2);
   } else if (warp == 3) {
     // ================= MMA issuer 2: O^T += V2^T P^T =================
-    if (lane == 0) {
-      for (int j = 0; j < n_pairs && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        ok = VSA_WAIT(bar(V_FULL + s), ph);
-        VSA_TRACE_AT(2, j);
-        ok = ok && VSA_WAIT(bar(P_FULL + s), ph);
-        if (!ok) break;
-        VSA_TRACE_AT(3, j);
-        tc_fence_after();
-        issue_mnmajor(tmem_o, base + FwdSmem::v + s * kPairBytes, base + FwdSmem::p + s * kPairHalf, j > 0);
+    for (int j = 0; j < n_pairs && ok; ++j) {
+      const int s = j & 1, pb = j % kPBufs;
+      ok = VSA_WARP_WAIT2(bar(V_FULL + s), (j >> 1) & 1, bar(P_FULL + pb), (j / kPBufs) & 1);
+      if (!ok) break;
+      if (lane == 0) VSA_TRACE_AT(3, j);
+      tc_fence_after();
+      if (elect_one()) {
+        issue_mnmajor(tmem_o, base + FwdSmem::v + s * kPairBytes, base + FwdSmem::p + pb * kPairHalf, j > 0);
         mma_commit(bar(V_EMPTY + s));
-        mma_commit(bar(P_EMPTY + s));
-        VSA_TRACE_AT(4, j);
+        mma_commit(bar(P_EMPTY + pb));
       }
+      __syncwarp();
+      if (lane == 0) VSA_TRACE_AT(4, j);
+    }
+    if (elect_one()) {
       if (ok) mma_commit(bar(O_FULL));
-      if (!ok) report_timeout(5);
+      else report_timeout(5);
     }
   } else if (warp >= 4) {
     // ================= softmax warps =================
@@ -406,7 +416,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int st = tid - 128;                     // index among the softmax threads
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     float* m_warp = reinterpret_cast<float*>(sm + FwdSmem::m_warp);
-    float* m_col = reinterpret_cast<float*>(sm + FwdSmem::m_col);
+    float m_shift = 0.f;
     float* l_col = reinterpret_cast<float*>(sm + FwdSmem::l_col);
     float lsum[kEwCols];
 #pragma unroll
@@ -420,7 +430,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool live = r < valid;
       const int sb = p % kSBufs;
       // the score accumulator and the free P buffer (released by the O^T MMA two pairs back) in one round trip
-      ok = VSA_WARP_WAIT2(bar(S_FULL + sb), (p / kSBufs) & 1, bar(P_EMPTY + s), ph ^ 1);
+      const int pb = p % kPBufs;
+      ok = VSA_WARP_WAIT2(bar(S_FULL + sb), (p / kSBufs) & 1, bar(P_EMPTY + pb), ((p / kPBufs) & 1) ^ 1);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
@@ -432,15 +443,18 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0) mbar_arrive(bar(S_EMPTY + sb));
       if (tid == 128) VSA_TRACE_AT(6, p);
 
-      if (p == 0) {   // exact column maxima of the first live pair: warp shuffle, then across the lane quarters
+      if (p == 0) {   // the shift: the largest score of the first live pair, one value for the whole tile
+        float x = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < kEwCols; ++j) {
-          const float x = warp_max(live ? __uint_as_float(sv[j]) * c : -INFINITY);
-          if (lane == 0) m_warp[quarter * 64 + c0 + j] = x;
-        }
+        for (int j = 0; j < kEwCols; ++j) x = fmaxf(x, live ? __uint_as_float(sv[j]) * c : -INFINITY);
+        x = warp_max(x);
+        if (lane == 0) m_warp[warp - 4] = x;
         named_barrier(1, kEwThreads);
-        if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st]));
-        named_barrier(1, kEwThreads);
+        x = m_warp[0];
+#pragma unroll
+        for (int i = 1; i < kEwWarps; ++i) x = fmaxf(x, m_warp[i]);
+        m_shift = x;
+        named_barrier(1, kEwThreads);     // m_warp is reused for the row sums at the end
       }
       // padding rows of a ragged tile (and the repeated tile of an odd tail): whatever sits in V there
       // must not reach the tensor core, where 0 * NaN would poison the sum
@@ -456,27 +470,31 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ok = __all_sync(0xffffffffu, ok);     // keep the warp's control flow uniform
       if (!ok) break;
       uint32_t packed[kEwCols / 2];
+      if (live) {
 #pragma unroll
-      for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
-        const float4 m4 = *reinterpret_cast<const float4*>(m_col + c0 + 4 * j4);
-        const float p0 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m4.x)) : 0.f;
-        const float p1 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m4.y)) : 0.f;
-        const float p2 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m4.z)) : 0.f;
-        const float p3 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m4.w)) : 0.f;
-        lsum[4 * j4 + 0] += p0; lsum[4 * j4 + 1] += p1; lsum[4 * j4 + 2] += p2; lsum[4 * j4 + 3] += p3;
-        packed[2 * j4] = pack_bf16(p0, p1);
-        packed[2 * j4 + 1] = pack_bf16(p2, p3);
+        for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m_shift));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m_shift));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m_shift));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m_shift));
+          lsum[4 * j4 + 0] += p0; lsum[4 * j4 + 1] += p1; lsum[4 * j4 + 2] += p2; lsum[4 * j4 + 3] += p3;
+          packed[2 * j4] = pack_bf16(p0, p1);
+          packed[2 * j4 + 1] = pack_bf16(p2, p3);
+        }
+      } else {   // a padding key row contributes nothing
+#pragma unroll
+        for (int j = 0; j < kEwCols / 2; ++j) packed[j] = 0u;
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
       if (tid == 128) VSA_TRACE_AT(8, p);
-      uint8_t* prow = sm + FwdSmem::p + s * kPairHalf + t * 128;
+      uint8_t* prow = sm + FwdSmem::p + pb * kPairHalf + t * 128;
 #pragma unroll
       for (int ch = 0; ch < kEwCols / 8; ++ch)     // this thread's query rows are 16-byte chunks of row t
         *reinterpret_cast<uint4*>(prow + ((((kEwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
             make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_FULL + s));
+      if (lane == 0) mbar_arrive(bar(P_FULL + pb));
       if (tid == 128) VSA_TRACE_AT(9, p);
     }
     if (!ok) report_timeout(3);
@@ -524,7 +542,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     if (st < 64) {
       const float l = l_col[st];
-      lse2[bh * Lq + (long long)qtile * kTile + st] = (redo || n_pairs == 0) ? NAN : m_col[st] + log2f(l);
+      lse2[bh * Lq + (long long)qtile * kTile + st] = (redo || n_pairs == 0) ? NAN : m_shift + log2f(l);
     }
   }
   tc_fence_before();

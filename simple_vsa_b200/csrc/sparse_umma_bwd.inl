@@ -134,7 +134,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (part == 0) {
       s_delta[row] = acc;
       delta[qrow0 + row] = acc;
-      s_lse[row] = lse2[qrow0 + row];
+      s_lse[row] = lse2[qrow0 + row] - log2f(scale);   // 2^(s c - lse) * scale in one exponential
     }
   }
   __syncthreads();
@@ -280,12 +280,12 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const float p1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -l4.y));
         const float p2 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -l4.z));
         const float p3 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -l4.w));
-        const float g0 = live ? p0 * (__uint_as_float(dv[4 * j4 + 0]) - d4.x) * scale : 0.f;
-        const float g1 = live ? p1 * (__uint_as_float(dv[4 * j4 + 1]) - d4.y) * scale : 0.f;
-        const float g2 = live ? p2 * (__uint_as_float(dv[4 * j4 + 2]) - d4.z) * scale : 0.f;
-        const float g3 = live ? p3 * (__uint_as_float(dv[4 * j4 + 3]) - d4.w) * scale : 0.f;
-        packed[2 * j4] = pack_bf16(g0, g1);
-        packed[2 * j4 + 1] = pack_bf16(g2, g3);
+        packed[2 * j4] = pack_bf16(p0 * (__uint_as_float(dv[4 * j4 + 0]) - d4.x), p1 * (__uint_as_float(dv[4 * j4 + 1]) - d4.y));
+        packed[2 * j4 + 1] = pack_bf16(p2 * (__uint_as_float(dv[4 * j4 + 2]) - d4.z), p3 * (__uint_as_float(dv[4 * j4 + 3]) - d4.w));
+      }
+      if (!live) {   // a padding key row: its scores come from whatever sits in K and V there
+#pragma unroll
+        for (int j = 0; j < kBwCols / 2; ++j) packed[j] = 0u;
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
       ok = VSA_WARP_WAIT(bar(DQ_DS_EMPTY), (p & 1) ^ 1);
@@ -333,19 +333,28 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // dK / dV
 // ------------------------------------------------------------------------------------------------------
 constexpr int kDkBufs = 2;     // (S, dP) accumulator pairs in flight: 2 x 128 columns, then dK^T and dV^T
+// A Q2 pair stays in shared memory from its score MMA (the first of a pair) to its dK MMA (the last), across the
+// whole elementwise stage, and a reload takes ~1500 cycles on top.  dO2 is needed 8 MMAs later (dP follows S) and
+// released 8 MMAs earlier (dV precedes dK), so it keeps two stages and Q2 gets three; P and dS pay for it with one
+// buffer each (written by pair p+1 only after the gradient MMAs of pair p have read them, which the elementwise
+// warps check right before their stores, after all their arithmetic).  Measured 2 % faster than 2 + 2 stages with
+// double-buffered P/dS: the kernel stays bound by the residency of the dO2 stages (reload + 16 MMAs + the elementwise stage + 8 MMAs,
+// per two pairs).
+constexpr int kDkQStages = 3;
+constexpr int kDkPdsBufs = 1;
 struct DkSmem {
   static constexpr uint32_t k = 0;                                // 16 KB
   static constexpr uint32_t v = k + 2 * kSlab;                    // 16 KB
-  static constexpr uint32_t q = v + 2 * kSlab;                    // 2 x 32 KB  (pairs of query tiles)
-  static constexpr uint32_t d_o = q + 2 * kPairBytes;             // 2 x 32 KB
-  static constexpr uint32_t p = d_o + 2 * kPairBytes;             // 2 x 16 KB
-  static constexpr uint32_t ds = p + 2 * kPairHalf;               // 2 x 16 KB
-  static constexpr uint32_t bars = ds + 2 * kPairHalf;
+  static constexpr uint32_t q = v + 2 * kSlab;                    // kDkQStages x 32 KB  (pairs of query tiles)
+  static constexpr uint32_t d_o = q + kDkQStages * kPairBytes;    // 2 x 32 KB
+  static constexpr uint32_t p = d_o + 2 * kPairBytes;             // kDkPdsBufs x 16 KB
+  static constexpr uint32_t ds = p + kDkPdsBufs * kPairHalf;      // kDkPdsBufs x 16 KB
+  static constexpr uint32_t bars = ds + kDkPdsBufs * kPairHalf;
   static constexpr uint32_t misc = bars + 32 * 8;
   static constexpr uint32_t total = misc + 64;
 };
-enum DkBar { DK_KV_FULL = 0, DK_Q_FULL = 1, DK_DO_FULL = 3, DK_Q_EMPTY = 5, DK_DO_EMPTY = 7, DK_PDS_FULL = 9,
-             DK_PDS_EMPTY = 11, DK_ACC_FULL = 13, DK_S_FULL = 14, DK_S_EMPTY = 14 + kDkBufs };
+enum DkBar { DK_KV_FULL = 0, DK_Q_FULL = 1, DK_DO_FULL = 4, DK_Q_EMPTY = 6, DK_DO_EMPTY = 9, DK_PDS_FULL = 11,
+             DK_PDS_EMPTY = 13, DK_ACC_FULL = 15, DK_S_FULL = 16, DK_S_EMPTY = 16 + kDkBufs };
 
 template <int SUB>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -391,11 +400,15 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   if (tid == 0) {
     mbar_init(bar(DK_KV_FULL), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kDkQStages; ++i) {
       mbar_init(bar(DK_Q_FULL + i), 4);
-      mbar_init(bar(DK_DO_FULL + i), 4);
       mbar_init(bar(DK_Q_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(DK_DO_FULL + i), 4);
       mbar_init(bar(DK_DO_EMPTY + i), 1);
+    }
+    for (int i = 0; i < kDkPdsBufs; ++i) {
       mbar_init(bar(DK_PDS_FULL + i), kBwWarps);
       mbar_init(bar(DK_PDS_EMPTY + i), 1);
     }
@@ -432,9 +445,10 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const CUtensorMap* map = is_q ? &map_q : &map_do;
     const int full0 = is_q ? DK_Q_FULL : DK_DO_FULL, empty0 = is_q ? DK_Q_EMPTY : DK_DO_EMPTY;
     const uint32_t ring = base + (is_q ? DkSmem::q : DkSmem::d_o);
+    const int depth = is_q ? kDkQStages : 2;
     for (int p = 0; p < n_pairs; ++p) {
-      const int s = p & 1;
-      const uint32_t ph = (p >> 1) & 1;
+      const int s = p % depth;
+      const uint32_t ph = (p / depth) & 1;
       int idx = 2 * p + which;
       if (idx >= n_tiles) idx = 2 * p;                  // odd tail: repeat the tile (its rows are masked)
       const int row = (int)(q_row_base + tile_row(idx));
@@ -450,14 +464,14 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (lane == 0) {   // scores: S = Q2 K^T and dP = dO2 V^T
       ok = VSA_WAIT(bar(DK_KV_FULL), 0);
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int s = p & 1, b = p % kDkBufs;
+        const int qs = p % kDkQStages, s = p & 1, b = p % kDkBufs;
         const uint32_t ph = (p >> 1) & 1;
-        ok = VSA_WAIT(bar(DK_Q_FULL + s), ph) && VSA_WAIT(bar(DK_DO_FULL + s), ph) &&
+        ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) && VSA_WAIT(bar(DK_DO_FULL + s), ph) &&
              VSA_WAIT(bar(DK_S_EMPTY + b), ((p / kDkBufs) & 1) ^ 1);
         if (!ok) break;
         VSA_TRACE_AT(0, p);
         tc_fence_after();
-        issue_kmajor(tmem + b * 128, base + DkSmem::q + s * kPairBytes, base + DkSmem::k);
+        issue_kmajor(tmem + b * 128, base + DkSmem::q + qs * kPairBytes, base + DkSmem::k);
         issue_kmajor(tmem + b * 128 + 64, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::v);
         mma_commit(bar(DK_S_FULL + b));
         VSA_TRACE_AT(1, p);
@@ -467,17 +481,18 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   } else if (warp == 3) {
     if (lane == 0) {   // dV^T += dO2^T P and dK^T += Q2^T dS
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int s = p & 1;
+        const int qs = p % kDkQStages, s = p & 1, pb = p % kDkPdsBufs;
         const uint32_t ph = (p >> 1) & 1;
-        ok = VSA_WAIT(bar(DK_Q_FULL + s), ph) && VSA_WAIT(bar(DK_DO_FULL + s), ph) && VSA_WAIT(bar(DK_PDS_FULL + s), ph);
+        ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) && VSA_WAIT(bar(DK_DO_FULL + s), ph) &&
+             VSA_WAIT(bar(DK_PDS_FULL + pb), (p / kDkPdsBufs) & 1);
         if (!ok) break;
         VSA_TRACE_AT(3, p);
         tc_fence_after();
-        issue_mnmajor(tmem_dv, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::p + s * kPairHalf, p > 0);
+        issue_mnmajor(tmem_dv, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::p + pb * kPairHalf, p > 0);
         mma_commit(bar(DK_DO_EMPTY + s));
-        issue_mnmajor(tmem_dk, base + DkSmem::q + s * kPairBytes, base + DkSmem::ds + s * kPairHalf, p > 0);
-        mma_commit(bar(DK_Q_EMPTY + s));
-        mma_commit(bar(DK_PDS_EMPTY + s));
+        issue_mnmajor(tmem_dk, base + DkSmem::q + qs * kPairBytes, base + DkSmem::ds + pb * kPairHalf, p > 0);
+        mma_commit(bar(DK_Q_EMPTY + qs));
+        mma_commit(bar(DK_PDS_EMPTY + pb));
         VSA_TRACE_AT(4, p);
       }
       if (ok) mma_commit(bar(DK_ACC_FULL));
@@ -492,30 +507,29 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int half = t >> 6, r = t & 63;
     const int st = tid - 128;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    // statistics of this lane's query row, fetched one pair ahead of their use
-    float lse_n = 0.f, dl_n = 0.f;
-    bool live_n = half < n_tiles;
-    if (live_n) {
+    const bool ragged = valid < kTile;      // same for the whole CTA: key columns >= valid are padding
+    // statistics of this lane's query row, fetched one pair ahead of their use.  A row that does not exist (the
+    // repeated tile of an odd tail) gets lse = +inf, i.e. P = 0 exactly, and delta = 0, so dS = 0 * finite = 0.
+    float lse_n = INFINITY, dl_n = 0.f;
+    if (half < n_tiles) {
       const long long row = q_row_base + tile_row(half) + r;
       lse_n = lse2[row];
       dl_n = delta[row];
     }
     for (int p = 0; p < n_pairs && ok; ++p) {
-      const int s = p & 1, b = p % kDkBufs;
-      const uint32_t ph = (p >> 1) & 1;
+      const int b = p % kDkBufs, pb = p % kDkPdsBufs;
       const float lse = lse_n, dl = dl_n;
-      const bool live = live_n;
       {
         const int nidx = 2 * (p + 1) + half;
-        live_n = nidx < n_tiles;
-        if (live_n) {
+        lse_n = INFINITY;
+        dl_n = 0.f;
+        if (nidx < n_tiles) {
           const long long row = q_row_base + tile_row(nidx) + r;
           lse_n = lse2[row];
           dl_n = delta[row];
         }
       }
-      // the score accumulators and the free P/dS buffers (released by the gradient MMAs two pairs back) together
-      ok = VSA_WARP_WAIT2(bar(DK_S_FULL + b), (p / kDkBufs) & 1, bar(DK_PDS_EMPTY + s), ph ^ 1);
+      ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
@@ -528,20 +542,33 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (lane == 0) mbar_arrive(bar(DK_S_EMPTY + b));
       if (tid == 128) VSA_TRACE_AT(6, p);
       uint32_t pp[kBwCols / 2], pg[kBwCols / 2];
+      if (!ragged) {
 #pragma unroll
-      for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
-        const bool k0 = live && (c0 + 2 * j2) < valid, k1 = live && (c0 + 2 * j2 + 1) < valid;
-        const float p0 = k0 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse)) : 0.f;
-        const float p1 = k1 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse)) : 0.f;
-        const float g0 = k0 ? p0 * (__uint_as_float(dvv[2 * j2]) - dl) : 0.f;
-        const float g1 = k1 ? p1 * (__uint_as_float(dvv[2 * j2 + 1]) - dl) : 0.f;
-        pp[j2] = pack_bf16(p0, p1);
-        pg[j2] = pack_bf16(g0, g1);
+        for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse));
+          pp[j2] = pack_bf16(p0, p1);
+          pg[j2] = pack_bf16(p0 * (__uint_as_float(dvv[2 * j2]) - dl), p1 * (__uint_as_float(dvv[2 * j2 + 1]) - dl));
+        }
+      } else {   // scores of a padding column come from whatever sits in K and V there: select, do not multiply
+#pragma unroll
+        for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
+          const bool k0 = (c0 + 2 * j2) < valid, k1 = (c0 + 2 * j2 + 1) < valid;
+          const float p0 = k0 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse)) : 0.f;
+          const float p1 = k1 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse)) : 0.f;
+          const float g0 = k0 ? p0 * (__uint_as_float(dvv[2 * j2]) - dl) : 0.f;
+          const float g1 = k1 ? p1 * (__uint_as_float(dvv[2 * j2 + 1]) - dl) : 0.f;
+          pp[j2] = pack_bf16(p0, p1);
+          pg[j2] = pack_bf16(g0, g1);
+        }
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
+      // the P/dS buffers are free once the gradient MMAs that read them (kDkPdsBufs pairs back) have completed
+      ok = VSA_WARP_WAIT(bar(DK_PDS_EMPTY + pb), ((p / kDkPdsBufs) & 1) ^ 1);
+      if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(8, p);
-      uint8_t* prow = sm + DkSmem::p + s * kPairHalf + t * 128;
-      uint8_t* grow = sm + DkSmem::ds + s * kPairHalf + t * 128;
+      uint8_t* prow = sm + DkSmem::p + pb * kPairHalf + t * 128;
+      uint8_t* grow = sm + DkSmem::ds + pb * kPairHalf + t * 128;
 #pragma unroll
       for (int ch = 0; ch < kBwCols / 8; ++ch) {
         const uint32_t off = (uint32_t)((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4);
@@ -550,7 +577,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(DK_PDS_FULL + s));
+      if (lane == 0) mbar_arrive(bar(DK_PDS_FULL + pb));
       if (tid == 128) VSA_TRACE_AT(9, p);
     }
     if (!ok && lane == 0) report_timeout(24);
