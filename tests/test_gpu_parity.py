@@ -90,6 +90,27 @@ def test_forward_fixed_shift_out_of_range_is_recomputed_exactly():
     _assert_close(lse, want_lse, atol=5e-2, rtol=1e-3)
 
 
+@pytest.mark.parametrize("factor", [30.0, 300.0])
+def test_forward_one_shift_per_query_tile_keeps_every_row_exact(factor):
+    """The tcgen05 forward subtracts ONE value (the largest score of the first pair) from all 64 rows of a
+    query tile.  One row with scores `factor` times larger drags that value up: at 30x the other rows live
+    ~100 binades lower and must keep their relative precision; at 300x they underflow to a zero sum, which
+    must send the tile to the exact kernel.  Either way every row matches the oracle."""
+    torch.manual_seed(62)
+    be, nb, D, tk = 64, 8, 128, 4
+    q, k, v = (torch.randn(1, 2, be * nb, D).to(torch.bfloat16) for _ in range(3))
+    q[:, :, 3::be] *= factor                 # row 3 of every query tile
+    sizes = torch.full((nb,), be)
+    selected = torch.stack([torch.randperm(nb)[:tk] for _ in range(2 * nb)]).to(torch.int32).view(1, 2, nb, tk)
+    want, want_lse = O.sparse_attention(q, k, v, selected, sizes, be, return_lse2=True)
+    from simple_vsa_b200 import ops
+    out, lse = ops.sparse_forward(q.to(DEV), k.to(DEV), v.to(DEV), selected.to(DEV), sizes.to(DEV, torch.int32),
+                                  be, 1.0 / math.sqrt(D), True)
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    _assert_close(out, want, atol=2e-2, rtol=2e-2)
+    _assert_close(lse, want_lse, atol=5e-2, rtol=1e-3)
+
+
 # ---------------------------------------------------------------------------------------------
 # bandwidth kernels
 # ---------------------------------------------------------------------------------------------
