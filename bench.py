@@ -1,6 +1,6 @@
 """Benchmark of the VSA forward+backward hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference|reference_triton] [--workload NAME]
 
 One "step" is one forward+backward of the whole operator over this rank's share of
 the workload.  The default workload is the 92,160-token / block-64 / topk-180 shape
@@ -20,6 +20,8 @@ during the timed region.
 
 ``--impl reference`` times the CPU restatement of the reference algorithm (the
 oracle) on the host cores on a bounded sample of the same workload.
+``--impl reference_triton`` (extra, optional) times the unmodified reference package's own
+Triton kernels on the GPU when ``baseline/_ref`` holds an installed copy.
 """
 
 from __future__ import annotations
@@ -436,12 +438,100 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+def run_reference_gpu(args, cfg, rank: int, world: int, local_rank: int):
+    """``--impl reference_triton``: the UNMODIFIED reference package (installed by ``__graft_entry__.build()``
+    into ``baseline/_ref``, never part of this repository's sources) running its own Triton kernels through its
+    own public API on the same GPU, same workload, same synthetic slices, CUDA events.  An extra comparison
+    point beside the required CPU reference arm; prints an ``unavailable`` line when the package or Triton
+    cannot be imported."""
+    def unavailable(why):
+        if rank == 0:
+            print(json.dumps({"impl": "reference_triton", "unavailable": why}), flush=True)
+
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "vsa")):
+        return unavailable("baseline/_ref is not installed (run __graft_entry__.build() where the reference is present)")
+    if cfg.get("sp"):
+        return unavailable("the reference has no sequence-parallel mode")
+    sys.path.insert(0, ref_dir)
+    try:
+        import torch
+        import torch.distributed as dist
+        from vsa import triton_sparse_attention, triton_vsa
+    except Exception as exc:        # noqa: BLE001 - any import problem is reported, not raised
+        return unavailable(f"import failed: {type(exc).__name__}: {exc}"[:200])
+    from oracle.vsa_oracle import block_elements
+
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    be = block_elements(cfg["block_size"])
+    L, D, tk = cfg["L"], cfg["D"], cfg["topk"]
+    total = cfg["B"] * cfg["H"]
+    per, extra = divmod(total, world)
+    count, first = per + (1 if rank < extra else 0), rank * per + min(rank, extra)
+    nb = L // be
+    data = make_slices(cfg, first, count, dev)
+    sizes = torch.full((nb,), be, dtype=torch.int64, device=dev)
+    if cfg.get("ragged_frac") or cfg.get("routes"):
+        return unavailable("ragged / explicit-route workloads are timed for this package only")
+    q, k, v = (data[n].requires_grad_() for n in ("q", "k", "v"))
+    gate, dout = data.get("gate"), data["dout"]
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        out = triton_vsa(q, k, v, sizes, sizes, tk, cfg["block_size"], gate)
+        out.backward(dout)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, args.warmup)):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    flops_total = useful_flops(total, L, tk, be, D)
+    print(json.dumps({
+        "metric": "VSA fwd+bwd useful TFLOPS, 92k tok blk64 bf16" if args.workload == DEFAULT_WORKLOAD
+                  else f"VSA fwd+bwd useful TFLOPS ({args.workload})",
+        "value": flops_total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic N(0,1), seeded per (batch,head) slice", "impl": "reference_triton",
+        "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], L, D], "block_elements": be,
+                   "topk": tk, "gate": cfg["gate"], "slices_per_gpu": count},
+        "e2e": None, "gpu_launches": None, "clocks": clocks,
+        "checksum": float(out[0, 0, :64].float().abs().sum())}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_triton"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-steps", type=int, default=3)
@@ -474,6 +564,8 @@ def main():
         print(json.dumps(line), flush=True)
         return
 
+    if args.impl == "reference_triton" and (args.gpus == 1 or world > 1):
+        return run_reference_gpu(args, cfg, rank, world, local_rank)
     if args.gpus > 1 and world == 1:
         # launched plainly with --gpus N: re-launch under torchrun, one rank per GPU
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

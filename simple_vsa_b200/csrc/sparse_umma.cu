@@ -9,15 +9,16 @@
 // K2/V2 are two 64-token tiles stacked in shared memory by four TMA boxes each.  In tensor
 // memory a lane is then a key token and a column a query row, so the softmax statistics run
 // ACROSS lanes.  They are handled without per-tile cross-lane traffic:
-//   * the shift m is ONE value per query tile: the largest score of the first live pair (one
-//     cross-lane reduction per CTA).  Softmax is shift-invariant, so any other score simply gives
-//     P = 2^(s-m) somewhere in the range of fp32/bf16 (2^-126 .. 2^127); a scalar shift lives in a
-//     register, where per-row shifts cost every thread sixteen shared-memory reads per pair on the
-//     pipe that also feeds the tensor core its operands (measured: the busiest unit of this kernel);
+//   * the shift m[q] is the exact column maximum of the FIRST live pair only (one cross-lane
+//     reduction per CTA); softmax is shift-invariant, so any later score simply gives
+//     P = 2^(s-m) > 1, which bf16 and fp32 hold up to 2^127.  (One shift for the whole tile would
+//     live in a register and spare sixteen shared-memory reads per thread and pair, measured 1 %
+//     faster, but rows ~100 binades below the tile's largest score then lose precision silently:
+//     products near 2^-126 are flushed.  Per-row shifts keep every row's largest term at 1.)
 //   * every thread keeps its own partial row sums (64 registers) and they are reduced across
 //     lanes once at the end;
-//   * if a sum or an output leaves the finite range, or a row underflows to a zero sum (scores more
-//     than ~2^7 apart in log2 units from the shift), the tile writes NaN into its log-sum-exp rows and
+//   * if a sum or an output leaves the finite range (scores more than ~2^7 apart in log2
+//     units from the first pair's maximum of that row) the tile writes NaN into its log-sum-exp rows and
 //     the exact warp-level kernel recomputes just those tiles in a follow-up launch.
 // P^T is written by its owner thread as one swizzled 128-byte row of shared memory (N-major B
 // operand), so no transposition is ever needed.
@@ -232,7 +233,8 @@ struct FwdSmem {
   static constexpr uint32_t tile_row = p + kPBufs * kPairHalf;        // int32 [kMaxTiles]
   static constexpr uint32_t tile_valid = tile_row + 4 * kMaxTiles;   // uint8 [kMaxTiles]
   static constexpr uint32_t m_warp = tile_valid + kMaxTiles;     // float [4 lane quarters][64]
-  static constexpr uint32_t l_col = m_warp + 4 * 64 * 4;         // float [64]
+  static constexpr uint32_t m_col = m_warp + 4 * 64 * 4;         // float [64]
+  static constexpr uint32_t l_col = m_col + 64 * 4;              // float [64]
   static constexpr uint32_t bars = l_col + 64 * 4;               // 8-byte mbarriers
   static constexpr uint32_t misc = bars + 32 * 8;                // tmem base, n_live, flags
   static constexpr uint32_t total = misc + 64;
@@ -416,7 +418,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int st = tid - 128;                     // index among the softmax threads
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     float* m_warp = reinterpret_cast<float*>(sm + FwdSmem::m_warp);
-    float m_shift = 0.f;
+    float* m_col = reinterpret_cast<float*>(sm + FwdSmem::m_col);
     float* l_col = reinterpret_cast<float*>(sm + FwdSmem::l_col);
     float lsum[kEwCols];
 #pragma unroll
@@ -443,18 +445,15 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0) mbar_arrive(bar(S_EMPTY + sb));
       if (tid == 128) VSA_TRACE_AT(6, p);
 
-      if (p == 0) {   // the shift: the largest score of the first live pair, one value for the whole tile
-        float x = -INFINITY;
+      if (p == 0) {   // exact column maxima of the first live pair: warp shuffle, then across the lane quarters
 #pragma unroll
-        for (int j = 0; j < kEwCols; ++j) x = fmaxf(x, live ? __uint_as_float(sv[j]) * c : -INFINITY);
-        x = warp_max(x);
-        if (lane == 0) m_warp[warp - 4] = x;
+        for (int j = 0; j < kEwCols; ++j) {
+          const float x = warp_max(live ? __uint_as_float(sv[j]) * c : -INFINITY);
+          if (lane == 0) m_warp[quarter * 64 + c0 + j] = x;
+        }
         named_barrier(1, kEwThreads);
-        x = m_warp[0];
-#pragma unroll
-        for (int i = 1; i < kEwWarps; ++i) x = fmaxf(x, m_warp[i]);
-        m_shift = x;
-        named_barrier(1, kEwThreads);     // m_warp is reused for the row sums at the end
+        if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st]));
+        named_barrier(1, kEwThreads);
       }
       // padding rows of a ragged tile (and the repeated tile of an odd tail): whatever sits in V there
       // must not reach the tensor core, where 0 * NaN would poison the sum
@@ -473,10 +472,11 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (live) {
 #pragma unroll
         for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m_shift));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m_shift));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m_shift));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m_shift));
+          const float4 m4 = *reinterpret_cast<const float4*>(m_col + c0 + 4 * j4);
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m4.x));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m4.y));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m4.z));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m4.w));
           lsum[4 * j4 + 0] += p0; lsum[4 * j4 + 1] += p1; lsum[4 * j4 + 2] += p2; lsum[4 * j4 + 3] += p3;
           packed[2 * j4] = pack_bf16(p0, p1);
           packed[2 * j4 + 1] = pack_bf16(p2, p3);
@@ -542,7 +542,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     if (st < 64) {
       const float l = l_col[st];
-      lse2[bh * Lq + (long long)qtile * kTile + st] = (redo || n_pairs == 0) ? NAN : m_shift + log2f(l);
+      lse2[bh * Lq + (long long)qtile * kTile + st] = (redo || n_pairs == 0) ? NAN : m_col[st] + log2f(l);
     }
   }
   tc_fence_before();

@@ -91,11 +91,10 @@ def test_forward_fixed_shift_out_of_range_is_recomputed_exactly():
 
 
 @pytest.mark.parametrize("factor", [30.0, 300.0])
-def test_forward_one_shift_per_query_tile_keeps_every_row_exact(factor):
-    """The tcgen05 forward subtracts ONE value (the largest score of the first pair) from all 64 rows of a
-    query tile.  One row with scores `factor` times larger drags that value up: at 30x the other rows live
-    ~100 binades lower and must keep their relative precision; at 300x they underflow to a zero sum, which
-    must send the tile to the exact kernel.  Either way every row matches the oracle."""
+def test_forward_rows_of_very_different_scale_in_one_query_tile(factor):
+    """One row of every 64-row query tile has scores `factor` times larger than its neighbours (~100 and
+    ~1000 binades): the softmax shift of the tcgen05 forward must be per row, or the small rows lose their
+    precision (or their sum) to the large one.  Every row matches the oracle."""
     torch.manual_seed(62)
     be, nb, D, tk = 64, 8, 128, 4
     q, k, v = (torch.randn(1, 2, be * nb, D).to(torch.bfloat16) for _ in range(3))
