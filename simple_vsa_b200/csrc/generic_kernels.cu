@@ -8,6 +8,7 @@
 // fp32 accumulation, base-2 log-sum-exp, masks from the per-block sizes.
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 
@@ -389,9 +390,9 @@ int coarse_bwd(const void* d_out_c, const void* out_c, const void* qc, const voi
 }
 
 // =========================================================================================
-// Top-K by radix select (vsa/torch_impl.py:85 of the reference): one CTA per score row.
-// The k-th largest key is found in four 8-bit passes; every id with a larger key, plus
-// the lowest-numbered ids equal to it, are written in ascending id order.
+// Top-K by radix select (vsa/torch_impl.py:85 of the reference).  Every id with a key above the
+// k-th largest, plus the lowest-numbered ids equal to it, are written in ascending id order.
+// Long rows (> 3072 scores): one CTA per row, keys in shared memory, four 8-bit histogram passes.
 // =========================================================================================
 constexpr int kTopkThreads = 256;
 constexpr int kTopkMaxCols = 8192;
@@ -496,6 +497,63 @@ __global__ void __launch_bounds__(kTopkThreads) topk_kernel(const T* __restrict_
   }
 }
 
+// Rows of up to 3072 scores: one WARP per row, the keys in registers (lane l holds ids l, l+32, ...), no shared
+// memory and no block-wide barrier.  The k-th largest key is built bit by bit from the top ("is the number of
+// keys >= candidate still >= k?": a compare-and-count over the registers and one redux.sync per bit); 16-bit
+// inputs need 16 bits only, because the low bits of their keys carry no information once masked.  Then one pass
+// over the registers in id order writes every id above the threshold and the lowest ids equal to it.
+template <typename T> struct KeyBits { static constexpr int low = 0; };
+template <> struct KeyBits<__nv_bfloat16> { static constexpr int low = 16; };
+template <> struct KeyBits<__half> { static constexpr int low = 13; };
+
+template <typename T, int SLOTS>
+__global__ void __launch_bounds__(256) topk_warp_kernel(const T* __restrict__ scores, int32_t* __restrict__ selected,
+                                                        long long rows, int n, int topk) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* s = scores + row * n;
+  int32_t* out = selected + row * topk;
+  constexpr int kLow = KeyBits<T>::low;
+  constexpr uint32_t kMask = kLow ? ~((1u << kLow) - 1u) : 0xffffffffu;
+  uint32_t key[SLOTS];
+#pragma unroll
+  for (int j = 0; j < SLOTS; ++j) {
+    const int i = j * 32 + lane;
+    key[j] = i < n ? (order_key(Elem<T>::ld(s + i)) & kMask) : 0u;     // 0 sorts below every candidate
+  }
+  uint32_t thr = 0;
+#pragma unroll 1
+  for (int b = 31; b >= kLow; --b) {
+    const uint32_t t = thr | (1u << b);
+    int cnt = 0;
+#pragma unroll
+    for (int j = 0; j < SLOTS; ++j) cnt += key[j] >= t ? 1 : 0;
+    cnt = __reduce_add_sync(0xffffffffu, cnt);
+    if (cnt >= topk) thr = t;
+  }
+  int above = 0;
+#pragma unroll
+  for (int j = 0; j < SLOTS; ++j) above += key[j] > thr ? 1 : 0;
+  above = __reduce_add_sync(0xffffffffu, above);
+  const int take_eq = topk - above;            // ids equal to the threshold that are kept (lowest first)
+  const unsigned lt = (1u << lane) - 1u;
+  int written = 0, eq_seen = 0;
+#pragma unroll
+  for (int j = 0; j < SLOTS; ++j) {
+    const int i = j * 32 + lane;
+    const bool gt = key[j] > thr;
+    const bool eq = key[j] == thr && i < n;
+    const unsigned eq_b = __ballot_sync(0xffffffffu, eq);
+    const bool take = gt || (eq && eq_seen + __popc(eq_b & lt) < take_eq);
+    const unsigned tk_b = __ballot_sync(0xffffffffu, take);
+    const int pos = written + __popc(tk_b & lt);
+    if (take && pos < topk) out[pos] = i;
+    eq_seen += __popc(eq_b);
+    written += __popc(tk_b);
+  }
+}
+
 int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int topk, int dtype, cudaStream_t st) {
   if (rows == 0) return VSA_OK;
   if (Kb > kTopkMaxCols) return fail(VSA_ERR_UNSUPPORTED, "topk: %d key blocks exceed the supported %d", Kb, kTopkMaxCols);
@@ -503,6 +561,19 @@ int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int
   const size_t smem = (size_t)Kb * sizeof(uint32_t);
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = VSA_TAG_TYPE(tag);
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+    if (Kb <= 512) {
+      topk_warp_kernel<T, 16><<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
+      return check_launch("topk_warp_kernel");
+    }
+    if (Kb <= 1536) {
+      topk_warp_kernel<T, 48><<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
+      return check_launch("topk_warp_kernel");
+    }
+    if (Kb <= 3072) {
+      topk_warp_kernel<T, 96><<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
+      return check_launch("topk_warp_kernel");
+    }
     topk_kernel<T><<<(unsigned)rows, kTopkThreads, smem, st>>>((const T*)scores, selected, Kb, topk);
     return check_launch("topk_kernel");
   });
@@ -565,6 +636,67 @@ __global__ void route_scatter_kernel(const int32_t* __restrict__ selected, int32
   inverse[bh * edges_per_bh + slot] = within / topk;
 }
 
+// Chunked forms of the two passes for key-block counts that fit in shared memory: a CTA owns a contiguous chunk
+// of one slice's edges, histograms it in shared memory, and touches global memory with ONE atomic per key block
+// it met (the plain forms above pay one global atomic per edge: 20.7 M at the 92k-token shape, now 1.8 M).
+// In the scatter pass the global atomic claims a run of slots for the CTA's edges of that key block; positions
+// inside the run come from a second shared-memory counter.  Order inside a key row stays unspecified.
+constexpr int kRouteChunkThreads = 512;
+constexpr int kRouteMaxSmemKb = 6144;        // 2 x int32 [Kb] <= 48 KB
+
+__global__ void __launch_bounds__(kRouteChunkThreads)
+route_count_chunk_kernel(const int32_t* __restrict__ selected, int32_t* __restrict__ counts, int edges_per_bh,
+                         int chunk, int Kb) {
+  extern __shared__ int32_t route_sm[];
+  int32_t* hist = route_sm;
+  const long long bh = blockIdx.y;
+  const int e0 = blockIdx.x * chunk, e1 = min(edges_per_bh, e0 + chunk);
+  const int32_t* sel = selected + bh * edges_per_bh;
+  for (int i = threadIdx.x; i < Kb; i += kRouteChunkThreads) hist[i] = 0;
+  __syncthreads();
+  for (int e = e0 + threadIdx.x; e < e1; e += kRouteChunkThreads) {
+    const int kv = sel[e];
+    if ((unsigned)kv < (unsigned)Kb) atomicAdd(&hist[kv], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < Kb; i += kRouteChunkThreads) {
+    const int c = hist[i];
+    if (c) atomicAdd(&counts[bh * Kb + i], c);
+  }
+}
+
+__global__ void __launch_bounds__(kRouteChunkThreads)
+route_scatter_chunk_kernel(const int32_t* __restrict__ selected, int32_t* __restrict__ cursor,
+                           int32_t* __restrict__ inverse, int edges_per_bh, int chunk, int Kb, int topk) {
+  extern __shared__ int32_t route_sm[];
+  int32_t* hist = route_sm;            // count of this chunk per key block, then the first claimed slot
+  int32_t* next = route_sm + Kb;       // slots handed out so far inside the claimed run
+  const long long bh = blockIdx.y;
+  const int e0 = blockIdx.x * chunk, e1 = min(edges_per_bh, e0 + chunk);
+  const int32_t* sel = selected + bh * edges_per_bh;
+  for (int i = threadIdx.x; i < Kb; i += kRouteChunkThreads) {
+    hist[i] = 0;
+    next[i] = 0;
+  }
+  __syncthreads();
+  for (int e = e0 + threadIdx.x; e < e1; e += kRouteChunkThreads) {
+    const int kv = sel[e];
+    if ((unsigned)kv < (unsigned)Kb) atomicAdd(&hist[kv], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < Kb; i += kRouteChunkThreads) {
+    const int c = hist[i];
+    if (c) hist[i] = atomicAdd(&cursor[bh * Kb + i], c);
+  }
+  __syncthreads();
+  int32_t* inv = inverse + bh * edges_per_bh;
+  for (int e = e0 + threadIdx.x; e < e1; e += kRouteChunkThreads) {
+    const int kv = sel[e];
+    if ((unsigned)kv >= (unsigned)Kb) continue;
+    inv[hist[kv] + atomicAdd(&next[kv], 1)] = e / topk;
+  }
+}
+
 int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int32_t* cursor,
                  int64_t BH, int Qb, int Kb, int topk, cudaStream_t st) {
   const long long per = (long long)Qb * topk;
@@ -573,19 +705,36 @@ int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int
   if (per > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "route inversion: too many edges per slice");
   if (cudaMemsetAsync(counts, 0, sizeof(int32_t) * BH * Kb, st) != cudaSuccess)
     return fail(VSA_ERR_LAUNCH, "route inversion: memset failed: %s", cudaGetErrorString(cudaGetLastError()));
+  const bool chunked = Kb <= kRouteMaxSmemKb && BH <= 65535;
+  // chunks of >= 8192 edges, at most 64 per slice: enough CTAs to fill the GPU, few enough global atomics
+  const int chunks = (int)std::max<long long>(1, std::min<long long>(64, per / 8192));
+  const int chunk = (int)((per + chunks - 1) / chunks);
+  const dim3 grid((unsigned)chunks, (unsigned)BH);
+  int rc = VSA_OK;
   if (total > 0) {
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    route_count_kernel<<<blocks, 256, 0, st>>>(selected, counts, total, (int)per, Kb);
-    int rc = check_launch("route_count_kernel");
+    if (chunked) {
+      route_count_chunk_kernel<<<grid, kRouteChunkThreads, sizeof(int32_t) * Kb, st>>>(selected, counts, (int)per, chunk, Kb);
+      rc = check_launch("route_count_chunk_kernel");
+    } else {
+      const unsigned blocks = (unsigned)((total + 255) / 256);
+      route_count_kernel<<<blocks, 256, 0, st>>>(selected, counts, total, (int)per, Kb);
+      rc = check_launch("route_count_kernel");
+    }
     if (rc) return rc;
   }
   route_scan_kernel<<<(unsigned)BH, 256, 0, st>>>(counts, offsets, cursor, Kb);
-  int rc = check_launch("route_scan_kernel");
+  rc = check_launch("route_scan_kernel");
   if (rc) return rc;
   if (total > 0) {
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    route_scatter_kernel<<<blocks, 256, 0, st>>>(selected, cursor, inverse, total, (int)per, Kb, topk);
-    rc = check_launch("route_scatter_kernel");
+    if (chunked) {
+      route_scatter_chunk_kernel<<<grid, kRouteChunkThreads, 2 * sizeof(int32_t) * Kb, st>>>(selected, cursor, inverse,
+                                                                                            (int)per, chunk, Kb, topk);
+      rc = check_launch("route_scatter_chunk_kernel");
+    } else {
+      const unsigned blocks = (unsigned)((total + 255) / 256);
+      route_scatter_kernel<<<blocks, 256, 0, st>>>(selected, cursor, inverse, total, (int)per, Kb, topk);
+      rc = check_launch("route_scatter_kernel");
+    }
   }
   return rc;
 }
