@@ -97,6 +97,69 @@ __global__ void __launch_bounds__(128) block_mean_kernel(MeanJob job, int D, int
   }
 }
 
+// Warp-per-block form for rows of at most 32 sixteen-byte chunks (every head dim the tensor path serves):
+// lane = (row parity group, chunk), eight independent loads in flight per lane, partial sums combined by
+// shuffles in a fixed order.  No shared memory and no block barrier, so a CTA of four warps is four
+// independent streams; the CTA-per-block kernel above spent a quarter of its time outside its loads.
+template <typename T>
+__global__ void __launch_bounds__(128) block_mean_warp_kernel(MeanJob job, int D, int be, long long total) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= total) return;
+  int t = 0;
+  if (unit >= job.first_cta[1]) t = 1;
+  if (unit >= job.first_cta[2]) t = 2;
+  // (picked with selects: indexing the parameter struct with a run-time index would copy it to the stack)
+  const long long first = t == 0 ? job.first_cta[0] : (t == 1 ? job.first_cta[1] : job.first_cta[2]);
+  const int nb = t == 0 ? job.nb[0] : (t == 1 ? job.nb[1] : job.nb[2]);
+  const void* xin = t == 0 ? job.x[0] : (t == 1 ? job.x[1] : job.x[2]);
+  void* xout = t == 0 ? job.out[0] : (t == 1 ? job.out[1] : job.out[2]);
+  const int32_t* sz = t == 0 ? job.sizes[0] : (t == 1 ? job.sizes[1] : job.sizes[2]);
+  const long long local = unit - first;
+  const int blk = (int)(local % nb);
+  const T* x = reinterpret_cast<const T*>(xin) + local * (long long)be * D;
+  T* out = reinterpret_cast<T*>(xout) + local * (long long)D;
+  int size = sz[blk];
+  size = size < 0 ? 0 : (size > be ? be : size);
+  const int cpr = D / VEC, rpl = 32 / cpr;       // chunks per row, rows per warp-wide load
+  const int chunk = lane % cpr, rsub = lane / cpr;
+  const T* px = x + chunk * VEC;
+  float part[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) part[i] = 0.f;
+  int r = rsub;
+  for (; r + 7 * rpl < size; r += 8 * rpl) {
+    uint4 raw[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const uint4*>(px + (long long)(r + u * rpl) * D);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(e + i);
+    }
+  }
+  for (; r < size; r += rpl) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(px + (long long)r * D);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(e + i);
+  }
+  for (int o = cpr; o < 32; o <<= 1) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) part[i] += __shfl_xor_sync(0xffffffffu, part[i], o);
+  }
+  if (rsub == 0) {
+    const float denom = (float)(size > 1 ? size : 1);
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) Elem<T>::st(e + i, part[i] / denom);
+    *reinterpret_cast<uint4*>(out + chunk * VEC) = raw;
+  }
+}
+
 template <typename T>
 static int launch_block_mean(MeanJob job, int ntensors, int64_t BH, int D, int be, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(T);
@@ -111,6 +174,11 @@ static int launch_block_mean(MeanJob job, int ntensors, int64_t BH, int D, int b
   for (int t = ntensors; t < 3; ++t) job.first_cta[t] = total + 1;  // never matched
   if (total == 0) return VSA_OK;
   if (total > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "block mean: too many blocks");
+  const int cpr = D / VEC;
+  if (cpr <= 32 && 32 % cpr == 0) {
+    block_mean_warp_kernel<T><<<(unsigned)((total + 3) / 4), 128, 0, st>>>(job, D, be, total);
+    return check_launch("block_mean_warp_kernel");
+  }
   block_mean_kernel<T><<<(unsigned)total, 128, 0, st>>>(job, D, be);
   return check_launch("block_mean_kernel");
 }
@@ -297,6 +365,55 @@ __global__ void __launch_bounds__(128) softmax_rows_kernel(const T* __restrict__
   for (int i = threadIdx.x; i < n; i += blockDim.x) Elem<T>::st(p + i, expf(Elem<T>::ld(s + i) - mx) * inv);
 }
 
+// The same for rows of up to 3072 scores: one warp per row, the row in registers (read once, one expf per
+// element), reductions by shuffles only.  Same arithmetic as above: fp32 max, expf, fp32 sum, one rounding.
+template <typename T, int SLOTS>
+__global__ void __launch_bounds__(256) softmax_rows_warp_kernel(const T* __restrict__ scores, T* __restrict__ probs,
+                                                                long long rows, int n) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* s = scores + row * n;
+  T* p = probs + row * n;
+  float x[SLOTS];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < SLOTS; ++j) {
+    const int i = j * 32 + lane;
+    x[j] = i < n ? Elem<T>::ld(s + i) : -INFINITY;
+    mx = fmaxf(mx, x[j]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < SLOTS; ++j) {
+    x[j] = expf(x[j] - mx);          // exp(-inf) = 0 for the slots beyond the row
+    sum += x[j];
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int j = 0; j < SLOTS; ++j) {
+    const int i = j * 32 + lane;
+    if (i < n) Elem<T>::st(p + i, x[j] * inv);
+  }
+}
+
+template <typename T>
+static int launch_softmax_rows(const T* scores, T* probs, long long rows, int n, cudaStream_t st) {
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (n <= 512) {
+    softmax_rows_warp_kernel<T, 16><<<grid, 256, 0, st>>>(scores, probs, rows, n);
+  } else if (n <= 1536) {
+    softmax_rows_warp_kernel<T, 48><<<grid, 256, 0, st>>>(scores, probs, rows, n);
+  } else if (n <= 3072) {
+    softmax_rows_warp_kernel<T, 96><<<grid, 256, 0, st>>>(scores, probs, rows, n);
+  } else {
+    softmax_rows_kernel<T><<<(unsigned)rows, 128, 0, st>>>(scores, probs, n);
+  }
+  return check_launch("softmax_rows_kernel");
+}
+
 // rowdot[r] = sum_d a[r,d] * b[r,d]  (one warp per row)
 template <typename T>
 __global__ void rowdot_kernel(const T* __restrict__ a, const T* __restrict__ b, float* __restrict__ out, long long rows, int D) {
@@ -313,8 +430,7 @@ int softmax_rows(const void* scores, void* probs, int64_t rows, int n, int dtype
   if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "pooled softmax: too many rows");
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = VSA_TAG_TYPE(tag);
-    softmax_rows_kernel<T><<<(unsigned)rows, 128, 0, st>>>((const T*)scores, (T*)probs, n);
-    return check_launch("softmax_rows_kernel");
+    return launch_softmax_rows<T>((const T*)scores, (T*)probs, rows, n, st);
   });
 }
 
@@ -336,8 +452,7 @@ static int coarse_fwd_t(const T* qc, const T* kc, const T* vc, T* scores, T* pro
   if (rc) return rc;
   const long long rows = BH * Qb;
   if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "coarse softmax: too many rows");
-  softmax_rows_kernel<T><<<(unsigned)rows, 128, 0, st>>>(scores, probs, Kb);
-  rc = check_launch("softmax_rows_kernel");
+  rc = launch_softmax_rows<T>(scores, probs, rows, Kb, st);
   if (rc) return rc;
   // out_c[Qb,D] = probs[Qb,Kb] * vc[Kb,D]
   return gemm<T>(probs, (long long)Qb * Kb, Kb, 1, vc, (long long)Kb * D, D, 1, out_c, BH, Qb, D, Kb, EpiStore{}, st,
