@@ -51,7 +51,8 @@ struct DqSmem {
   static constexpr uint32_t total = misc + 64;
 };
 enum DqBar { DQ_QDO_FULL = 0, DQ_K_FULL = 1, DQ_K_EMPTY = 4, DQ_V_FULL = 7, DQ_V_EMPTY = 9, DQ_DS_FULL = 11,
-             DQ_DS_EMPTY = 12, DQ_ACC_FULL = 13, DQ_S_FULL = 14, DQ_S_EMPTY = 14 + kDqBufs };
+             DQ_DS_EMPTY = 12, DQ_ACC_FULL = 13, DQ_S_FULL = 14, DQ_S_EMPTY = 14 + kDqBufs,
+             DQ_DP_FULL = 14 + 2 * kDqBufs };
 
 template <int SUB>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -96,6 +97,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     mbar_init(bar(DQ_DS_EMPTY), 1);
     for (int i = 0; i < kDqBufs; ++i) {
       mbar_init(bar(DQ_S_FULL + i), 1);
+      mbar_init(bar(DQ_DP_FULL + i), 1);
       mbar_init(bar(DQ_S_EMPTY + i), kBwWarps);
     }
     mbar_init(bar(DQ_ACC_FULL), 1);
@@ -204,16 +206,20 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int p = 0; p < n_pairs && ok; ++p) {
         const int ks = p % kDqKStages, s = p & 1, b = p % kDqBufs;
         const uint32_t ph = (p >> 1) & 1;
-        ok = VSA_WAIT(bar(DQ_K_FULL + ks), (p / kDqKStages) & 1) && VSA_WAIT(bar(DQ_V_FULL + s), ph) &&
+        ok = VSA_WAIT(bar(DQ_K_FULL + ks), (p / kDqKStages) & 1) &&
              VSA_WAIT(bar(DQ_S_EMPTY + b), ((p / kDqBufs) & 1) ^ 1);
         if (!ok) break;
         VSA_TRACE_AT(0, p);
         tc_fence_after();
-        // dP^T first: its commit hands the V stage back to the producer ~8 MMAs earlier (V has two stages only)
-        issue_kmajor(tmem + b * 128 + 64, base + DqSmem::v + s * kPairBytes, base + DqSmem::d_o);
-        mma_commit(bar(DQ_V_EMPTY + s));
+        // S^T first and signalled on its own: the elementwise warps turn it into 2^(S c - lse) while dP^T still runs
         issue_kmajor(tmem + b * 128, base + DqSmem::k + ks * kPairBytes, base + DqSmem::q);
         mma_commit(bar(DQ_S_FULL + b));
+        ok = VSA_WAIT(bar(DQ_V_FULL + s), ph);
+        if (!ok) break;
+        tc_fence_after();
+        issue_kmajor(tmem + b * 128 + 64, base + DqSmem::v + s * kPairBytes, base + DqSmem::d_o);
+        mma_commit(bar(DQ_V_EMPTY + s));
+        mma_commit(bar(DQ_DP_FULL + b));
         VSA_TRACE_AT(1, p);
       }
       if (!ok) report_timeout(12);
@@ -253,13 +259,9 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
-      uint32_t sv[kBwCols], dv[kBwCols];
+      uint32_t sv[kBwCols];
       tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
-      tmem_ld(tmem + b * 128 + 64 + lane_addr + c0, dv);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(DQ_S_EMPTY + b));
       if (tid == 128) VSA_TRACE_AT(6, p);
       // rows of K beyond a ragged tile's size (and the repeated tile of an odd tail) must be finite zeros:
       // they meet dS = 0 in the dQ product, where 0 * NaN would poison the sum.  S(p) has completed.
@@ -271,17 +273,32 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           *reinterpret_cast<uint4*>(krow + kPairHalf + ch * 16) = make_uint4(0, 0, 0, 0);
         }
       }
-      uint32_t packed[kBwCols / 2];
+      float pf[kBwCols];      // 2^(S c - lse) * scale
 #pragma unroll
       for (int j4 = 0; j4 < kBwCols / 4; ++j4) {
         const float4 l4 = *reinterpret_cast<const float4*>(s_lse + c0 + 4 * j4);
+        pf[4 * j4 + 0] = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -l4.x));
+        pf[4 * j4 + 1] = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -l4.y));
+        pf[4 * j4 + 2] = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -l4.z));
+        pf[4 * j4 + 3] = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -l4.w));
+      }
+      ok = VSA_WARP_WAIT(bar(DQ_DP_FULL + b), (p / kDqBufs) & 1);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dv[kBwCols];
+      tmem_ld(tmem + b * 128 + 64 + lane_addr + c0, dv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DQ_S_EMPTY + b));      // both accumulators of this buffer have been read
+      uint32_t packed[kBwCols / 2];
+#pragma unroll
+      for (int j4 = 0; j4 < kBwCols / 4; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c0 + 4 * j4);
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -l4.x));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -l4.y));
-        const float p2 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -l4.z));
-        const float p3 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -l4.w));
-        packed[2 * j4] = pack_bf16(p0 * (__uint_as_float(dv[4 * j4 + 0]) - d4.x), p1 * (__uint_as_float(dv[4 * j4 + 1]) - d4.y));
-        packed[2 * j4 + 1] = pack_bf16(p2 * (__uint_as_float(dv[4 * j4 + 2]) - d4.z), p3 * (__uint_as_float(dv[4 * j4 + 3]) - d4.w));
+        packed[2 * j4] = pack_bf16(pf[4 * j4 + 0] * (__uint_as_float(dv[4 * j4 + 0]) - d4.x),
+                                   pf[4 * j4 + 1] * (__uint_as_float(dv[4 * j4 + 1]) - d4.y));
+        packed[2 * j4 + 1] = pack_bf16(pf[4 * j4 + 2] * (__uint_as_float(dv[4 * j4 + 2]) - d4.z),
+                                       pf[4 * j4 + 3] * (__uint_as_float(dv[4 * j4 + 3]) - d4.w));
       }
       if (!live) {   // a padding key row: its scores come from whatever sits in K and V there
 #pragma unroll
@@ -334,27 +351,26 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // ------------------------------------------------------------------------------------------------------
 constexpr int kDkBufs = 2;     // (S, dP) accumulator pairs in flight: 2 x 128 columns, then dK^T and dV^T
 // A Q2 pair stays in shared memory from its score MMA (the first of a pair) to its dK MMA (the last), across the
-// whole elementwise stage, and a reload takes ~1500 cycles on top.  dO2 is needed 8 MMAs later (dP follows S) and
-// released 8 MMAs earlier (dV precedes dK), so it keeps two stages and Q2 gets three; P and dS pay for it with one
-// buffer each (written by pair p+1 only after the gradient MMAs of pair p have read them, which the elementwise
-// warps check right before their stores, after all their arithmetic).  Measured 2 % faster than 2 + 2 stages with
-// double-buffered P/dS: the kernel stays bound by the residency of the dO2 stages (reload + 16 MMAs + the elementwise stage + 8 MMAs,
-// per two pairs).
+// whole elementwise stage, and a reload takes ~1500 cycles on top, so Q2 gets three stages; dO2 gets two and is
+// released as early as the data flow allows: S and dP signal the elementwise warps separately, the warps turn S
+// into P while the dP MMAs still run and publish P before they look at dP, and dV^T (which needs only P) is
+// issued and committed on its own, ahead of dS and dK^T.  P and dS have one buffer each (written by pair p+1 only
+// after the MMA of pair p that reads them has completed, checked right before the stores).
 constexpr int kDkQStages = 3;
-constexpr int kDkPdsBufs = 1;
 struct DkSmem {
   static constexpr uint32_t k = 0;                                // 16 KB
   static constexpr uint32_t v = k + 2 * kSlab;                    // 16 KB
   static constexpr uint32_t q = v + 2 * kSlab;                    // kDkQStages x 32 KB  (pairs of query tiles)
   static constexpr uint32_t d_o = q + kDkQStages * kPairBytes;    // 2 x 32 KB
-  static constexpr uint32_t p = d_o + 2 * kPairBytes;             // kDkPdsBufs x 16 KB
-  static constexpr uint32_t ds = p + kDkPdsBufs * kPairHalf;      // kDkPdsBufs x 16 KB
-  static constexpr uint32_t bars = ds + kDkPdsBufs * kPairHalf;
+  static constexpr uint32_t p = d_o + 2 * kPairBytes;             // 16 KB
+  static constexpr uint32_t ds = p + kPairHalf;                   // 16 KB
+  static constexpr uint32_t bars = ds + kPairHalf;
   static constexpr uint32_t misc = bars + 32 * 8;
   static constexpr uint32_t total = misc + 64;
 };
-enum DkBar { DK_KV_FULL = 0, DK_Q_FULL = 1, DK_DO_FULL = 4, DK_Q_EMPTY = 6, DK_DO_EMPTY = 9, DK_PDS_FULL = 11,
-             DK_PDS_EMPTY = 13, DK_ACC_FULL = 15, DK_S_FULL = 16, DK_S_EMPTY = 16 + kDkBufs };
+enum DkBar { DK_KV_FULL = 0, DK_Q_FULL = 1, DK_DO_FULL = 4, DK_Q_EMPTY = 6, DK_DO_EMPTY = 9, DK_P_FULL = 11,
+             DK_P_EMPTY = 12, DK_DS_FULL = 13, DK_DS_EMPTY = 14, DK_ACC_FULL = 15, DK_S_FULL = 16,
+             DK_DP_FULL = 16 + kDkBufs, DK_S_EMPTY = 16 + 2 * kDkBufs };
 
 template <int SUB>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -406,14 +422,15 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(DK_DO_FULL + i), 4);
-      mbar_init(bar(DK_DO_EMPTY + i), 1);
+      mbar_init(bar(DK_DO_EMPTY + i), 2);    // read by the dP MMAs of one issuer and the dV^T MMAs of the other
     }
-    for (int i = 0; i < kDkPdsBufs; ++i) {
-      mbar_init(bar(DK_PDS_FULL + i), kBwWarps);
-      mbar_init(bar(DK_PDS_EMPTY + i), 1);
-    }
+    mbar_init(bar(DK_P_FULL), kBwWarps);
+    mbar_init(bar(DK_P_EMPTY), 1);
+    mbar_init(bar(DK_DS_FULL), kBwWarps);
+    mbar_init(bar(DK_DS_EMPTY), 1);
     for (int i = 0; i < kDkBufs; ++i) {
       mbar_init(bar(DK_S_FULL + i), 1);
+      mbar_init(bar(DK_DP_FULL + i), 1);
       mbar_init(bar(DK_S_EMPTY + i), kBwWarps);
     }
     mbar_init(bar(DK_ACC_FULL), 1);
@@ -466,14 +483,19 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       for (int p = 0; p < n_pairs && ok; ++p) {
         const int qs = p % kDkQStages, s = p & 1, b = p % kDkBufs;
         const uint32_t ph = (p >> 1) & 1;
-        ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) && VSA_WAIT(bar(DK_DO_FULL + s), ph) &&
+        ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) &&
              VSA_WAIT(bar(DK_S_EMPTY + b), ((p / kDkBufs) & 1) ^ 1);
         if (!ok) break;
         VSA_TRACE_AT(0, p);
         tc_fence_after();
         issue_kmajor(tmem + b * 128, base + DkSmem::q + qs * kPairBytes, base + DkSmem::k);
-        issue_kmajor(tmem + b * 128 + 64, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::v);
         mma_commit(bar(DK_S_FULL + b));
+        ok = VSA_WAIT(bar(DK_DO_FULL + s), ph);      // dO2 has two stages only and is usually the later one
+        if (!ok) break;
+        tc_fence_after();
+        issue_kmajor(tmem + b * 128 + 64, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::v);
+        mma_commit(bar(DK_DP_FULL + b));
+        mma_commit(bar(DK_DO_EMPTY + s));      // a commit covers the MMAs of the committing thread only: dP here, dV^T there
         VSA_TRACE_AT(1, p);
       }
       if (!ok) report_timeout(22);
@@ -481,19 +503,24 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   } else if (warp == 3) {
     if (lane == 0) {   // dV^T += dO2^T P and dK^T += Q2^T dS
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int qs = p % kDkQStages, s = p & 1, pb = p % kDkPdsBufs;
+        const int qs = p % kDkQStages, s = p & 1;
         const uint32_t ph = (p >> 1) & 1;
-        ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) && VSA_WAIT(bar(DK_DO_FULL + s), ph) &&
-             VSA_WAIT(bar(DK_PDS_FULL + pb), (p / kDkPdsBufs) & 1);
+        ok = VSA_WAIT(bar(DK_DO_FULL + s), ph) && VSA_WAIT(bar(DK_P_FULL), p & 1);
         if (!ok) break;
         VSA_TRACE_AT(3, p);
         tc_fence_after();
-        issue_mnmajor(tmem_dv, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::p + pb * kPairHalf, p > 0);
-        mma_commit(bar(DK_DO_EMPTY + s));
-        issue_mnmajor(tmem_dk, base + DkSmem::q + qs * kPairBytes, base + DkSmem::ds + pb * kPairHalf, p > 0);
-        mma_commit(bar(DK_Q_EMPTY + qs));
-        mma_commit(bar(DK_PDS_EMPTY + pb));
+        issue_mnmajor(tmem_dv, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::p, p > 0);
+        mma_commit(bar(DK_P_EMPTY));
+        mma_commit(bar(DK_DO_EMPTY + s));      // second of two arrivals: the other issuer commits its dP reads of the stage
         VSA_TRACE_AT(4, p);
+        ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) && VSA_WAIT(bar(DK_DS_FULL), p & 1);
+        if (!ok) break;
+        VSA_TRACE_AT(10, p);
+        tc_fence_after();
+        issue_mnmajor(tmem_dk, base + DkSmem::q + qs * kPairBytes, base + DkSmem::ds, p > 0);
+        mma_commit(bar(DK_Q_EMPTY + qs));
+        mma_commit(bar(DK_DS_EMPTY));
+        VSA_TRACE_AT(11, p);
       }
       if (ok) mma_commit(bar(DK_ACC_FULL));
       if (!ok) report_timeout(23);
@@ -516,8 +543,10 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       lse_n = lse2[row];
       dl_n = delta[row];
     }
+    uint8_t* prow = sm + DkSmem::p + t * 128;
+    uint8_t* grow = sm + DkSmem::ds + t * 128;
     for (int p = 0; p < n_pairs && ok; ++p) {
-      const int b = p % kDkBufs, pb = p % kDkPdsBufs;
+      const int b = p % kDkBufs;
       const float lse = lse_n, dl = dl_n;
       {
         const int nidx = 2 * (p + 1) + half;
@@ -529,56 +558,72 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           dl_n = delta[row];
         }
       }
+      // ---- P from S, published before dP is even looked at (the dP MMAs are still running)
       ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
-      uint32_t sv[kBwCols], dvv[kBwCols];
+      uint32_t sv[kBwCols];
       tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
+      tmem_ld_wait();
+      if (tid == 128) VSA_TRACE_AT(6, p);
+      float pf[kBwCols];
+      if (!ragged) {
+#pragma unroll
+        for (int j = 0; j < kBwCols; ++j) pf[j] = fast_exp2(fmaf(__uint_as_float(sv[j]), c, -lse));
+      } else {   // scores of a padding column come from whatever sits in K there: select, do not multiply
+#pragma unroll
+        for (int j = 0; j < kBwCols; ++j)
+          pf[j] = (c0 + j) < valid ? fast_exp2(fmaf(__uint_as_float(sv[j]), c, -lse)) : 0.f;
+      }
+      if (tid == 128) VSA_TRACE_AT(7, p);
+      ok = VSA_WARP_WAIT(bar(DK_P_EMPTY), (p & 1) ^ 1);      // dV^T of the previous pair has read the buffer
+      if (!ok) break;
+      if (tid == 128) VSA_TRACE_AT(8, p);
+#pragma unroll
+      for (int ch = 0; ch < kBwCols / 8; ++ch)
+        *reinterpret_cast<uint4*>(prow + ((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
+            make_uint4(pack_bf16(pf[8 * ch], pf[8 * ch + 1]), pack_bf16(pf[8 * ch + 2], pf[8 * ch + 3]),
+                       pack_bf16(pf[8 * ch + 4], pf[8 * ch + 5]), pack_bf16(pf[8 * ch + 6], pf[8 * ch + 7]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DK_P_FULL));
+      if (tid == 128) VSA_TRACE_AT(9, p);
+      // ---- dS = P * (dP - delta)
+      ok = VSA_WARP_WAIT(bar(DK_DP_FULL + b), (p / kDkBufs) & 1);
+      if (!ok) break;
+      if (tid == 128) VSA_TRACE_AT(12, p);
+      tc_fence_after();
+      uint32_t dvv[kBwCols];
       tmem_ld(tmem + b * 128 + 64 + lane_addr + c0, dvv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(DK_S_EMPTY + b));
-      if (tid == 128) VSA_TRACE_AT(6, p);
-      uint32_t pp[kBwCols / 2], pg[kBwCols / 2];
+      if (lane == 0) mbar_arrive(bar(DK_S_EMPTY + b));       // both accumulators of this buffer have been read
+      uint32_t pg[kBwCols / 2];
       if (!ragged) {
 #pragma unroll
-        for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse));
-          pp[j2] = pack_bf16(p0, p1);
-          pg[j2] = pack_bf16(p0 * (__uint_as_float(dvv[2 * j2]) - dl), p1 * (__uint_as_float(dvv[2 * j2 + 1]) - dl));
-        }
-      } else {   // scores of a padding column come from whatever sits in K and V there: select, do not multiply
+        for (int j2 = 0; j2 < kBwCols / 2; ++j2)
+          pg[j2] = pack_bf16(pf[2 * j2] * (__uint_as_float(dvv[2 * j2]) - dl),
+                             pf[2 * j2 + 1] * (__uint_as_float(dvv[2 * j2 + 1]) - dl));
+      } else {   // dP of a padding column comes from whatever sits in V there
 #pragma unroll
         for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
-          const bool k0 = (c0 + 2 * j2) < valid, k1 = (c0 + 2 * j2 + 1) < valid;
-          const float p0 = k0 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2]), c, -lse)) : 0.f;
-          const float p1 = k1 ? fast_exp2(fmaf(__uint_as_float(sv[2 * j2 + 1]), c, -lse)) : 0.f;
-          const float g0 = k0 ? p0 * (__uint_as_float(dvv[2 * j2]) - dl) : 0.f;
-          const float g1 = k1 ? p1 * (__uint_as_float(dvv[2 * j2 + 1]) - dl) : 0.f;
-          pp[j2] = pack_bf16(p0, p1);
+          const float g0 = (c0 + 2 * j2) < valid ? pf[2 * j2] * (__uint_as_float(dvv[2 * j2]) - dl) : 0.f;
+          const float g1 = (c0 + 2 * j2 + 1) < valid ? pf[2 * j2 + 1] * (__uint_as_float(dvv[2 * j2 + 1]) - dl) : 0.f;
           pg[j2] = pack_bf16(g0, g1);
         }
       }
-      if (tid == 128) VSA_TRACE_AT(7, p);
-      // the P/dS buffers are free once the gradient MMAs that read them (kDkPdsBufs pairs back) have completed
-      ok = VSA_WARP_WAIT(bar(DK_PDS_EMPTY + pb), ((p / kDkPdsBufs) & 1) ^ 1);
+      ok = VSA_WARP_WAIT(bar(DK_DS_EMPTY), (p & 1) ^ 1);     // dK^T of the previous pair has read the buffer
       if (!ok) break;
-      if (tid == 128) VSA_TRACE_AT(8, p);
-      uint8_t* prow = sm + DkSmem::p + pb * kPairHalf + t * 128;
-      uint8_t* grow = sm + DkSmem::ds + pb * kPairHalf + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < kBwCols / 8; ++ch) {
-        const uint32_t off = (uint32_t)((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4);
-        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
-        *reinterpret_cast<uint4*>(grow + off) = make_uint4(pg[4 * ch], pg[4 * ch + 1], pg[4 * ch + 2], pg[4 * ch + 3]);
-      }
+      for (int ch = 0; ch < kBwCols / 8; ++ch)
+        *reinterpret_cast<uint4*>(grow + ((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
+            make_uint4(pg[4 * ch], pg[4 * ch + 1], pg[4 * ch + 2], pg[4 * ch + 3]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(DK_PDS_FULL + pb));
-      if (tid == 128) VSA_TRACE_AT(9, p);
+      if (lane == 0) mbar_arrive(bar(DK_DS_FULL));
+      if (tid == 128) VSA_TRACE_AT(13, p);
     }
     if (!ok && lane == 0) report_timeout(24);
     if (ok) ok = VSA_WARP_WAIT(bar(DK_ACC_FULL), 0);
