@@ -11,20 +11,17 @@
 // ACROSS lanes.  They are handled without per-tile cross-lane traffic:
 //   * the shift m[q] is the exact column maximum of the FIRST live pair only (one cross-lane
 //     reduction per CTA); softmax is shift-invariant, so any later score simply gives
-//     P = 2^(s-m) > 1, which bf16 and fp32 hold up to 2^127.  (One shift for the whole tile would
-//     live in a register and spare sixteen shared-memory reads per thread and pair, measured 1 %
-//     faster, but rows ~100 binades below the tile's largest score then lose precision silently:
-//     products near 2^-126 are flushed.  Per-row shifts keep every row's largest term at 1.)
+//     P = 2^(s-m) > 1, which bf16 and fp32 hold up to 2^127;
 //   * every thread keeps its own partial row sums (64 registers) and they are reduced across
 //     lanes once at the end;
 //   * if a sum or an output leaves the finite range (scores more than ~2^7 apart in log2
-//     units from the first pair's maximum of that row) the tile writes NaN into its log-sum-exp rows and
+//     units from the first pair's maximum) the tile writes NaN into its log-sum-exp rows and
 //     the exact warp-level kernel recomputes just those tiles in a follow-up launch.
 // P^T is written by its owner thread as one swizzled 128-byte row of shared memory (N-major B
 // operand), so no transposition is ever needed.
 //
 // Roles: warp 0 = K producer, warp 1 = V producer (four lanes, one TMA box each; warp 1 also owns the
-// tensor memory), warp 2 = issuer of the S^T MMAs, warp 3 = issuer of the O^T MMAs, warps 4-19 = softmax (a TMEM lane quarter and sixteen of the
+// tensor memory), warp 2 = issuer of the S^T MMAs, warp 3 = issuer of the O^T MMAs, warps 4-19 = softmax (a TMEM lane quarter and half of the
 // query-row columns each).  Every mbarrier wait is bounded; on a time-out the CTA records an error code in a
 // device status word, stops issuing work, frees its tensor memory and returns.
 #include <cuda.h>
@@ -66,7 +63,6 @@ constexpr int kPairBytes = 2 * kPairHalf;
 constexpr uint32_t kTmemCols = 512;
 // K pairs in flight: a reload from L2 takes ~2000 cycles, two stages left the S^T issuer waiting for it
 constexpr int kFwdKStages = 2;
-constexpr int kPBufs = 2;              // P^T buffers in shared memory (16 KB each); four measured no faster
 constexpr int kSBufs = 4;              // S^T accumulators in flight (64 columns each); O^T sits behind them
 
 // ---- host: tensor maps ---------------------------------------------------------------------------
@@ -230,7 +226,7 @@ struct FwdSmem {
   static constexpr uint32_t k = q + 2 * kSlab;                   // 2 stages x 32 KB
   static constexpr uint32_t v = k + kFwdKStages * kPairBytes;    // 2 stages x 32 KB (K above: 3 stages)
   static constexpr uint32_t p = v + 2 * kPairBytes;              // 2 buffers x 16 KB
-  static constexpr uint32_t tile_row = p + kPBufs * kPairHalf;        // int32 [kMaxTiles]
+  static constexpr uint32_t tile_row = p + 2 * kPairHalf;        // int32 [kMaxTiles]
   static constexpr uint32_t tile_valid = tile_row + 4 * kMaxTiles;   // uint8 [kMaxTiles]
   static constexpr uint32_t m_warp = tile_valid + kMaxTiles;     // float [4 lane quarters][64]
   static constexpr uint32_t m_col = m_warp + 4 * 64 * 4;         // float [64]
@@ -243,8 +239,8 @@ constexpr int kEwCols = 16;          // columns of a TMEM tile one elementwise t
 constexpr int kEwWarps = 4 * (64 / kEwCols);   // lane quarters x column groups = 16 warps
 constexpr int kEwThreads = 32 * kEwWarps;
 constexpr int kFwdThreads = 128 + kEwThreads;   // K producer, V producer, two MMA issuers, elementwise warps
-enum FwdBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, P_FULL = 11, P_EMPTY = 15, O_FULL = 19,
-              S_FULL = 20, S_EMPTY = 20 + kSBufs };
+enum FwdBar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 9, P_FULL = 11, P_EMPTY = 13, O_FULL = 15,
+              S_FULL = 16, S_EMPTY = 16 + kSBufs };
 
 template <int SUB>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -280,8 +276,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(V_FULL + i), 4);
       mbar_init(bar(V_EMPTY + i), 1);
-    }
-    for (int i = 0; i < kPBufs; ++i) {
       mbar_init(bar(P_FULL + i), kEwWarps);      // one elected lane per softmax warp
       mbar_init(bar(P_EMPTY + i), 1);
     }
@@ -370,41 +364,40 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else if (warp == 2) {
     // ================= MMA issuer 1: S^T = K2 Q^T, as far ahead as operands and accumulators allow =================
-    ok = VSA_WARP_WAIT(bar(Q_FULL), 0);
-    for (int p = 0; p < n_pairs && ok; ++p) {
-      const int s = p % kFwdKStages, b = p % kSBufs;
-      ok = VSA_WARP_WAIT2(bar(K_FULL + s), (p / kFwdKStages) & 1, bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
-      if (!ok) break;
-      if (lane == 0) VSA_TRACE_AT(0, p);
-      tc_fence_after();
-      if (elect_one()) {
+    if (lane == 0) {
+      ok = VSA_WAIT(bar(Q_FULL), 0);
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p % kFwdKStages, b = p % kSBufs;
+        ok = VSA_WAIT(bar(K_FULL + s), (p / kFwdKStages) & 1) && VSA_WAIT(bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
+        if (!ok) break;
+        VSA_TRACE_AT(0, p);
+        tc_fence_after();
         issue_kmajor(tmem_s0 + b * 64, base + FwdSmem::k + s * kPairBytes, base + FwdSmem::q);
         mma_commit(bar(K_EMPTY + s));
         mma_commit(bar(S_FULL + b));
+        VSA_TRACE_AT(1, p);
       }
-      __syncwarp();
-      if (lane == 0) VSA_TRACE_AT(1, p);
+      if (!ok) report_timeout(2);
     }
-    if (!ok && lane == 0) report_timeout(2);
   } else if (warp == 3) {
     // ================= MMA issuer 2: O^T += V2^T P^T =================
-    for (int j = 0; j < n_pairs && ok; ++j) {
-      const int s = j & 1, pb = j % kPBufs;
-      ok = VSA_WARP_WAIT2(bar(V_FULL + s), (j >> 1) & 1, bar(P_FULL + pb), (j / kPBufs) & 1);
-      if (!ok) break;
-      if (lane == 0) VSA_TRACE_AT(3, j);
-      tc_fence_after();
-      if (elect_one()) {
-        issue_mnmajor(tmem_o, base + FwdSmem::v + s * kPairBytes, base + FwdSmem::p + pb * kPairHalf, j > 0);
+    if (lane == 0) {
+      for (int j = 0; j < n_pairs && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = VSA_WAIT(bar(V_FULL + s), ph);
+        VSA_TRACE_AT(2, j);
+        ok = ok && VSA_WAIT(bar(P_FULL + s), ph);
+        if (!ok) break;
+        VSA_TRACE_AT(3, j);
+        tc_fence_after();
+        issue_mnmajor(tmem_o, base + FwdSmem::v + s * kPairBytes, base + FwdSmem::p + s * kPairHalf, j > 0);
         mma_commit(bar(V_EMPTY + s));
-        mma_commit(bar(P_EMPTY + pb));
+        mma_commit(bar(P_EMPTY + s));
+        VSA_TRACE_AT(4, j);
       }
-      __syncwarp();
-      if (lane == 0) VSA_TRACE_AT(4, j);
-    }
-    if (elect_one()) {
       if (ok) mma_commit(bar(O_FULL));
-      else report_timeout(5);
+      if (!ok) report_timeout(5);
     }
   } else if (warp >= 4) {
     // ================= softmax warps =================
@@ -432,8 +425,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool live = r < valid;
       const int sb = p % kSBufs;
       // the score accumulator and the free P buffer (released by the O^T MMA two pairs back) in one round trip
-      const int pb = p % kPBufs;
-      ok = VSA_WARP_WAIT2(bar(S_FULL + sb), (p / kSBufs) & 1, bar(P_EMPTY + pb), ((p / kPBufs) & 1) ^ 1);
+      ok = VSA_WARP_WAIT2(bar(S_FULL + sb), (p / kSBufs) & 1, bar(P_EMPTY + s), ph ^ 1);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
@@ -469,32 +461,27 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ok = __all_sync(0xffffffffu, ok);     // keep the warp's control flow uniform
       if (!ok) break;
       uint32_t packed[kEwCols / 2];
-      if (live) {
 #pragma unroll
-        for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
-          const float4 m4 = *reinterpret_cast<const float4*>(m_col + c0 + 4 * j4);
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m4.x));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m4.y));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m4.z));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m4.w));
-          lsum[4 * j4 + 0] += p0; lsum[4 * j4 + 1] += p1; lsum[4 * j4 + 2] += p2; lsum[4 * j4 + 3] += p3;
-          packed[2 * j4] = pack_bf16(p0, p1);
-          packed[2 * j4 + 1] = pack_bf16(p2, p3);
-        }
-      } else {   // a padding key row contributes nothing
-#pragma unroll
-        for (int j = 0; j < kEwCols / 2; ++j) packed[j] = 0u;
+      for (int j4 = 0; j4 < kEwCols / 4; ++j4) {
+        const float4 m4 = *reinterpret_cast<const float4*>(m_col + c0 + 4 * j4);
+        const float p0 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 0]), c, -m4.x)) : 0.f;
+        const float p1 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 1]), c, -m4.y)) : 0.f;
+        const float p2 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m4.z)) : 0.f;
+        const float p3 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m4.w)) : 0.f;
+        lsum[4 * j4 + 0] += p0; lsum[4 * j4 + 1] += p1; lsum[4 * j4 + 2] += p2; lsum[4 * j4 + 3] += p3;
+        packed[2 * j4] = pack_bf16(p0, p1);
+        packed[2 * j4 + 1] = pack_bf16(p2, p3);
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
       if (tid == 128) VSA_TRACE_AT(8, p);
-      uint8_t* prow = sm + FwdSmem::p + pb * kPairHalf + t * 128;
+      uint8_t* prow = sm + FwdSmem::p + s * kPairHalf + t * 128;
 #pragma unroll
       for (int ch = 0; ch < kEwCols / 8; ++ch)     // this thread's query rows are 16-byte chunks of row t
         *reinterpret_cast<uint4*>(prow + ((((kEwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
             make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_FULL + pb));
+      if (lane == 0) mbar_arrive(bar(P_FULL + s));
       if (tid == 128) VSA_TRACE_AT(9, p);
     }
     if (!ok) report_timeout(3);

@@ -156,15 +156,6 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// One lane of a converged warp.  The issuer warps run their loops with all 32 lanes (waits, descriptor
-// arithmetic on warp-uniform values) and only the tcgen05.mma / tcgen05.commit instructions sit under this
-// predicate: a loop that is divergent as a whole (if (lane == 0) { ... }) issued one MMA per ~65 cycles on an
-// idle tensor pipe, slower than the pipe executes them.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
 // mbarrier arrives once every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
