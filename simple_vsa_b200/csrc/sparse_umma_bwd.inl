@@ -18,15 +18,17 @@
 //
 // Nothing here needs a running maximum (the forward saved the log-sum-exp), so there is no
 // cross-lane traffic at all.  Roles per CTA: warp 0 and 1 = TMA producers (four lanes, one box each),
-// warp 2 = issuer of the score MMAs, warp 3 = issuer of the gradient MMAs, warps 4-19 = elementwise
-// (a TMEM lane quarter x 16 of the 64 columns each).
+// warp 2 = issuer of the S MMAs, warp 3 = issuer of the gradient MMAs, warps 4-11 = elementwise (a TMEM
+// lane quarter x 32 of the 64 columns each), warp 12 = issuer of the dP MMAs (the three issuers wait on
+// different operands and must not hold one another back).
 
 // The backward passes are closest to the shared-memory bandwidth limit (every operand byte is read by an
 // MMA once or twice per pair); eight wider elementwise warps disturb that pipe less than sixteen narrow ones.
 constexpr int kBwCols = 32;
 constexpr int kBwWarps = 4 * (64 / kBwCols);
 constexpr int kBwEwThreads = 32 * kBwWarps;
-constexpr int kBwdThreads = 128 + kBwEwThreads;
+constexpr int kBwdThreads = 128 + kBwEwThreads + 32;   // ... plus the dP issuer, the last warp
+constexpr int kDpWarp = 4 + kBwWarps;
 
 // ------------------------------------------------------------------------------------------------------
 // dQ
@@ -111,7 +113,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
     tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
   }
-  if (warp >= 4) {   // delta = rowsum(out_s * dout) and the saved statistic, eight threads per query row
+  if (warp >= 4 && warp < kDpWarp) {   // delta = rowsum(out_s * dout) and the saved statistic, eight threads per query row
     constexpr int kPer = kBwEwThreads / 64;            // threads per row
     constexpr int kDims = kD / kPer;                 // dims per thread
     const int st = tid - 128;
@@ -201,28 +203,35 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
     if (!ok && lane == 0) report_timeout(11);
   } else if (warp == 2) {
-    if (lane == 0) {   // scores: S^T = K2 Q^T and dP^T = V2 dO^T
+    if (lane == 0) {   // scores: S^T = K2 Q^T
       ok = VSA_WAIT(bar(DQ_QDO_FULL), 0);
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int ks = p % kDqKStages, s = p & 1, b = p % kDqBufs;
-        const uint32_t ph = (p >> 1) & 1;
+        const int ks = p % kDqKStages, b = p % kDqBufs;
         ok = VSA_WAIT(bar(DQ_K_FULL + ks), (p / kDqKStages) & 1) &&
              VSA_WAIT(bar(DQ_S_EMPTY + b), ((p / kDqBufs) & 1) ^ 1);
         if (!ok) break;
         VSA_TRACE_AT(0, p);
         tc_fence_after();
-        // S^T first and signalled on its own: the elementwise warps turn it into 2^(S c - lse) while dP^T still runs
+        // S^T is signalled on its own: the elementwise warps turn it into 2^(S c - lse) while dP^T still runs
         issue_kmajor(tmem + b * 128, base + DqSmem::k + ks * kPairBytes, base + DqSmem::q);
         mma_commit(bar(DQ_S_FULL + b));
-        ok = VSA_WAIT(bar(DQ_V_FULL + s), ph);
+        VSA_TRACE_AT(1, p);
+      }
+      if (!ok) report_timeout(12);
+    }
+  } else if (warp == kDpWarp) {
+    if (lane == 0) {   // dP^T = V2 dO^T from a thread of its own: a late V pair must not hold back the next S^T
+      ok = VSA_WAIT(bar(DQ_QDO_FULL), 0);
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p & 1, b = p % kDqBufs;
+        ok = VSA_WAIT(bar(DQ_V_FULL + s), (p >> 1) & 1) && VSA_WAIT(bar(DQ_S_EMPTY + b), ((p / kDqBufs) & 1) ^ 1);
         if (!ok) break;
         tc_fence_after();
         issue_kmajor(tmem + b * 128 + 64, base + DqSmem::v + s * kPairBytes, base + DqSmem::d_o);
         mma_commit(bar(DQ_V_EMPTY + s));
         mma_commit(bar(DQ_DP_FULL + b));
-        VSA_TRACE_AT(1, p);
       }
-      if (!ok) report_timeout(12);
+      if (!ok) report_timeout(16);
     }
   } else if (warp == 3) {
     if (lane == 0) {   // dQ^T += K2^T dS^T
@@ -478,11 +487,10 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     if (!ok && lane == 0) report_timeout(21);
   } else if (warp == 2) {
-    if (lane == 0) {   // scores: S = Q2 K^T and dP = dO2 V^T
+    if (lane == 0) {   // scores: S = Q2 K^T
       ok = VSA_WAIT(bar(DK_KV_FULL), 0);
       for (int p = 0; p < n_pairs && ok; ++p) {
-        const int qs = p % kDkQStages, s = p & 1, b = p % kDkBufs;
-        const uint32_t ph = (p >> 1) & 1;
+        const int qs = p % kDkQStages, b = p % kDkBufs;
         ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) &&
              VSA_WAIT(bar(DK_S_EMPTY + b), ((p / kDkBufs) & 1) ^ 1);
         if (!ok) break;
@@ -490,15 +498,23 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         tc_fence_after();
         issue_kmajor(tmem + b * 128, base + DkSmem::q + qs * kPairBytes, base + DkSmem::k);
         mma_commit(bar(DK_S_FULL + b));
-        ok = VSA_WAIT(bar(DK_DO_FULL + s), ph);      // dO2 has two stages only and is usually the later one
+        VSA_TRACE_AT(1, p);
+      }
+      if (!ok) report_timeout(22);
+    }
+  } else if (warp == kDpWarp) {
+    if (lane == 0) {   // dP = dO2 V^T from a thread of its own: dO2 has two stages only and must not hold back the next S
+      ok = VSA_WAIT(bar(DK_KV_FULL), 0);
+      for (int p = 0; p < n_pairs && ok; ++p) {
+        const int s = p & 1, b = p % kDkBufs;
+        ok = VSA_WAIT(bar(DK_DO_FULL + s), (p >> 1) & 1) && VSA_WAIT(bar(DK_S_EMPTY + b), ((p / kDkBufs) & 1) ^ 1);
         if (!ok) break;
         tc_fence_after();
         issue_kmajor(tmem + b * 128 + 64, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::v);
         mma_commit(bar(DK_DP_FULL + b));
         mma_commit(bar(DK_DO_EMPTY + s));      // a commit covers the MMAs of the committing thread only: dP here, dV^T there
-        VSA_TRACE_AT(1, p);
       }
-      if (!ok) report_timeout(22);
+      if (!ok) report_timeout(26);
     }
   } else if (warp == 3) {
     if (lane == 0) {   // dV^T += dO2^T P and dK^T += Q2^T dS
