@@ -259,8 +259,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int st = tid - 128;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     for (int p = 0; p < n_pairs && ok; ++p) {
-      const int s = p & 1, b = p % kDqBufs;
-      const uint32_t ph = (p >> 1) & 1;
+      const int b = p % kDqBufs;
       const int idx = 2 * p + half;
       const int valid = idx < n_live ? (int)tile_valid[idx] : 0;
       const bool live = r < valid;
