@@ -55,7 +55,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const v
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
-      __nanosleep(20);   // measured: no slower than a bare retry loop, and it leaves the issue slots to others
+      __nanosleep(20);   // measured with 0, 20, 100 and 400 ns: no difference in kernel time or board power
     }
     if (*abort_flag != 0) return false;
     const unsigned long long now = global_ns();
