@@ -482,8 +482,17 @@ def run_reference_gpu(args, cfg, rank: int, world: int, local_rank: int):
     nb = L // be
     data = make_slices(cfg, first, count, dev)
     sizes = torch.full((nb,), be, dtype=torch.int64, device=dev)
-    if cfg.get("ragged_frac") or cfg.get("routes"):
-        return unavailable("ragged / explicit-route workloads are timed for this package only")
+    if cfg.get("routes"):
+        return unavailable("explicit-route workloads are timed for this package only")
+    if cfg.get("ragged_frac"):      # the same ragged blocks as run_gpu: seeded choice, sizes in [1, be), padding rows zeroed
+        g = torch.Generator().manual_seed(SEED)
+        ragged = torch.randperm(nb, generator=g)[:max(1, int(round(nb * cfg["ragged_frac"])))]
+        sizes_h = torch.full((nb,), be, dtype=torch.int32)
+        sizes_h[ragged] = torch.randint(1, be, (ragged.numel(),), generator=g, dtype=torch.int32)
+        sizes = sizes_h.to(dev, torch.int64)
+        pad = (torch.arange(be)[None, :] >= sizes_h[:, None]).reshape(L).to(dev)
+        for n in ("q", "k", "v"):
+            data[n][:, :, pad] = 0
     q, k, v = (data[n].requires_grad_() for n in ("q", "k", "v"))
     gate, dout = data.get("gate"), data["dout"]
 
