@@ -167,6 +167,25 @@ int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const vo
                         int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                         float scale, int dtype, void* stream);
 
+/* vsa_sparse_bwd_dq / vsa_sparse_bwd_dkdv with the block-mean backward folded into their stores:
+ * dq[t] = fine gradient + dq_mean[block] / max(q_sizes[block], 1) for t < q_sizes[block] (and likewise dk, dv
+ * with kv_sizes), rounded once.  dq_mean, dk_mean, dv_mean are the pooled gradients [BH, Qb | Kb, D] that
+ * vsa_coarse_bwd produced.  Replaces the fine backward kernels PLUS _block_mean_backward_kernel and the
+ * AccumulateGrad adds that follow it: vsa/triton_impl.py:703-1318 + vsa/fused_common.py:62-103,146-172. */
+int vsa_sparse_bwd_dq_fused(const void* dout, const void* q, const void* k, const void* v,
+                            const void* out_s, const float* lse2,
+                            const int32_t* selected, const int32_t* kv_sizes,
+                            float* delta, void* dq, const void* dq_mean, const int32_t* q_sizes,
+                            int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                            float scale, int dtype, void* stream);
+int vsa_sparse_bwd_dkdv_fused(const void* dout, const void* q, const void* k, const void* v,
+                              const float* lse2, const float* delta,
+                              const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                              const int32_t* kv_sizes, void* dk, void* dv,
+                              const void* dk_mean, const void* dv_mean,
+                              int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                              float scale, int dtype, void* stream);
+
 /* dst[b, r, :] = map[r] >= 0 ? src[b, map[r], :] : 0 for rows of row_bytes bytes (even; 16-byte
  * multiples take the vector path).  With the maps of the tiling metadata this is the raster ->
  * zero-padded tile layout move and its inverse.

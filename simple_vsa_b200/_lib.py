@@ -32,6 +32,8 @@ SIGNATURES = {
     "vsa_route_invert_static": [P, P, P, P, L, I, I, I, P],
     "vsa_sparse_bwd_dq": [P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dkdv": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_bwd_dq_fused": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_bwd_dkdv_fused": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_combine_fwd": [P, P, P, P, L, L, I, I, I, P],
     "vsa_gather_rows": [P, P, P, L, L, L, L, P],
     "vsa_selftest_umma": [P, P, P, I, P],

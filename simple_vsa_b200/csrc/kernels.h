@@ -62,11 +62,12 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
                     cudaStream_t st);
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
-                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st);
+                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
+                   const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr);
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                     float scale, cudaStream_t st);
+                     float scale, cudaStream_t st, const void* dk_mean = nullptr, const void* dv_mean = nullptr);
 bool coarse_umma_eligible(int Qb, int Kb, int D, int dtype);
 int coarse_fwd_umma(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
                     int Qb, int Kb, int D, float scale, cudaStream_t st);

@@ -584,7 +584,8 @@ static int reserve_smem(Kern kern, int bytes, const char* what) {
 
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
-                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st) {
+                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
+                   const void* dq_mean, const int32_t* q_sizes) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dQ: batch*heads %lld exceeds 65535", (long long)BH);
   CUtensorMap mq, mdo, mk, mv;
@@ -598,11 +599,13 @@ int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v
   if (be == 64) {
     if ((rc = reserve_smem(sparse_dq_umma_kernel<1>, smem, "sparse dQ"))) return rc;
     sparse_dq_umma_kernel<1><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const bf16*)dout, (const bf16*)out_s, lse2,
-                                                              selected, kv_sizes, delta, (bf16*)dq, Lq, Lkv, topk, scale);
+                                                              selected, kv_sizes, delta, (bf16*)dq, (const bf16*)dq_mean, q_sizes, Lq, Lkv,
+                                                              topk, scale);
   } else {
     if ((rc = reserve_smem(sparse_dq_umma_kernel<4>, smem, "sparse dQ"))) return rc;
     sparse_dq_umma_kernel<4><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const bf16*)dout, (const bf16*)out_s, lse2,
-                                                              selected, kv_sizes, delta, (bf16*)dq, Lq, Lkv, topk, scale);
+                                                              selected, kv_sizes, delta, (bf16*)dq, (const bf16*)dq_mean, q_sizes, Lq, Lkv,
+                                                              topk, scale);
   }
   return check_launch("sparse_dq_umma_kernel");
 }
@@ -610,7 +613,7 @@ int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                     float scale, cudaStream_t st) {
+                     float scale, cudaStream_t st, const void* dk_mean, const void* dv_mean) {
   if (BH == 0 || Lkv == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: batch*heads %lld exceeds 65535", (long long)BH);
   CUtensorMap mq, mdo, mk, mv;
@@ -624,11 +627,13 @@ int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void*
   if (be == 64) {
     if ((rc = reserve_smem(sparse_dkdv_umma_kernel<1>, smem, "sparse dK/dV"))) return rc;
     sparse_dkdv_umma_kernel<1><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse,
-                                                                kv_sizes, (bf16*)dk, (bf16*)dv, Lq, Lkv, topk, scale);
+                                                                kv_sizes, (bf16*)dk, (bf16*)dv, (const bf16*)dk_mean,
+                                                                (const bf16*)dv_mean, Lq, Lkv, topk, scale);
   } else {
     if ((rc = reserve_smem(sparse_dkdv_umma_kernel<4>, smem, "sparse dK/dV"))) return rc;
     sparse_dkdv_umma_kernel<4><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse,
-                                                                kv_sizes, (bf16*)dk, (bf16*)dv, Lq, Lkv, topk, scale);
+                                                                kv_sizes, (bf16*)dk, (bf16*)dv, (const bf16*)dk_mean,
+                                                                (const bf16*)dv_mean, Lq, Lkv, topk, scale);
   }
   return check_launch("sparse_dkdv_umma_kernel");
 }

@@ -62,8 +62,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const bf16* __restrict__ dout, const bf16* __restrict__ out_s, const float* __restrict__ lse2,
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
-                      float* __restrict__ delta, bf16* __restrict__ dq, long long Lq, long long Lkv, int topk,
-                      float scale) {
+                      float* __restrict__ delta, bf16* __restrict__ dq, const bf16* __restrict__ mean_grad,
+                      const int32_t* __restrict__ q_sizes, long long Lq, long long Lkv, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -331,14 +331,24 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (!ok && lane == 0) report_timeout(15);
     tc_fence_after();
     bf16* stage = reinterpret_cast<bf16*>(sm + DqSmem::k);      // [64 query rows][128 dims]; every MMA is done
+    // block-mean backward folded in (optional): query row r of the block also receives dmean[block] / max(size, 1)
+    // while r < size (vsa/fused_common.py:62-103 of the reference); here lane t is the head dim, a column a row
+    float gm = 0.f;
+    int rows_live = 0;
+    if (mean_grad != nullptr) {
+      const int size = q_sizes[qb];
+      gm = __bfloat162float(mean_grad[(bh * Qb + qb) * (long long)kD + t]) / (float)(size > 1 ? size : 1);
+      rows_live = size - (qtile % SUB) * kTile;
+    }
     if (ok && n_pairs > 0) {
       uint32_t av[kBwCols];
       tmem_ld(tmem_acc + lane_addr + c0, av);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
+      for (int j = 0; j < kBwCols; ++j)
+        stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]) + ((c0 + j) < rows_live ? gm : 0.f));
     } else {
-      for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
+      for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn((c0 + j) < rows_live ? gm : 0.f);
     }
     named_barrier(1, kBwEwThreads);
     bf16* og = dq + qrow0 * kD;
@@ -387,8 +397,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const float* __restrict__ lse2, const float* __restrict__ delta,
                         const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
                         const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
-                        bf16* __restrict__ dk, bf16* __restrict__ dv, long long Lq, long long Lkv, int topk,
-                        float scale) {
+                        bf16* __restrict__ dk, bf16* __restrict__ dv, const bf16* __restrict__ mean_grad_k,
+                        const bf16* __restrict__ mean_grad_v, long long Lq, long long Lkv, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -408,12 +418,26 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const float c = scale * kLog2e;
   const long long q_row_base = bh * Lq;
 
-  if (n_pairs == 0) {   // nobody selected this tile, or it is all padding: zero gradients, no pipeline
+  // block-mean backward folded in (optional): key row r of the block also receives dmean[block] / max(size, 1)
+  // while r < size (vsa/fused_common.py:62-103 of the reference)
+  const float mean_inv = 1.f / (float)(kv_sizes[kvb] > 1 ? kv_sizes[kvb] : 1);
+  const long long mean_off = (bh * Kb + kvb) * (long long)kD;
+  if (n_pairs == 0) {   // nobody selected this tile, or it is all padding: no fine gradient, no pipeline
     uint4* gk = reinterpret_cast<uint4*>(dk + krow0 * kD);
     uint4* gv = reinterpret_cast<uint4*>(dv + krow0 * kD);
     for (int i = tid; i < 1024; i += kBwdThreads) {
-      gk[i] = make_uint4(0, 0, 0, 0);
-      gv[i] = make_uint4(0, 0, 0, 0);
+      uint4 ok4 = make_uint4(0, 0, 0, 0), ov4 = make_uint4(0, 0, 0, 0);
+      if (mean_grad_k != nullptr && (i >> 4) < valid) {     // 16 chunks of eight dims per row
+        bf16* ek = reinterpret_cast<bf16*>(&ok4);
+        bf16* ev = reinterpret_cast<bf16*>(&ov4);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          ek[e] = __float2bfloat16_rn(__bfloat162float(mean_grad_k[mean_off + (i & 15) * 8 + e]) * mean_inv);
+          ev[e] = __float2bfloat16_rn(__bfloat162float(mean_grad_v[mean_off + (i & 15) * 8 + e]) * mean_inv);
+        }
+      }
+      gk[i] = ok4;
+      gv[i] = ov4;
     }
     return;
   }
@@ -651,10 +675,16 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tmem_ld(tmem_dk + lane_addr + c0, ak);
       tmem_ld(tmem_dv + lane_addr + c0, av);
       tmem_ld_wait();
+      float gmk = 0.f, gmv = 0.f;            // lane t is the head dim here, a column a key row
+      if (mean_grad_k != nullptr) {
+        gmk = __bfloat162float(mean_grad_k[mean_off + t]) * mean_inv;
+        gmv = __bfloat162float(mean_grad_v[mean_off + t]) * mean_inv;
+      }
 #pragma unroll
       for (int j = 0; j < kBwCols; ++j) {
-        stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(ak[j]) * scale);
-        stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]));
+        const bool row_live = (c0 + j) < valid;
+        stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(ak[j]) * scale + (row_live ? gmk : 0.f));
+        stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]) + (row_live ? gmv : 0.f));
       }
     } else {
       for (int j = 0; j < kBwCols; ++j) {

@@ -124,7 +124,9 @@ def invert_routes(selected: Tensor, key_blocks: int):
     return inverse, offsets, counts
 
 
-def sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be: int, scale: float):
+def sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be: int, scale: float, pooled_grads=None):
+    """dQ, dK, dV of the fine branch.  ``pooled_grads = (dq_mean, dk_mean, dv_mean, q_sizes)`` folds the
+    block-mean backward of the pooled branch into the same kernels' stores."""
     B, H, Lq, D = q.shape
     Lkv = k.shape[2]
     dt = _check_device_dtype(q, k, v)
@@ -135,6 +137,15 @@ def sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be: int, scal
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
+    if pooled_grads is not None:
+        dqc, dkc, dvc, q_sizes = pooled_grads
+        call("vsa_sparse_bwd_dq_fused", dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out_s.data_ptr(),
+             lse.data_ptr(), selected.data_ptr(), kv_sizes.data_ptr(), delta.data_ptr(), dq.data_ptr(),
+             dqc.data_ptr(), q_sizes.data_ptr(), B * H, Lq, Lkv, D, be, tk, scale, dt, st)
+        call("vsa_sparse_bwd_dkdv_fused", dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), lse.data_ptr(),
+             delta.data_ptr(), counts.data_ptr(), offsets.data_ptr(), inverse.data_ptr(), kv_sizes.data_ptr(),
+             dk.data_ptr(), dv.data_ptr(), dkc.data_ptr(), dvc.data_ptr(), B * H, Lq, Lkv, D, be, tk, scale, dt, st)
+        return dq, dk, dv
     call("vsa_sparse_bwd_dq", dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out_s.data_ptr(),
          lse.data_ptr(), selected.data_ptr(), kv_sizes.data_ptr(), delta.data_ptr(), dq.data_ptr(),
          B * H, Lq, Lkv, D, be, tk, scale, dt, st)
@@ -261,13 +272,9 @@ class _VideoSparseAttention(torch.autograd.Function):
                  probs.data_ptr(), ds_ws.data_ptr(), rowdot.data_ptr(), dqc.data_ptr(), dkc.data_ptr(),
                  dvc.data_ptr(), B * H, Qb, Kb, D, scale, dt, st)
             del ds_ws
-            dq, dk, dv = sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale)
-            call("vsa_block_mean_bwd_accumulate", dq.data_ptr(), dqc.data_ptr(), q_sizes.data_ptr(), B * H, Lq, D,
-                 be, dt, st)
-            call("vsa_block_mean_bwd_accumulate", dk.data_ptr(), dkc.data_ptr(), kv_sizes.data_ptr(), B * H, Lkv, D,
-                 be, dt, st)
-            call("vsa_block_mean_bwd_accumulate", dv.data_ptr(), dvc.data_ptr(), kv_sizes.data_ptr(), B * H, Lkv, D,
-                 be, dt, st)
+            # the block-mean backward of the pooled gradients rides on the stores of the fine backward
+            dq, dk, dv = sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale,
+                                         pooled_grads=(dqc, dkc, dvc, q_sizes))
         return dq, dk, dv, dgate, None, None, None, None, None, None
 
 

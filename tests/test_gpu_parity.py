@@ -539,3 +539,43 @@ def test_pooled_attention_tensor_core_path_matches_scalar_path(Qb, Kb, monkeypat
     torch.testing.assert_close(fast[2].float(), ref, atol=2e-2, rtol=2e-2)
     for got, leaf in zip(fast[3:], (ql, kl, vl)):
         torch.testing.assert_close(got.float(), leaf.grad, atol=3e-2, rtol=3e-2)
+
+
+def test_fused_block_mean_backward_equals_the_two_step_form():
+    """vsa_sparse_bwd_dq_fused / _dkdv_fused = plain backward + vsa_block_mean_bwd_accumulate, up to the one
+    rounding the fusion saves; ragged sizes, an unselected key block and a wholly padded tail included."""
+    from simple_vsa_b200 import ops
+    torch.manual_seed(77)
+    B, H, nb, be, D, tk = 1, 2, 12, 64, 128, 3
+    L = nb * be
+    q, k, v, dout = (torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16) for _ in range(4))
+    kv_sizes = torch.full((nb,), be, dtype=torch.int32, device=DEV)
+    kv_sizes[2], kv_sizes[5], kv_sizes[11] = 37, 1, 0
+    q_sizes = torch.full((nb,), be, dtype=torch.int32, device=DEV)
+    q_sizes[1], q_sizes[7] = 50, 3
+    # block 9 is never selected: its dK/dV come from the pooled gradients alone; block 11 (all padding) is selected
+    pool = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 8, 10, 11], device=DEV)
+    selected = torch.stack([pool[torch.randperm(pool.numel(), device=DEV)[:tk]] for _ in range(B * H * nb)])
+    selected = selected.view(B, H, nb, tk).to(torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    out_s, lse = ops.sparse_forward(q, k, v, selected, kv_sizes, be, scale, True)
+    dqc, dkc, dvc = (torch.randn(B, H, nb, D, device=DEV).to(torch.bfloat16) for _ in range(3))
+    fused = ops.sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale,
+                                pooled_grads=(dqc, dkc, dvc, q_sizes))
+    plain = ops.sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale)
+    st = torch.cuda.current_stream().cuda_stream
+    from simple_vsa_b200 import _lib
+    for g, m, sizes in zip(plain, (dqc, dkc, dvc), (q_sizes, kv_sizes, kv_sizes)):
+        _lib.call("vsa_block_mean_bwd_accumulate", g.data_ptr(), m.data_ptr(), sizes.data_ptr(), B * H, L, D, be,
+                  _lib.VSA_BF16, st)
+    for name, f, p_ in zip(("dq", "dk", "dv"), fused, plain):
+        # dK/dV sums run in a different order from launch to launch (unordered CSR), hence not bitwise
+        _assert_close(f, p_, atol=2e-2, rtol=2e-2)
+        assert torch.isfinite(f.float()).all(), name
+    # rows beyond a block's size receive nothing from the pooled gradient: same values as the plain backward
+    plain2 = ops.sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale)
+    pad_q = (torch.arange(be, device=DEV)[None, :] >= q_sizes[:, None]).reshape(L)
+    assert torch.equal(fused[0][:, :, pad_q], plain2[0][:, :, pad_q])
+    pad_k = (torch.arange(be, device=DEV)[None, :] >= kv_sizes[:, None]).reshape(L)
+    assert float(fused[1][:, :, pad_k].float().abs().max()) == 0.0
+    assert float(fused[2][:, :, pad_k].float().abs().max()) == 0.0
