@@ -16,6 +16,25 @@ from torch import Tensor
 from . import b200_vsa
 
 
+def _chunk_spans(total: int, per_chunk: int):
+    """Chunks of ``per_chunk`` slices with a short ramp at both ends (1, 2, ... slices): the first copy-in and
+    the last copy-out cannot overlap with any compute, so they should be small."""
+    per_chunk = max(1, min(per_chunk, total))
+    head, size = [], 1
+    while size < per_chunk and sum(head) + size <= total // 4:
+        head.append(size)
+        size *= 2
+    tail = list(reversed(head))
+    middle = total - sum(head) - sum(tail)
+    sizes = head + [per_chunk] * (middle // per_chunk) + ([middle % per_chunk] if middle % per_chunk else []) + tail
+    spans, lo = [], 0
+    for n in sizes:
+        spans.append((lo, lo + n))
+        lo += n
+    assert lo == total
+    return spans
+
+
 def vsa_step_from_host(q: Tensor, k: Tensor, v: Tensor, dout: Tensor, variable_block_sizes: Tensor,
                        q_variable_block_sizes: Tensor, topk: int, block_size, gate: Optional[Tensor] = None, *,
                        out: Dict[str, Tensor], device=None, slices_per_chunk: int = 8) -> None:
@@ -35,8 +54,8 @@ def vsa_step_from_host(q: Tensor, k: Tensor, v: Tensor, dout: Tensor, variable_b
     host_out = {n: t.reshape(1, BH, L, D) for n, t in out.items()}
     copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     compute = torch.cuda.current_stream(device)
-    spans = [(s, min(BH, s + slices_per_chunk)) for s in range(0, BH, slices_per_chunk)]
-    width = spans[0][1] - spans[0][0]
+    spans = _chunk_spans(BH, slices_per_chunk)
+    width = max(hi - lo for lo, hi in spans)
     # two fixed sets of device input buffers (no allocator traffic between streams); results are the
     # operator's own fresh tensors and are kept referenced until their copy-out has finished
     ring = [{n: torch.empty((1, width, host_in[n].shape[2], D), device=device, dtype=q.dtype) for n in names}
