@@ -105,6 +105,7 @@ __device__ __forceinline__ void report_timeout(int code) { atomicCAS(&g_device_s
 #define VSA_WAIT(bar_, parity_) mbar_wait((bar_), (parity_), &g_device_status)
 #define VSA_WARP_WAIT(bar_, parity_) warp_wait((bar_), (parity_), &g_device_status, lane)
 #define VSA_WARP_WAIT2(a_, pa_, b_, pb_) warp_wait2((a_), (pa_), (b_), (pb_), &g_device_status, lane)
+#define VSA_WARP_WAIT_TEST(a_, pa_, b_, pb_, done_) warp_wait_and_test((a_), (pa_), (b_), (pb_), &g_device_status, lane, (done_))
 
 // One 64x128 tile = two boxes (head-dim halves); `dst` is the row offset inside a stacked pair.
 __device__ __forceinline__ void load_tile(uint32_t pair_base, int half_rows_off, const CUtensorMap* map, int row,

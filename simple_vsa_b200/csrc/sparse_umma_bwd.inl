@@ -290,7 +290,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         pf[4 * j4 + 2] = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -l4.z));
         pf[4 * j4 + 3] = fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -l4.w));
       }
-      ok = VSA_WARP_WAIT(bar(DQ_DP_FULL + b), (p / kDqBufs) & 1);
+      bool ds_free;
+      ok = VSA_WARP_WAIT_TEST(bar(DQ_DP_FULL + b), (p / kDqBufs) & 1, bar(DQ_DS_EMPTY), (p & 1) ^ 1, &ds_free);
       if (!ok) break;
       tc_fence_after();
       uint32_t dv[kBwCols];
@@ -313,7 +314,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int j = 0; j < kBwCols / 2; ++j) packed[j] = 0u;
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
-      ok = VSA_WARP_WAIT(bar(DQ_DS_EMPTY), (p & 1) ^ 1);
+      if (!ds_free) ok = VSA_WARP_WAIT(bar(DQ_DS_EMPTY), (p & 1) ^ 1);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(8, p);
       uint8_t* drow = sm + DqSmem::ds + t * 128;
@@ -598,7 +599,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
       }
       // ---- P from S, published before dP is even looked at (the dP MMAs are still running)
-      ok = VSA_WARP_WAIT(bar(DK_S_FULL + b), (p / kDkBufs) & 1);
+      bool p_free, ds_free;       // looked at together with the blocking waits: usually already true
+      ok = VSA_WARP_WAIT_TEST(bar(DK_S_FULL + b), (p / kDkBufs) & 1, bar(DK_P_EMPTY), (p & 1) ^ 1, &p_free);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
@@ -616,7 +618,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           pf[j] = (c0 + j) < valid ? fast_exp2(fmaf(__uint_as_float(sv[j]), c, -lse)) : 0.f;
       }
       if (tid == 128) VSA_TRACE_AT(7, p);
-      ok = VSA_WARP_WAIT(bar(DK_P_EMPTY), (p & 1) ^ 1);      // dV^T of the previous pair has read the buffer
+      if (!p_free) ok = VSA_WARP_WAIT(bar(DK_P_EMPTY), (p & 1) ^ 1);      // dV^T of the previous pair has read the buffer
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(8, p);
 #pragma unroll
@@ -629,7 +631,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (lane == 0) mbar_arrive(bar(DK_P_FULL));
       if (tid == 128) VSA_TRACE_AT(9, p);
       // ---- dS = P * (dP - delta)
-      ok = VSA_WARP_WAIT(bar(DK_DP_FULL + b), (p / kDkBufs) & 1);
+      ok = VSA_WARP_WAIT_TEST(bar(DK_DP_FULL + b), (p / kDkBufs) & 1, bar(DK_DS_EMPTY), (p & 1) ^ 1, &ds_free);
       if (!ok) break;
       if (tid == 128) VSA_TRACE_AT(12, p);
       tc_fence_after();
@@ -653,7 +655,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           pg[j2] = pack_bf16(g0, g1);
         }
       }
-      ok = VSA_WARP_WAIT(bar(DK_DS_EMPTY), (p & 1) ^ 1);     // dK^T of the previous pair has read the buffer
+      if (!ds_free) ok = VSA_WARP_WAIT(bar(DK_DS_EMPTY), (p & 1) ^ 1);     // dK^T of the previous pair has read the buffer
       if (!ok) break;
 #pragma unroll
       for (int ch = 0; ch < kBwCols / 8; ++ch)

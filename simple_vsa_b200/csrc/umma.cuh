@@ -88,6 +88,32 @@ __device__ __forceinline__ bool warp_wait2(uint32_t bar_a, uint32_t parity_a, ui
   return __all_sync(0xffffffffu, ok) != 0;
 }
 
+// Wait for barrier A and, in the same shared-memory round trip, LOOK at barrier B (mbarrier.test_wait: no
+// suspension).  Returns false on a time-out of A; *b_done tells whether B's phase had completed.  For a second
+// barrier that is needed a few hundred cycles later and has usually flipped by now: the later blocking wait (and
+// its ~180-cycle round trip) is then skipped.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool warp_wait_and_test(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b,
+                                                   const volatile int* abort_flag, int lane, bool* b_done) {
+  int ok = 1, done = 1;
+  if (lane == 0) {
+    if (!mbar_try_wait(bar_a, parity_a)) ok = mbar_wait(bar_a, parity_a, abort_flag) ? 1 : 0;
+  } else if (lane == 1) {
+    done = mbar_test(bar_b, parity_b) ? 1 : 0;
+  }
+  __syncwarp();
+  *b_done = __all_sync(0xffffffffu, done) != 0;
+  return __all_sync(0xffffffffu, ok) != 0;
+}
+
 // ---- fences ----------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
