@@ -1,4 +1,4 @@
-// sm_100a building blocks: mbarriers with bounded waits, TMA tile loads (never multicast),
+// sm_100a building blocks: mbarriers with bounded waits, TMA tile loads (plain: every CTA fetches its own boxes),
 // tensor-memory allocation, tcgen05.mma with shared-memory operand descriptors, tcgen05.ld.
 #pragma once
 
@@ -119,7 +119,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// ---- TMA: one 2-D box global -> shared, completion counted on an mbarrier (no multicast) ------
+// ---- TMA: one 2-D box global -> shared, completion counted on an mbarrier (plain form, one CTA) ------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
