@@ -81,3 +81,22 @@ def test_product_package_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("oracle form", ""), f"{f} mentions the oracle"
+
+
+def test_compression_gate_shape_layout_and_argument_check():
+    """Mirrors the reference's CompressionGate tests (tests/test_common.py:24-61): [B,S,dim] -> [B,H,S,D],
+    and a ``ValueError`` containing "divisible" for a head count that does not divide dim."""
+    import torch
+
+    import simple_vsa_b200 as V
+    torch.manual_seed(0)
+    batch, heads, seq, head_dim = 2, 3, 12, 8
+    layer = V.CompressionGate(dim=heads * head_dim, num_heads=heads)
+    hidden = torch.randn(batch, seq, heads * head_dim)
+    gate = layer(hidden)
+    assert gate.shape == (batch, heads, seq, head_dim)
+    # head h, token s, channel d of the gate is channel h*head_dim + d of the linear layer's output
+    want = layer.to_gate_compress(hidden)
+    assert torch.equal(gate[1, 2, 5], want[1, 5, 2 * head_dim:3 * head_dim])
+    with pytest.raises(ValueError, match="divisible"):
+        V.CompressionGate(dim=10, num_heads=3)

@@ -579,3 +579,27 @@ def test_fused_block_mean_backward_equals_the_two_step_form():
     pad_k = (torch.arange(be, device=DEV)[None, :] >= kv_sizes[:, None]).reshape(L)
     assert float(fused[1][:, :, pad_k].float().abs().max()) == 0.0
     assert float(fused[2][:, :, pad_k].float().abs().max()) == 0.0
+
+
+def test_compression_gate_trains_through_the_operator():
+    """The gate layer sits outside the operator; its weights must receive gradient through the pooled branch
+    (mirrors tests/test_common.py:33-55 of the reference; block of 4 tokens, D = 8: the CUDA-core path)."""
+    V = _V()
+    torch.manual_seed(1)
+    batch, heads, head_dim, be, nb = 1, 2, 8, 4, 3
+    seq, dim = be * nb, heads * head_dim
+    hidden = torch.randn(batch, seq, dim, device=DEV)
+    q, k, v = (torch.randn(batch, heads, seq, head_dim, device=DEV) for _ in range(3))
+    vbs = torch.full((nb,), be, dtype=torch.long, device=DEV)
+    layer = V.CompressionGate(dim=dim, num_heads=heads).to(DEV)
+    out = V.video_sparse_attn(q, k, v, vbs, vbs, 2, (1, 1, be), layer(hidden))
+    out.square().mean().backward()
+    grad = layer.to_gate_compress.weight.grad
+    assert grad is not None and torch.isfinite(grad).all() and float(grad.abs().sum()) > 0
+    # same value as the oracle on the CPU
+    layer_c = V.CompressionGate(dim=dim, num_heads=heads)
+    layer_c.load_state_dict({n: t.cpu() for n, t in layer.state_dict().items()})
+    want = O.vsa(q.cpu(), k.cpu(), v.cpu(), vbs.cpu(), vbs.cpu(), 2, (1, 1, be), layer_c(hidden.cpu()))
+    want.square().mean().backward()
+    _assert_close(out.detach(), want.detach(), atol=1e-5, rtol=1e-5)
+    _assert_close(grad, layer_c.to_gate_compress.weight.grad, atol=1e-5, rtol=1e-4)
