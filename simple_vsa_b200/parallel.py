@@ -70,10 +70,21 @@ def gather_sequence(x: Tensor, group=None) -> Tensor:
     return _GatherSequence.apply(x, group)
 
 
+def _head_chunks(heads: int, chunks: int):
+    chunks = max(1, min(chunks, heads))
+    per, extra = divmod(heads, chunks)
+    spans, lo = [], 0
+    for i in range(chunks):
+        n = per + (1 if i < extra else 0)
+        spans.append((lo, lo + n))
+        lo += n
+    return spans
+
+
 def sequence_parallel_vsa(q_local: Tensor, k_local: Tensor, v_local: Tensor, variable_block_sizes: Tensor,
                           q_variable_block_sizes_local: Tensor, topk: int, block_size=64,
                           compress_attn_weight_local: Optional[Tensor] = None, *, group=None,
-                          local_op: Optional[Callable] = None) -> Tensor:
+                          local_op: Optional[Callable] = None, head_chunks: int = 4) -> Tensor:
     """VSA with the sequence split over the ranks of ``group``.
 
     ``q_local/k_local/v_local`` are this rank's ``[B,H,L/W,D]`` shards (rank r holds tokens
@@ -81,11 +92,59 @@ def sequence_parallel_vsa(q_local: Tensor, k_local: Tensor, v_local: Tensor, var
     ``variable_block_sizes`` lists ALL key blocks, ``q_variable_block_sizes_local`` this rank's query
     blocks.  Returns the local ``[B,H,L/W,D]`` output; gradients reach the local q/k/v (dK/dV are
     summed over ranks by the reduce-scatter) and the local gate.  ``local_op`` defaults to the CUDA
-    operator and exists so that the glue can be exercised on CPU ranks with a stand-in.
+    operator and exists so that the glue can be exercised on CPU ranks with a stand-in.  The heads are
+    processed in ``head_chunks`` groups so that the collectives of one group overlap the kernels of another.
     """
     if local_op is None:
         from . import b200_vsa as local_op
-    k_full = gather_sequence(k_local, group)
-    v_full = gather_sequence(v_local, group)
-    return local_op(q_local, k_full, v_full, variable_block_sizes, q_variable_block_sizes_local, topk, block_size,
-                    compress_attn_weight_local)
+    H = q_local.shape[1]
+    spans = _head_chunks(H, head_chunks)
+    on_gpu = q_local.is_cuda
+    if len(spans) == 1 or not on_gpu:
+        outs = []
+        for h0, h1 in spans:     # same arithmetic as the overlapped form below, on one stream
+            gate = compress_attn_weight_local[:, h0:h1] if compress_attn_weight_local is not None else None
+            outs.append(local_op(q_local[:, h0:h1], gather_sequence(k_local[:, h0:h1], group),
+                                 gather_sequence(v_local[:, h0:h1], group), variable_block_sizes,
+                                 q_variable_block_sizes_local, topk, block_size, gate))
+        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
+
+    # Heads are independent, so the exchange of one group of heads can run while another group computes.  The
+    # gathers are issued on a side stream one group ahead of the compute; autograd runs each node's backward on
+    # the stream of its forward, so the reduce-scatter of a group's dK/dV likewise overlaps the backward
+    # compute of the group before it.  Exposed communication: the first gather and the last reduce-scatter.
+    main = torch.cuda.current_stream(q_local.device)
+    comm = _comm_stream(q_local.device)
+
+    def start_gather(h0, h1):
+        comm.wait_stream(main)                  # the shards (and whatever produced them) are ready
+        with torch.cuda.stream(comm):
+            kf = gather_sequence(k_local[:, h0:h1], group)
+            vf = gather_sequence(v_local[:, h0:h1], group)
+            done = torch.cuda.Event()
+            done.record(comm)
+        return kf, vf, done
+
+    pending = [start_gather(*spans[0])]
+    outs = []
+    for i, (h0, h1) in enumerate(spans):
+        if i + 1 < len(spans):
+            pending.append(start_gather(*spans[i + 1]))
+        kf, vf, done = pending[i]
+        main.wait_event(done)
+        kf.record_stream(main)
+        vf.record_stream(main)
+        gate = compress_attn_weight_local[:, h0:h1] if compress_attn_weight_local is not None else None
+        outs.append(local_op(q_local[:, h0:h1], kf, vf, variable_block_sizes, q_variable_block_sizes_local, topk,
+                             block_size, gate))
+    return torch.cat(outs, dim=1)
+
+
+_COMM_STREAMS = {}
+
+
+def _comm_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device).index
+    if key not in _COMM_STREAMS:
+        _COMM_STREAMS[key] = torch.cuda.Stream(device)
+    return _COMM_STREAMS[key]
