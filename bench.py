@@ -246,7 +246,12 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        opts = None
+        try:        # NCCL's kernels on a high-priority stream: they must find SMs between our long one-CTA-per-SM kernels
+            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        except Exception:       # noqa: BLE001 - older builds: default options
+            opts = None
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     be = V.as_block_elements(cfg["block_size"])
     L, D, tk = cfg["L"], cfg["D"], cfg["topk"]
     total_slices = cfg["B"] * cfg["H"]
