@@ -431,7 +431,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
       uint32_t sv[kEwCols];
-      tmem_ld16(tmem_s0 + sb * 64 + lane_addr + c0, sv);
+      tmem_ld(tmem_s0 + sb * 64 + lane_addr + c0, sv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
@@ -503,7 +503,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     bf16* stage = reinterpret_cast<bf16*>(sm + FwdSmem::k);     // [64 query rows][128 dims], all MMAs are done
     if (ok && n_pairs > 0) {
       uint32_t ov[kEwCols];
-      tmem_ld16(tmem_o + lane_addr + c0, ov);
+      tmem_ld(tmem_o + lane_addr + c0, ov);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < kEwCols; ++j) {
