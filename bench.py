@@ -45,6 +45,8 @@ WORKLOADS = {
     "c2_16k_be64_tk32_gate": dict(B=1, H=12, L=16384, D=128, block_size=(4, 4, 4), topk=32, gate=True),
     # one tenth of the headline slices, with a gate: the profiling case (2.8 GB on the device, tensors > L2)
     "mid_92k_h8_tk180_gate": dict(B=1, H=8, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=True),
+    # two slices of the headline shape: small enough for multi-pass ncu captures (0.4 GB of tensors + 4.2 GB dS workspace)
+    "prof_92k_h2_tk180": dict(B=1, H=2, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False),
     "small_8k_be64_tk16": dict(B=1, H=8, L=8192, D=128, block_size=(4, 4, 4), topk=16, gate=False),
     # logical 256 blocks, 10 % of them ragged (sizes uniform in [1,255], padded rows zeroed)
     "c3_40k_be256_tk20_ragged": dict(B=1, H=40, L=40960, D=128, block_size=(4, 8, 8), topk=20, gate=False,
@@ -55,6 +57,13 @@ WORKLOADS = {
     "sp_small_32k_be64_tk64": dict(B=1, H=8, L=32768, D=128, block_size=(4, 4, 4), topk=64, gate=False, sp=True),
     # route-explicit executor only: 180 of 1440 key blocks per query block, Zipf(1.1) without replacement
     "c4_92k_routes_zipf": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="zipf"),
+    # the three route kinds of the reference's component bench (examples/bench_components.py:51-63) at the same shape:
+    # uniform = Top-K of random scores, local = the next topk blocks (mod Kb), hotset = every query block reads blocks 0..topk-1
+    "c4_92k_routes_uniform": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="uniform"),
+    "c4_92k_routes_local": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="local"),
+    "c4_92k_routes_hotset": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="hotset"),
+    # the reference's own CPU-runnable case: fp32, 16 full blocks of 64, head dim 64, topk 4 (fp32 runs on the CUDA-core kernels)
+    "c1_1k_be64_tk4_fp32": dict(B=1, H=2, L=1024, D=64, block_size=(1, 1, 64), topk=4, gate=False, dtype="f32"),
 }
 DEFAULT_WORKLOAD = "c5_92k_be64_tk180"
 SEED = 1234
@@ -72,7 +81,7 @@ def measured_peaks():
             p = json.load(fh)
         return dict(tflops=float(p.get("bf16_tflops_sustained", p.get("bf16_tflops"))), hbm=float(p["hbm_gbs"]),
                     source="measured (MEASURED_PEAKS.json, sustained bf16)")
-    return dict(tflops=1400.0, hbm=6650.0, source="fallback (earlier pool measurement, sustained bf16)")
+    return dict(tflops=1590.0, hbm=6650.0, source="fallback (no MEASURED_PEAKS.json: 1590 TFLOP/s bf16, 6650 GB/s)")
 
 
 # --------------------------------------------------------------------------------------------
@@ -139,54 +148,86 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # CPU arm (oracle port of the reference algorithm on a bounded sample)
 # --------------------------------------------------------------------------------------------
-def cpu_sample_setup(cfg, q_blocks: int):
-    """One (batch, head) slice of the workload: full-length K/V, a chunk of ``q_blocks`` query blocks.
+def _reference_torch_vsa():
+    """``vsa.torch_vsa`` of the UNMODIFIED reference package installed under ``baseline/_ref`` (pure PyTorch), or
+    None when that copy is absent or does not import."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "vsa")):
+        return None
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    try:
+        from vsa.torch_impl import torch_vsa
+        return torch_vsa
+    except Exception:       # noqa: BLE001 - any import problem falls back to the port
+        return None
 
-    The pooled branch (block means, scores, Top-K) runs over the whole slice; the fine
-    branch, which carries all the counted FLOPs, runs on the chunk.
+
+def cpu_sample_setup(cfg, q_blocks: int):
+    """One (batch, head) slice of the workload: full-length K/V, the first ``q_blocks`` query blocks.
+
+    The timed code is the reference's own ``torch_vsa`` (``vsa/torch_impl.py:49-113``) when the installed copy
+    imports -- it accepts fewer query tokens than key tokens, so the sample is a plain call of it -- and the
+    oracle port of the same algorithm otherwise.  Small workloads (the reference's CPU case) run whole.
     """
     import torch
     from oracle import vsa_oracle as O
 
     be = O.block_elements(cfg["block_size"])
     L, D, tk = cfg["L"], cfg["D"], cfg["topk"]
+    dt = torch.float32 if cfg.get("dtype") == "f32" else torch.bfloat16
+    whole = cfg["B"] * cfg["H"] * (L // be) <= 64
+    slices = cfg["B"] * cfg["H"] if whole else 1
+    q_blocks = L // be if whole else min(q_blocks, L // be)
     g = torch.Generator().manual_seed(SEED)
-    q = torch.randn(1, 1, L, D, generator=g).to(torch.bfloat16)
-    k = torch.randn(1, 1, L, D, generator=g).to(torch.bfloat16)
-    v = torch.randn(1, 1, L, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(1, slices, q_blocks * be, D, generator=g).to(dt)
+    k = torch.randn(1, slices, L, D, generator=g).to(dt)
+    v = torch.randn(1, slices, L, D, generator=g).to(dt)
     sizes = torch.full((L // be,), be)
-    dout = torch.randn(1, 1, q_blocks * be, D, generator=g)
+    q_sizes = torch.full((q_blocks,), be)
+    dout = torch.randn(1, slices, q_blocks * be, D, generator=g).to(dt)
+    ref = _reference_torch_vsa()
 
     def step():
-        scale = D ** -0.5
-        kl, vl = k.clone().requires_grad_(), v.clone().requires_grad_()
-        ql = q.clone().requires_grad_()
-        scores, out_c = O.coarse_compact(ql, kl, vl, sizes, sizes, be, scale)
-        sel = O.select_topk(scores, tk)[:, :, :q_blocks]
-        qs = ql[:, :, :q_blocks * be]
-        out_s = O.sparse_attention(qs, kl, vl, sel, sizes, be, scale, q_blocks_per_chunk=8)
-        out = O.combine(out_s, out_c[:, :, :q_blocks], None, be, torch.float32)
+        ql, kl, vl = q.clone().requires_grad_(), k.clone().requires_grad_(), v.clone().requires_grad_()
+        if ref is not None:
+            out = ref(ql, kl, vl, sizes, q_sizes, tk, cfg["block_size"], None)
+        else:
+            out = O.vsa(ql, kl, vl, sizes, q_sizes, tk, cfg["block_size"], None, q_blocks_per_chunk=8)
         out.backward(dout)
         return out
 
-    flops = useful_flops(1, q_blocks * be, tk, be, D)
-    sample = (f"oracle (CPU restatement of torch_vsa), 1 of {cfg['B'] * cfg['H']} (batch,head) slices, pooled branch "
-              f"on all {L} tokens, fine branch fwd+bwd on the first {q_blocks} of {L // be} query blocks "
-              f"(topk {tk}, block {be}, D {D}), bf16 inputs, fp32 fine math")
-    return step, flops, sample
+    flops = useful_flops(slices, q_blocks * be, tk, be, D)
+    what = "the reference's own vsa.torch_vsa (installed copy under baseline/_ref)" if ref is not None else \
+        "oracle port (CPU restatement of torch_vsa)"
+    sample = (f"{what}: " + ("the whole workload" if whole else
+              f"1 of {cfg['B'] * cfg['H']} (batch,head) slices, the first {q_blocks} of {L // be} query blocks "
+              f"against all {L // be} key blocks") +
+              f" (topk {tk}, block {be}, D {D}, {'fp32' if dt == torch.float32 else 'bf16 inputs, fp32 fine math'}), "
+              "forward+backward; throughput = the sample's useful FLOPs / its time")
+    return step, flops, sample, ("reference" if ref is not None else "port")
 
 
 def run_cpu(cfg, steps: int, warmup: int, q_blocks: int = 64):
+    """Times the CPU sample with every core this process may use, and once more on one thread."""
     import torch
-    step, flops, sample = cpu_sample_setup(cfg, q_blocks)
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)        # torch.distributed.run exports OMP_NUM_THREADS=1: do not inherit that
+    step, flops, sample, kind = cpu_sample_setup(cfg, q_blocks)
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / max(1, steps)
-    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
-                sample=sample, ms_per_step=dt * 1e3)
+    torch.set_num_threads(1)
+    step()
+    t0 = time.perf_counter()
+    step()
+    dt1 = time.perf_counter() - t0
+    torch.set_num_threads(cores)
+    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=cores, kind=kind, sample=sample,
+                ms_per_step=dt * 1e3, one_thread_value=flops / dt1 / 1e12, one_thread_ms_per_step=dt1 * 1e3)
 
 
 # --------------------------------------------------------------------------------------------
@@ -389,13 +430,19 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     flops_total = useful_flops(total_slices, L, tk, be, D)
     peaks = measured_peaks()
     # dominant kernel by total device time
-    fine = {n: kernels[n] for n in ("vsa_sparse_fwd", "vsa_sparse_bwd_dq", "vsa_sparse_bwd_dkdv") if n in kernels}
+    # GEMM FLOPs a kernel's algorithm performs per edge (units of be^2*D): forward S,O = 4; recomputing dQ pass S,dP,dQ = 6;
+    # dK/dV pass S,dP,dK,dV = 8 (with or without the dS stores); dQ from stored dS = 2
+    gemm_units = {"vsa_sparse_fwd": 4, "vsa_sparse_bwd_dq": 6, "vsa_sparse_bwd_dkdv": 8, "vsa_sparse_bwd_dkdv_ds": 8,
+                  "vsa_sparse_bwd_dq_from_ds": 2}
+    fine = {n: kernels[n] for n in gemm_units if n in kernels}
     top = max(fine, key=lambda n: fine[n]["total_ms"])
-    # GEMM FLOPs the kernel's algorithm performs per edge: forward S,O = 4; dQ pass S,dP,dQ = 6; dK/dV pass S,dP,dK,dV = 8
-    per_edge = {"vsa_sparse_fwd": 4, "vsa_sparse_bwd_dq": 6, "vsa_sparse_bwd_dkdv": 8}[top]
+    per_edge = gemm_units[top]
+    # a kernel may be launched several times per step (groups of slices, head groups): its launches of one step
+    # together cover every edge of this rank once, so the rate is edges per step over its time per step
     edges = count * (l_loc // be) * tk
-    flops_launch = per_edge * float(be) * be * D * edges
-    achieved = flops_launch / (fine[top]["avg_ms"] * 1e-3) / 1e12
+    flops_step = per_edge * float(be) * be * D * edges
+    top_ms_per_step = fine[top]["total_ms"] / args.steps
+    achieved = flops_step / (top_ms_per_step * 1e-3) / 1e12
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
@@ -438,10 +485,12 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["tflops"],
                      "unit": "TFLOP/s", "frac": achieved / peaks["tflops"], "traffic": traffic,
                      "peak_source": peaks["source"], "avg_launch_ms": fine[top]["avg_ms"],
+                     "launches_per_step": fine[top]["launches"] / args.steps, "ms_per_step": top_ms_per_step,
                      "gemm_flops_per_edge_over_be2D": per_edge,
                      "useful_frac_whole_step": flops_total / world / (ms_dev * 1e-3) / 1e12 / peaks["tflops"]},
         "kernel_time_share": shares,
         "kernel_avg_ms": {n: round(kv["avg_ms"], 4) for n, kv in sorted(kernels.items())},
+        "kernel_ms_per_step": {n: round(kv["total_ms"] / args.steps, 4) for n, kv in sorted(kernels.items())},
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu

@@ -56,8 +56,22 @@ int vsa_version(void);
 int64_t vsa_launch_count(void);
 
 /* Device-side status word: 0, or the code of the first bounded wait (mbarrier) that ran out in a
- * tcgen05 kernel since the last call.  Synchronises the device; clears the word. */
+ * tcgen05 kernel since the last call.  Synchronises the device; clears the word.
+ *
+ * Every wait inside the tcgen05 kernels is bounded (250 ms).  When one runs out the CTA records a code
+ * here, stops issuing work, frees its tensor memory and returns; from then on every tcgen05 kernel of this
+ * library returns at its first instruction WITHOUT writing its outputs, until this call has cleared the
+ * word.  The launching entry points cannot see that (they do not synchronise), so a caller that consumes
+ * results must call this after it has synchronised: non-zero means the outputs since the last clear are
+ * not valid.  (The Python layer does so wherever it synchronises anyway and raises VsaError.)
+ * The entry points use the CALLER'S CURRENT DEVICE: set it (cudaSetDevice) to the device that owns the
+ * pointers and the stream before calling; the status word is per device.  No reference counterpart. */
 int vsa_device_status(int* status);
+
+/* Exercises the time-out path without making anything fail: one warp waits up to limit_ns
+ * (1 us .. 100 ms) on a barrier nothing arrives at, gives up, records code 201 in the status word, writes
+ * 1 to *gave_up (a device pointer) and returns.  For tests of the reporting path. */
+int vsa_selftest_wait_timeout(int64_t limit_ns, int* gave_up, void* stream);
 
 /* Unit check of the tcgen05 building blocks (TMA boxes, shared-memory operand descriptors, tensor
  * memory read-out): out[128x64] fp32 = A * B for bf16 operands.  mode 0: a is [128 x 128] with the
@@ -183,6 +197,60 @@ int vsa_sparse_bwd_dkdv_fused(const void* dout, const void* q, const void* k, co
                               const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                               const int32_t* kv_sizes, void* dk, void* dv,
                               const void* dk_mean, const void* dv_mean,
+                              int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                              float scale, int dtype, void* stream);
+
+/* ---- the backward that forms dS once ---------------------------------------------------------------
+ * The two passes above (like _vsa_dq_kernel and _vsa_dkdv_kernel of the reference,
+ * vsa/triton_impl.py:838-1126) each recompute the scores and dP.  The entry points below compute them
+ * once: vsa_sparse_bwd_delta, then vsa_sparse_bwd_dkdv_ds (key-owned; also writes every dS tile), then
+ * vsa_sparse_bwd_dq_from_ds (query-owned; only multiplies the stored tiles by K).  Same results within
+ * rounding, deterministic, 16 of 56 tensor-core products per pair of edges fewer -- paid for with 8 KB per
+ * edge written and read back, which on a B200 costs the key-owned pass about what the dQ pass gains; the
+ * Python operator therefore uses it only on request.  Tensor path only: vsa_sparse_bwd_ds_supported() says
+ * whether a shape qualifies (bf16, D = 128, be = 64 or 256).
+ *
+ * ds_ws holds one bf16 tile of 64 query rows x 64 key tokens (8 KB, stored as 8 chunks of 8 key tokens, each
+ * chunk [64 rows][16 bytes]) per (query tile, selected key tile):
+ * vsa_sparse_bwd_ds_workspace_bytes(BH, Lq, be, topk) bytes in all, BH*Qb*topk*(be/64)^2 tiles, tile index
+ * ((edge * be/64 + query sub-tile) * be/64 + key sub-tile) with edge = (bh*Qb + query block)*topk + slot.
+ * At 2.1 GB per slice for 92,160 tokens x topk 180, callers with many slices run the two passes over groups
+ * of slices (every pointer advanced to the group's first slice, BH = slices in the group). */
+
+/* vsa_route_invert with each in-edge recorded as (query block << 11) | slot, slot = position of the key
+ * block in that query block's row of `selected` (so the entry names the edge).  Needs topk <= 2048 and
+ * Qb < 2^20.  Extends _invert_indices: vsa/triton_impl.py:544-595. */
+int vsa_route_invert_edges(const int32_t* selected, int32_t* counts, int32_t* offsets,
+                           int32_t* inverse_edges, int32_t* cursor_ws,
+                           int64_t BH, int Qb, int Kb, int topk, void* stream);
+
+/* delta[row] = sum_d out_s[row, d] * dout[row, d] in fp32.
+ * Replaces _delta_kernel / _delta_256_kernel: vsa/triton_impl.py:598-700. */
+int vsa_sparse_bwd_delta(const void* out_s, const void* dout, float* delta,
+                         int64_t BH, int64_t Lq, int D, int dtype, void* stream);
+
+/* 1 if the two entry points below cover (D, be, topk, dtype) in this process, else 0. */
+int vsa_sparse_bwd_ds_supported(int D, int be, int topk, int dtype);
+
+/* Size of ds_ws in bytes (see above); -1 for a block volume that is not a multiple of 64. */
+int64_t vsa_sparse_bwd_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk);
+
+/* vsa_sparse_bwd_dkdv_fused over packed edges, also writing dS = P * (dP - delta) (not yet times scale) of
+ * every edge tile to ds_ws.  dk_mean and dv_mean may both be NULL (no pooled gradients folded in).
+ * Replaces _vsa_dkdv_kernel / _vsa_dkdv_256_kernel: vsa/triton_impl.py:972-1318. */
+int vsa_sparse_bwd_dkdv_ds(const void* dout, const void* q, const void* k, const void* v,
+                           const float* lse2, const float* delta,
+                           const int32_t* counts, const int32_t* offsets, const int32_t* inverse_edges,
+                           const int32_t* kv_sizes, void* dk, void* dv,
+                           const void* dk_mean, const void* dv_mean, void* ds_ws,
+                           int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                           float scale, int dtype, void* stream);
+
+/* dq = scale * sum over the selected key tiles of dS K (+ dq_mean[block] / max(q_sizes[block], 1) on the
+ * block's valid rows when dq_mean and q_sizes are given; both may be NULL).  Ids in `selected` outside
+ * [0, Kb) count as empty blocks.  Replaces _vsa_dq_kernel / _vsa_dq_256_kernel: vsa/triton_impl.py:703-969. */
+int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int32_t* kv_sizes,
+                              const void* ds_ws, void* dq, const void* dq_mean, const int32_t* q_sizes,
                               int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                               float scale, int dtype, void* stream);
 

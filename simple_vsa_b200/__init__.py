@@ -60,8 +60,10 @@ def video_sparse_attn(q: Tensor, k: Tensor, v: Tensor, variable_block_sizes: Ten
     if not return_aux:
         return out
     mask = torch.zeros_like(scores, dtype=torch.bool).scatter_(-1, selected.long(), True)
+    be = as_block_elements(block_size)
     return out, {"coarse_scores": scores, "block_mask": mask, "selected": selected,
-                 "out_compress": out_c, "out_sparse": out_s}
+                 "out_compress": out_c.repeat_interleave(be, dim=2), "out_compress_blocks": out_c,
+                 "out_sparse": out_s}
 
 
 def b200_vsa(q, k, v, variable_block_sizes, q_variable_block_sizes, topk, block_size: BlockSize = 64,

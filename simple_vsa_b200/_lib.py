@@ -34,14 +34,21 @@ SIGNATURES = {
     "vsa_sparse_bwd_dkdv": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dq_fused": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dkdv_fused": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
+    "vsa_route_invert_edges": [P, P, P, P, P, L, I, I, I, P],
+    "vsa_sparse_bwd_delta": [P, P, P, L, L, I, I, P],
+    "vsa_sparse_bwd_dkdv_ds": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_bwd_dq_from_ds": [P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_combine_fwd": [P, P, P, P, L, L, I, I, I, P],
     "vsa_gather_rows": [P, P, P, L, L, L, L, P],
     "vsa_selftest_umma": [P, P, P, I, P],
     "vsa_device_status": [P],
+    "vsa_selftest_wait_timeout": [L, P, P],
     "vsa_combine_bwd": [P, P, P, P, P, L, L, I, I, I, P],
 }
 PLAIN = {"vsa_last_error_string": ([], c_char_p), "vsa_version": ([], c_int),
-         "vsa_launch_count": ([], c_int64)}
+         "vsa_launch_count": ([], c_int64),
+         "vsa_sparse_bwd_ds_supported": ([I, I, I, I], c_int),
+         "vsa_sparse_bwd_ds_workspace_bytes": ([L, L, I, I], c_int64)}
 
 
 class VsaError(RuntimeError):
@@ -75,6 +82,17 @@ def device_status() -> int:
     if rc:
         raise VsaError(f"vsa_device_status: {last_error()}")
     return out.value
+
+
+def raise_on_device_timeout(where: str) -> None:
+    """For callers that have just synchronised: raise if a bounded device-side wait ran out since the last check.
+
+    After a time-out every tcgen05 kernel returns without writing its outputs until the word is cleared, so the
+    results produced since then are not valid; the word is cleared by this call."""
+    code = device_status()
+    if code:
+        raise VsaError(f"{where}: a bounded device-side wait ran out (code {code}, status {ERR_DEVICE_TIMEOUT}); "
+                       "results since the last check are not valid")
 
 
 def last_error() -> str:

@@ -276,6 +276,66 @@ int vsa_sparse_bwd_dkdv_fused(const void* dout, const void* q, const void* k, co
   return block_mean_bwd(dv, dv_mean, kv_sizes, BH, Lkv, D, be, dtype, true, (cudaStream_t)stream);
 }
 
+// ---- the backward that forms dS once ---------------------------------------------------------------------
+// vsa_sparse_bwd_dq + vsa_sparse_bwd_dkdv compute the scores and dP twice, once per pass (as the reference's
+// _vsa_dq_kernel / _vsa_dkdv_kernel do).  The three entry points below compute them once: delta first, then the
+// key-owned pass, which also writes every dS tile into a workspace, then a query-owned pass that only multiplies
+// the stored tiles by K.  Tensor path only (vsa_sparse_bwd_ds_supported tells); the workspace holds 8 KB per
+// (query tile, selected key tile), so callers with many slices run the two passes over groups of slices.
+int vsa_route_invert_edges(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse_edges,
+                           int32_t* cursor_ws, int64_t BH, int Qb, int Kb, int topk, void* stream) {
+  VSA_REQUIRE(selected && counts && offsets && inverse_edges && cursor_ws, "route inversion: null pointer");
+  VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && topk >= 1, "route inversion: bad extents");
+  return route_invert(selected, counts, offsets, inverse_edges, cursor_ws, BH, Qb, Kb, topk, (cudaStream_t)stream, true);
+}
+
+int vsa_sparse_bwd_delta(const void* out_s, const void* dout, float* delta, int64_t BH, int64_t Lq, int D, int dtype,
+                         void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(out_s && dout && delta, "sparse delta: null pointer");
+  VSA_REQUIRE(BH >= 0 && Lq >= 0 && D >= 1, "sparse delta: bad extents");
+  return rowdot_rows(out_s, dout, delta, BH * Lq, D, dtype, (cudaStream_t)stream);
+}
+
+int vsa_sparse_bwd_ds_supported(int D, int be, int topk, int dtype) {
+  return !scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk) && topk <= 2048 ? 1 : 0;
+}
+
+int64_t vsa_sparse_bwd_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk) {
+  if (BH < 0 || Lq < 0 || be < 64 || be % 64 || topk < 0) return -1;
+  return sparse_ds_workspace_bytes(BH, Lq, be, topk);
+}
+
+int vsa_sparse_bwd_dkdv_ds(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                           const float* delta, const int32_t* counts, const int32_t* offsets,
+                           const int32_t* inverse_edges, const int32_t* kv_sizes, void* dk, void* dv,
+                           const void* dk_mean, const void* dv_mean, void* ds_ws, int64_t BH, int64_t Lq, int64_t Lkv,
+                           int D, int be, int topk, float scale, int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && q && k && v && lse2 && delta && counts && offsets && inverse_edges && kv_sizes && dk && dv && ds_ws,
+              "sparse dK/dV (dS stored): null pointer");
+  VSA_REQUIRE((dk_mean == nullptr) == (dv_mean == nullptr), "sparse dK/dV (dS stored): give both pooled gradients or neither");
+  if (!vsa_sparse_bwd_ds_supported(D, be, topk, dtype))
+    return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV (dS stored): needs bf16, head dim 128, block volume 64 or 256");
+  return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse_edges, kv_sizes, dk, dv, BH, Lq, Lkv, be,
+                          topk, scale, (cudaStream_t)stream, dk_mean, dv_mean, ds_ws);
+}
+
+int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int32_t* kv_sizes, const void* ds_ws,
+                              void* dq, const void* dq_mean, const int32_t* q_sizes, int64_t BH, int64_t Lq,
+                              int64_t Lkv, int D, int be, int topk, float scale, int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(k && selected && kv_sizes && ds_ws && dq, "sparse dQ (from dS): null pointer");
+  VSA_REQUIRE((dq_mean == nullptr) == (q_sizes == nullptr), "sparse dQ (from dS): give the pooled gradient and the query sizes, or neither");
+  if (!vsa_sparse_bwd_ds_supported(D, be, topk, dtype))
+    return fail(VSA_ERR_UNSUPPORTED, "sparse dQ (from dS): needs bf16, head dim 128, block volume 64 or 256");
+  return sparse_dq_from_ds_umma(k, selected, kv_sizes, ds_ws, dq, BH, Lq, Lkv, be, topk, scale, (cudaStream_t)stream,
+                                dq_mean, q_sizes);
+}
+
 int vsa_gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
                     int64_t row_bytes, void* stream) {
   VSA_REQUIRE(src && map && dst, "gather rows: null pointer");
@@ -286,6 +346,12 @@ int vsa_gather_rows(const void* src, const int32_t* map, void* dst, int64_t batc
 int vsa_selftest_umma(const void* a, const void* b, float* out, int mode, void* stream) {
   VSA_REQUIRE(a && b && out && (mode == 0 || mode == 1), "selftest: bad argument");
   return umma_selftest(a, b, out, mode, (cudaStream_t)stream);
+}
+
+int vsa_selftest_wait_timeout(int64_t limit_ns, int* gave_up, void* stream) {
+  VSA_REQUIRE(gave_up, "wait self-test: null pointer");
+  VSA_REQUIRE(limit_ns >= 1000 && limit_ns <= 100000000LL, "wait self-test: the limit must lie in [1 us, 100 ms]");
+  return wait_timeout_selftest((unsigned long long)limit_ns, gave_up, (cudaStream_t)stream);
 }
 
 int vsa_device_status(int* status) {

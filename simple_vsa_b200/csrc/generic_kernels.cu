@@ -738,9 +738,16 @@ __global__ void __launch_bounds__(256) route_scan_kernel(const int32_t* __restri
   }
 }
 
+// What a row of the inverse table holds per in-edge: the query block id (the reference's table), or, packed,
+// (query block << 11) | position of the key block in that query block's route -- which names the edge itself.
+__device__ __forceinline__ int32_t route_entry(int edge_in_slice, int topk, bool packed) {
+  const int qb = edge_in_slice / topk;
+  return packed ? (int32_t)((qb << 11) | (edge_in_slice - qb * topk)) : (int32_t)qb;
+}
+
 __global__ void route_scatter_kernel(const int32_t* __restrict__ selected, int32_t* __restrict__ cursor,
                                      int32_t* __restrict__ inverse, long long edges_total, int edges_per_bh, int Kb,
-                                     int topk) {
+                                     int topk, bool packed) {
   const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= edges_total) return;
   const long long bh = e / edges_per_bh;
@@ -748,7 +755,7 @@ __global__ void route_scatter_kernel(const int32_t* __restrict__ selected, int32
   const int kv = selected[e];
   if ((unsigned)kv >= (unsigned)Kb) return;
   const int slot = atomicAdd(&cursor[bh * Kb + kv], 1);
-  inverse[bh * edges_per_bh + slot] = within / topk;
+  inverse[bh * edges_per_bh + slot] = route_entry(within, topk, packed);
 }
 
 // Chunked forms of the two passes for key-block counts that fit in shared memory: a CTA owns a contiguous chunk
@@ -782,7 +789,7 @@ route_count_chunk_kernel(const int32_t* __restrict__ selected, int32_t* __restri
 
 __global__ void __launch_bounds__(kRouteChunkThreads)
 route_scatter_chunk_kernel(const int32_t* __restrict__ selected, int32_t* __restrict__ cursor,
-                           int32_t* __restrict__ inverse, int edges_per_bh, int chunk, int Kb, int topk) {
+                           int32_t* __restrict__ inverse, int edges_per_bh, int chunk, int Kb, int topk, bool packed) {
   extern __shared__ int32_t route_sm[];
   int32_t* hist = route_sm;            // count of this chunk per key block, then the first claimed slot
   int32_t* next = route_sm + Kb;       // slots handed out so far inside the claimed run
@@ -808,13 +815,15 @@ route_scatter_chunk_kernel(const int32_t* __restrict__ selected, int32_t* __rest
   for (int e = e0 + threadIdx.x; e < e1; e += kRouteChunkThreads) {
     const int kv = sel[e];
     if ((unsigned)kv >= (unsigned)Kb) continue;
-    inv[hist[kv] + atomicAdd(&next[kv], 1)] = e / topk;
+    inv[hist[kv] + atomicAdd(&next[kv], 1)] = route_entry(e, topk, packed);
   }
 }
 
 int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int32_t* cursor,
-                 int64_t BH, int Qb, int Kb, int topk, cudaStream_t st) {
+                 int64_t BH, int Qb, int Kb, int topk, cudaStream_t st, bool packed) {
   const long long per = (long long)Qb * topk;
+  if (packed && (topk > 2048 || Qb >= (1 << 20)))
+    return fail(VSA_ERR_UNSUPPORTED, "route inversion: packed edges need topk <= 2048 and fewer than 2^20 query blocks");
   const long long total = BH * per;
   if (BH == 0 || Kb == 0) return VSA_OK;
   if (per > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "route inversion: too many edges per slice");
@@ -843,11 +852,11 @@ int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int
   if (total > 0) {
     if (chunked) {
       route_scatter_chunk_kernel<<<grid, kRouteChunkThreads, 2 * sizeof(int32_t) * Kb, st>>>(selected, cursor, inverse,
-                                                                                            (int)per, chunk, Kb, topk);
+                                                                                            (int)per, chunk, Kb, topk, packed);
       rc = check_launch("route_scatter_chunk_kernel");
     } else {
       const unsigned blocks = (unsigned)((total + 255) / 256);
-      route_scatter_kernel<<<blocks, 256, 0, st>>>(selected, cursor, inverse, total, (int)per, Kb, topk);
+      route_scatter_kernel<<<blocks, 256, 0, st>>>(selected, cursor, inverse, total, (int)per, Kb, topk, packed);
       rc = check_launch("route_scatter_kernel");
     }
   }
@@ -905,7 +914,7 @@ int route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offse
   int32_t* cursor = static_cursor_for_current_device(&rc);
   if (!cursor) return rc;
   // the scan step rewrites every cursor entry it will use, so nothing left by an earlier call survives
-  return route_invert(selected, counts, offsets, inverse, cursor, BH, Qb, Kb, topk, st);
+  return route_invert(selected, counts, offsets, inverse, cursor, BH, Qb, Kb, topk, st, false);
 }
 
 // =========================================================================================
@@ -1124,7 +1133,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_scalar_kernel(const T* __restr
   const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
   for (int s = 0; s < topk; ++s) {
     const int kvb = sel[s];
-    int size = kv_sizes[kvb];
+    int size = (unsigned)kvb < (unsigned)(Lkv / be) ? kv_sizes[kvb] : 0;     // an id outside the table is an empty block
     size = size > be ? be : size;
     const T* kp = k + (bh * Lkv + (long long)kvb * be) * D;
     const T* vp = v + (bh * Lkv + (long long)kvb * be) * D;
@@ -1177,7 +1186,7 @@ __global__ void __launch_bounds__(256) sparse_dq_scalar_kernel(const T* __restri
   const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
   for (int s = 0; s < topk; ++s) {
     const int kvb = sel[s];
-    int size = kv_sizes[kvb];
+    int size = (unsigned)kvb < (unsigned)(Lkv / be) ? kv_sizes[kvb] : 0;     // an id outside the table is an empty block
     size = size > be ? be : size;
     const T* kp = k + (bh * Lkv + (long long)kvb * be) * D;
     const T* vp = v + (bh * Lkv + (long long)kvb * be) * D;

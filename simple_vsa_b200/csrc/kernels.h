@@ -18,8 +18,9 @@ int coarse_bwd(const void* d_out_c, const void* out_c, const void* qc, const voi
 int softmax_rows(const void* scores, void* probs, int64_t rows, int n, int dtype, cudaStream_t st);
 int rowdot_rows(const void* a, const void* b, float* out, int64_t rows, int D, int dtype, cudaStream_t st);
 int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int topk, int dtype, cudaStream_t st);
+// packed: rows hold (query block << 11) | slot of the key block in that query block's route, instead of query block ids
 int route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int32_t* cursor,
-                 int64_t BH, int Qb, int Kb, int topk, cudaStream_t st);
+                 int64_t BH, int Qb, int Kb, int topk, cudaStream_t st, bool packed = false);
 int route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse, int64_t BH,
                         int Qb, int Kb, int topk, cudaStream_t st);
 int gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
@@ -67,7 +68,14 @@ int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                     float scale, cudaStream_t st, const void* dk_mean = nullptr, const void* dv_mean = nullptr);
+                     float scale, cudaStream_t st, const void* dk_mean = nullptr, const void* dv_mean = nullptr,
+                     void* ds_ws = nullptr);
+// the backward that forms dS once: the key-owned pass (above, with ds_ws and packed edges) stores it, this
+// query-owned pass multiplies it by K
+int64_t sparse_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk);
+int sparse_dq_from_ds_umma(const void* k, const int32_t* selected, const int32_t* kv_sizes, const void* ds_ws, void* dq,
+                           int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
+                           const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr);
 bool coarse_umma_eligible(int Qb, int Kb, int D, int dtype);
 int coarse_fwd_umma(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
                     int Qb, int Kb, int D, float scale, cudaStream_t st);
@@ -75,6 +83,7 @@ int coarse_bwd_umma(const void* d_out_c, const void* out_c, const void* qc, cons
                     const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb,
                     int Kb, int D, float scale, cudaStream_t st);
 int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st);
+int wait_timeout_selftest(unsigned long long limit_ns, int* gave_up, cudaStream_t st);
 int device_status_fetch_and_clear(int* status);
 
 }  // namespace vsa

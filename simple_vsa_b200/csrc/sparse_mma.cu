@@ -121,7 +121,8 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
 
   auto tile_valid = [&](int it, int& kvb) -> int {
     kvb = sel[it / SUB];
-    const int left = kv_sizes[kvb] - (it % SUB) * kTile;
+    // an id outside the table is an empty tile, as route inversion treats it
+    const int left = (unsigned)kvb < (unsigned)(Lkv / (kTile * SUB)) ? kv_sizes[kvb] - (it % SUB) * kTile : 0;
     return left < 0 ? 0 : (left > kTile ? kTile : left);
   };
   auto next_live = [&](int it, int& kvb, int& valid) -> int {
@@ -284,7 +285,8 @@ sparse_dq_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, 
 
   auto tile_valid = [&](int it, int& kvb) -> int {
     kvb = sel[it / SUB];
-    const int left = kv_sizes[kvb] - (it % SUB) * kTile;
+    // an id outside the table is an empty tile, as route inversion treats it
+    const int left = (unsigned)kvb < (unsigned)(Lkv / (kTile * SUB)) ? kv_sizes[kvb] - (it % SUB) * kTile : 0;
     return left < 0 ? 0 : (left > kTile ? kTile : left);
   };
   auto next_live = [&](int it, int& kvb, int& valid) -> int {

@@ -83,14 +83,15 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows, 128] bf16 row-major, boxes of 64 rows x 64 columns, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* ptr, int64_t rows, const char* what) {
+// [rows, cols] bf16 row-major (cols = 128: q/k/v-like tensors; cols = 64: stored dS tiles), boxes of 64 rows x 64
+// columns, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int64_t rows, const char* what, int cols = kD) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(VSA_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
   if (reinterpret_cast<uintptr_t>(ptr) % 16) return fail(VSA_ERR_BAD_ARGUMENT, "%s: pointer is not 16-byte aligned", what);
   if (rows > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "%s: %lld rows exceed the TMA coordinate range", what, (long long)rows);
-  const cuuint64_t gdim[2] = {(cuuint64_t)kD, (cuuint64_t)rows};
-  const cuuint64_t gstride[1] = {(cuuint64_t)kD * 2};
+  const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
   const cuuint32_t box[2] = {64, 64};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
@@ -196,6 +197,26 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
   if (warp == 0) tmem_dealloc(tmem, 64);
 }
 
+// ---- bounded-wait self-test ---------------------------------------------------------------------------
+// One warp waits, with a caller-chosen limit, on a barrier that nothing will ever arrive at.  The wait must give
+// up, the code must land in the device status word, and the kernel must return normally: the path every product
+// kernel takes when a producer or a tensor-core commit fails to show up, exercised without making anything fail.
+constexpr int kSelftestTimeoutCode = 201;
+__global__ void __launch_bounds__(32) wait_timeout_selftest_kernel(unsigned long long limit_ns, int* __restrict__ gave_up) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait(bar, 0, &g_device_status, limit_ns);
+    if (!ok) report_timeout(kSelftestTimeoutCode);
+    *gave_up = ok ? 0 : 1;
+  }
+}
+
 // 8 MMAs over the 128-wide reduction, both operands reduction-contiguous ("K-major").
 // a_pair: a stacked pair [2 halves][128 rows][128 B]; b_tile: one tile [2 halves][64 rows][128 B].
 // Descriptors are advanced with one 32-bit add each (offsets in 16-byte units are compile-time constants).
@@ -294,7 +315,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // every thread looks up some of the routed tiles (two dependent global loads, all in flight at once) ...
   for (int it = tid; it < n_iter; it += kFwdThreads) {
     const int kvb = sel[it / SUB];
-    const int left = kv_sizes[kvb] - (it % SUB) * kTile;
+    // an id outside the table is an empty tile, as route inversion treats it
+    const int left = (unsigned)kvb < (unsigned)(Lkv / (kTile * SUB)) ? kv_sizes[kvb] - (it % SUB) * kTile : 0;
     tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
     tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
   }
@@ -611,32 +633,59 @@ int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v
   return check_launch("sparse_dq_umma_kernel");
 }
 
+int64_t sparse_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk) {
+  const int64_t sub = be / kTile;
+  return BH * (Lq / be) * topk * sub * sub * (int64_t)(kTile * kTile * 2);
+}
+
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                     float scale, cudaStream_t st, const void* dk_mean, const void* dv_mean) {
+                     float scale, cudaStream_t st, const void* dk_mean, const void* dv_mean, void* ds_ws) {
   if (BH == 0 || Lkv == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: batch*heads %lld exceeds 65535", (long long)BH);
+  if (ds_ws && topk > (1 << kEdgeSlotBits))
+    return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: packed edges hold at most %d routes per query block", 1 << kEdgeSlotBits);
   CUtensorMap mq, mdo, mk, mv;
   int rc;
   if ((rc = make_map(&mq, q, BH * Lq, "sparse dK/dV (q)"))) return rc;
   if ((rc = make_map(&mdo, dout, BH * Lq, "sparse dK/dV (dout)"))) return rc;
   if ((rc = make_map(&mk, k, BH * Lkv, "sparse dK/dV (k)"))) return rc;
   if ((rc = make_map(&mv, v, BH * Lkv, "sparse dK/dV (v)"))) return rc;
+  if (ds_ws && reinterpret_cast<uintptr_t>(ds_ws) % 16)
+    return fail(VSA_ERR_BAD_ARGUMENT, "sparse dK/dV: the dS workspace is not 16-byte aligned");
   const int smem = DkSmem::total + 1024;
   dim3 grid((unsigned)(Lkv / kTile), (unsigned)BH);
-  if (be == 64) {
-    if ((rc = reserve_smem(sparse_dkdv_umma_kernel<1>, smem, "sparse dK/dV"))) return rc;
-    sparse_dkdv_umma_kernel<1><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse,
-                                                                kv_sizes, (bf16*)dk, (bf16*)dv, (const bf16*)dk_mean,
-                                                                (const bf16*)dv_mean, Lq, Lkv, topk, scale);
-  } else {
-    if ((rc = reserve_smem(sparse_dkdv_umma_kernel<4>, smem, "sparse dK/dV"))) return rc;
-    sparse_dkdv_umma_kernel<4><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse,
-                                                                kv_sizes, (bf16*)dk, (bf16*)dv, (const bf16*)dk_mean,
-                                                                (const bf16*)dv_mean, Lq, Lkv, topk, scale);
-  }
-  return check_launch("sparse_dkdv_umma_kernel");
+  auto launch = [&](auto kern) -> int {
+    if ((rc = reserve_smem(kern, smem, "sparse dK/dV"))) return rc;
+    kern<<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse, kv_sizes, (bf16*)dk,
+                                          (bf16*)dv, (const bf16*)dk_mean, (const bf16*)dv_mean, (bf16*)ds_ws, Lq, Lkv,
+                                          topk, scale);
+    return check_launch("sparse_dkdv_umma_kernel");
+  };
+  if (be == 64) return ds_ws ? launch(sparse_dkdv_umma_kernel<1, true>) : launch(sparse_dkdv_umma_kernel<1, false>);
+  return ds_ws ? launch(sparse_dkdv_umma_kernel<4, true>) : launch(sparse_dkdv_umma_kernel<4, false>);
+}
+
+int sparse_dq_from_ds_umma(const void* k, const int32_t* selected, const int32_t* kv_sizes, const void* ds_ws, void* dq,
+                           int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
+                           const void* dq_mean, const int32_t* q_sizes) {
+  if (BH == 0 || Lq == 0) return VSA_OK;
+  if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dQ: batch*heads %lld exceeds 65535", (long long)BH);
+  if (reinterpret_cast<uintptr_t>(ds_ws) % 16)
+    return fail(VSA_ERR_BAD_ARGUMENT, "sparse dQ: the dS workspace is not 16-byte aligned");
+  CUtensorMap mk;
+  int rc;
+  if ((rc = make_map(&mk, k, BH * Lkv, "sparse dQ (k)"))) return rc;
+  const int smem = DqdsSmem::total + 1024;
+  dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
+  auto launch = [&](auto kern) -> int {
+    if ((rc = reserve_smem(kern, smem, "sparse dQ"))) return rc;
+    kern<<<grid, kDsThreads, smem, st>>>(mk, (const bf16*)ds_ws, selected, kv_sizes, (bf16*)dq, (const bf16*)dq_mean,
+                                         q_sizes, Lq, Lkv, topk, scale);
+    return check_launch("sparse_dq_from_ds_kernel");
+  };
+  return be == 64 ? launch(sparse_dq_from_ds_kernel<1>) : launch(sparse_dq_from_ds_kernel<4>);
 }
 
 // ---- pooled attention on tcgen05 ---------------------------------------------------------------------------
@@ -731,6 +780,11 @@ extern "C" int vsa_debug_trace(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 16 * 128) == cudaSuccess ? 0 : -3;
 }
 #endif
+
+int wait_timeout_selftest(unsigned long long limit_ns, int* gave_up, cudaStream_t st) {
+  wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(limit_ns, gave_up);
+  return check_launch("wait_timeout_selftest_kernel");
+}
 
 int device_status_fetch_and_clear(int* status) {
   int zero = 0;

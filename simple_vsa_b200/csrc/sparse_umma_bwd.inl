@@ -109,7 +109,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   }
   for (int it = tid; it < n_iter; it += kBwdThreads) {
     const int kvb = sel[it / SUB];
-    const int left = kv_sizes[kvb] - (it % SUB) * kTile;
+    // an id outside the table is an empty tile, as route inversion treats it
+    const int left = (unsigned)kvb < (unsigned)(Lkv / (kTile * SUB)) ? kv_sizes[kvb] - (it % SUB) * kTile : 0;
     tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
     tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
   }
@@ -391,7 +392,16 @@ enum DkBar { DK_KV_FULL = 0, DK_Q_FULL = 1, DK_DO_FULL = 4, DK_Q_EMPTY = 6, DK_D
              DK_P_EMPTY = 12, DK_DS_FULL = 13, DK_DS_EMPTY = 14, DK_ACC_FULL = 15, DK_S_FULL = 16,
              DK_DP_FULL = 16 + kDkBufs, DK_S_EMPTY = 16 + 2 * kDkBufs };
 
-template <int SUB>
+// DS = true: the rows of `inverse` hold packed edges (query block << kEdgeSlotBits | slot in that block's route)
+// and every dS tile (64 query rows x 64 key tokens, 8 KB) is also written to `ds_ws` at tile index
+// ((edge * SUB + query sub-tile) * SUB + key sub-tile), edge = (slice * Qb + query block) * topk + slot, for the
+// dQ pass that only multiplies it by K (sparse_dq_from_ds_kernel below) instead of recomputing S and dP.
+// Layout of a stored tile: [8 chunks of 8 key tokens][64 query rows][16 bytes] -- the order in which the rows'
+// owner threads hold it (a warp's 32 rows of one chunk are 512 contiguous bytes: fully coalesced stores straight
+// from registers), and at the same time the un-swizzled K-major operand layout of tcgen05 (8 rows x 16 bytes per
+// core matrix), so the dQ pass copies the 8 KB verbatim into shared memory and multiplies.
+constexpr int kEdgeSlotBits = 11;
+template <int SUB, bool DS>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                         const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -399,7 +409,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
                         const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
                         bf16* __restrict__ dk, bf16* __restrict__ dv, const bf16* __restrict__ mean_grad_k,
-                        const bf16* __restrict__ mean_grad_v, long long Lq, long long Lkv, int topk, float scale) {
+                        const bf16* __restrict__ mean_grad_v, bf16* __restrict__ ds_ws, long long Lq, long long Lkv,
+                        int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -426,7 +437,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (n_pairs == 0) {   // nobody selected this tile, or it is all padding: no fine gradient, no pipeline
     uint4* gk = reinterpret_cast<uint4*>(dk + krow0 * kD);
     uint4* gv = reinterpret_cast<uint4*>(dv + krow0 * kD);
-    for (int i = tid; i < 1024; i += kBwdThreads) {
+    for (int i = tid; i < 1024; i += (int)blockDim.x) {
       uint4 ok4 = make_uint4(0, 0, 0, 0), ov4 = make_uint4(0, 0, 0, 0);
       if (mean_grad_k != nullptr && (i >> 4) < valid) {     // 16 chunks of eight dims per row
         bf16* ek = reinterpret_cast<bf16*>(&ok4);
@@ -445,7 +456,16 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(sm + DkSmem::misc);
   auto bar = [&](int i) -> uint32_t { return base + DkSmem::bars + 8u * i; };
   // row (inside this batch-head slice) of the i-th query tile that selected this key block
-  auto tile_row = [&](int i) -> int { return inv[i / SUB] * (kTile * SUB) + (i % SUB) * kTile; };
+  auto tile_row = [&](int i) -> int {
+    const int e = inv[i / SUB];
+    return (DS ? (e >> kEdgeSlotBits) : e) * (kTile * SUB) + (i % SUB) * kTile;
+  };
+  // index of the dS tile of the i-th in-edge query tile (DS only)
+  auto ds_tile = [&](int i) -> long long {
+    const int e = inv[i / SUB];
+    const long long edge = (bh * Qb + (e >> kEdgeSlotBits)) * (long long)topk + (e & ((1 << kEdgeSlotBits) - 1));
+    return (edge * SUB + (i % SUB)) * SUB + sub;
+  };
 
   if (tid == 0) {
     mbar_init(bar(DK_KV_FULL), 1);
@@ -578,24 +598,29 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // statistics of this lane's query row, fetched one pair ahead of their use.  A row that does not exist (the
     // repeated tile of an odd tail) gets lse = +inf, i.e. P = 0 exactly, and delta = 0, so dS = 0 * finite = 0.
     float lse_n = INFINITY, dl_n = 0.f;
+    long long dst_n = -1;                    // DS: tile index of this lane's dS row in the coming pair
     if (half < n_tiles) {
       const long long row = q_row_base + tile_row(half) + r;
       lse_n = lse2[row];
       dl_n = delta[row];
+      if (DS) dst_n = ds_tile(half);
     }
     uint8_t* prow = sm + DkSmem::p + t * 128;
     uint8_t* grow = sm + DkSmem::ds + t * 128;
     for (int p = 0; p < n_pairs && ok; ++p) {
       const int b = p % kDkBufs;
       const float lse = lse_n, dl = dl_n;
+      const long long dst = dst_n;
       {
         const int nidx = 2 * (p + 1) + half;
         lse_n = INFINITY;
         dl_n = 0.f;
+        dst_n = -1;
         if (nidx < n_tiles) {
           const long long row = q_row_base + tile_row(nidx) + r;
           lse_n = lse2[row];
           dl_n = delta[row];
+          if (DS) dst_n = ds_tile(nidx);
         }
       }
       // ---- P from S, published before dP is even looked at (the dP MMAs are still running)
@@ -655,6 +680,12 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           pg[j2] = pack_bf16(g0, g1);
         }
       }
+      if (DS && dst >= 0) {   // chunk-major tile: chunk c of row r at c * 1024 + r * 16 bytes
+        uint4* g = reinterpret_cast<uint4*>(ds_ws + dst * (kTile * kTile)) + ((kBwCols / 8) * cg) * kTile + r;
+#pragma unroll
+        for (int ch = 0; ch < kBwCols / 8; ++ch)
+          __stcs(g + ch * kTile, make_uint4(pg[4 * ch], pg[4 * ch + 1], pg[4 * ch + 2], pg[4 * ch + 3]));
+      }
       if (!ds_free) ok = VSA_WARP_WAIT(bar(DK_DS_EMPTY), (p & 1) ^ 1);     // dK^T of the previous pair has read the buffer
       if (!ok) break;
 #pragma unroll
@@ -708,4 +739,202 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// dQ from stored dS:  dQ^T [128 dims x 64 query rows] = scale * sum over the selected key tiles of K^T dS^T
+// ------------------------------------------------------------------------------------------------------
+// The key-owned pass above has already formed every dS tile; this query-owned pass only streams, per selected
+// key tile, the K tile (16 KB) and the dS tile (8 KB) and issues four M128 x N64 x K16 MMAs: no scores, no
+// exponentials, no elementwise stage.  It is bound by how fast TMA brings the 24 KB in, so the ring is deep.
+// Roles: warp 0 = TMA producer (three lanes, one box each), warp 1 = MMA issuer (owns the tensor memory; the
+// whole warp zero-fills the padding rows of a ragged K tile first), warps 2-5 = epilogue.
+constexpr int kDsStages = 8;
+constexpr int kDsStageBytes = 3 * kSlab;        // K head-dim half 0 | K head-dim half 1 | dS
+constexpr int kDsThreads = 192;
+struct DqdsSmem {
+  static constexpr uint32_t ring = 0;
+  static constexpr uint32_t tile_row = ring + kDsStages * kDsStageBytes;   // int32 [kMaxTiles]
+  static constexpr uint32_t tile_it = tile_row + 4 * kMaxTiles;            // uint16 [kMaxTiles]: position in the route
+  static constexpr uint32_t tile_valid = tile_it + 2 * kMaxTiles;          // uint8 [kMaxTiles]
+  static constexpr uint32_t bars = tile_valid + kMaxTiles;
+  static constexpr uint32_t misc = bars + 32 * 8;
+  static constexpr uint32_t total = misc + 64;
+};
+enum DqdsBar { DD_FULL = 0, DD_EMPTY = kDsStages, DD_ACC_FULL = 2 * kDsStages };
+
+template <int SUB>
+__global__ void __launch_bounds__(kDsThreads, 1)
+sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const bf16* __restrict__ ds_ws,
+                         const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
+                         bf16* __restrict__ dq, const bf16* __restrict__ mean_grad, const int32_t* __restrict__ q_sizes,
+                         long long Lq, long long Lkv, int topk, float scale) {
+  extern __shared__ uint8_t smem_raw[];
+  if (*(volatile int*)&g_device_status != 0) return;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qtile = blockIdx.x;
+  const long long bh = blockIdx.y;
+  const int Qb = (int)(Lq / (kTile * SUB)), Kb = (int)(Lkv / (kTile * SUB));
+  const int qb = qtile / SUB, qsub = qtile % SUB;
+  const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
+  const int n_iter = topk * SUB;
+  const long long qrow0 = bh * Lq + (long long)qtile * kTile;
+  const long long edge0 = (bh * Qb + qb) * (long long)topk;
+
+  int32_t* tile_row = reinterpret_cast<int32_t*>(sm + DqdsSmem::tile_row);
+  uint16_t* tile_it = reinterpret_cast<uint16_t*>(sm + DqdsSmem::tile_it);
+  uint8_t* tile_valid = sm + DqdsSmem::tile_valid;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(sm + DqdsSmem::misc);
+  auto bar = [&](int i) -> uint32_t { return base + DqdsSmem::bars + 8u * i; };
+
+  if (tid == 0) {
+    for (int i = 0; i < kDsStages; ++i) {
+      mbar_init(bar(DD_FULL + i), 3);
+      mbar_init(bar(DD_EMPTY + i), 1);
+    }
+    mbar_init(bar(DD_ACC_FULL), 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&map_k);
+  }
+  for (int it = tid; it < n_iter; it += kDsThreads) {
+    const int kvb = sel[it / SUB];
+    const int left = (unsigned)kvb < (unsigned)Kb ? kv_sizes[kvb] - (it % SUB) * kTile : 0;   // an id outside the table is an empty tile
+    tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
+    tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
+    tile_it[it] = (uint16_t)it;
+  }
+  __syncthreads();
+  if (warp == 2) {   // squeeze out the empty tiles in place, keeping the routing order
+    int n_live = 0;
+    for (int it0 = 0; it0 < n_iter; it0 += 32) {
+      const int it = it0 + lane;
+      const int valid = it < n_iter ? (int)tile_valid[it] : 0;
+      const int row = it < n_iter ? tile_row[it] : 0;
+      const unsigned live = __ballot_sync(0xffffffffu, valid > 0);
+      __syncwarp();
+      if (valid > 0) {
+        const int pos = n_live + __popc(live & ((1u << lane) - 1u));
+        tile_row[pos] = row;
+        tile_valid[pos] = (uint8_t)valid;
+        tile_it[pos] = (uint16_t)it;
+      }
+      n_live += __popc(live);
+      __syncwarp();
+    }
+    if (lane == 0) misc[1] = (uint32_t)n_live;
+  }
+  if (warp == 1) {
+    tmem_alloc(base + DqdsSmem::misc, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = misc[0];
+  const int n_live = (int)misc[1];
+  const long long kv_row_base = bh * Lkv;
+  bool ok = true;
+
+  if (warp == 0) {
+    for (int i = 0; i < n_live; ++i) {
+      const int s = i % kDsStages;
+      ok = VSA_WARP_WAIT(bar(DD_EMPTY + s), ((i / kDsStages) & 1) ^ 1);
+      if (!ok) break;
+      if (lane < 3) {
+        const uint32_t dst = base + DqdsSmem::ring + s * kDsStageBytes + lane * kSlab;
+        mbar_arrive_expect_tx(bar(DD_FULL + s), kSlab);
+        if (lane < 2) {
+          tma_load_2d(dst, &map_k, lane * 64, (int)(kv_row_base + tile_row[i]), bar(DD_FULL + s));
+        } else {
+          const int it = tile_it[i];
+          const long long tile = ((edge0 + it / SUB) * SUB + qsub) * SUB + (it % SUB);
+          bulk_load_1d(dst, ds_ws + tile * (kTile * kTile), kSlab, bar(DD_FULL + s));
+        }
+      }
+    }
+    if (!ok && lane == 0) report_timeout(31);
+  } else if (warp == 1) {
+    constexpr uint32_t idesc = instr_desc(128, 64, 1, 0);     // A = K^T (dims contiguous), B = dS (keys contiguous)
+    constexpr uint32_t hi = desc_hi(1024);
+    // B: un-swizzled K-major, core matrices of 8 query rows x 16 bytes; the next 8 rows 128 bytes on, the next
+    // 8 key tokens (chunk) 1024 bytes on; one MMA consumes two chunks
+    constexpr uint32_t hi_b = desc_hi_noswizzle(128);
+    for (int i = 0; i < n_live; ++i) {
+      const int s = i % kDsStages;
+      ok = VSA_WARP_WAIT(bar(DD_FULL + s), (i / kDsStages) & 1);
+      if (!ok) break;
+      const uint32_t stage = base + DqdsSmem::ring + s * kDsStageBytes;
+      const int valid = tile_valid[i];
+      if (valid < kTile) {
+        // rows of K beyond a ragged tile's size meet dS = 0 in the product; they must be finite zeros (0 * NaN)
+        uint8_t* kst = sm + DqdsSmem::ring + s * kDsStageBytes;
+        for (int r = valid + (lane >> 4); r < kTile; r += 2) {
+          const int ch = lane & 15;                 // 16 chunks of 16 bytes: both head-dim halves of the row
+          *reinterpret_cast<uint4*>(kst + (ch >> 3) * kSlab + r * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
+      if (lane == 0) {
+        tc_fence_after();
+        const uint32_t a0 = desc_lo(stage, kSlab), b0 = desc_lo(stage + 2 * kSlab, 1024);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ss(tmem, desc_pack(a0 + (uint32_t)(ks * 128), hi), desc_pack(b0 + (uint32_t)(ks * 128), hi_b), idesc,
+                 (i > 0 || ks > 0) ? 1u : 0u);
+        mma_commit(bar(DD_EMPTY + s));
+      }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      if (ok) mma_commit(bar(DD_ACC_FULL));
+      else report_timeout(32);
+    }
+  } else {
+    // epilogue: lane t = head dim, a column = a query row
+    const int quarter = warp & 3;
+    const int t = quarter * 32 + lane;
+    const int st = tid - 64;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    float gm = 0.f;
+    int rows_live = 0;
+    if (mean_grad != nullptr) {   // block-mean backward folded in, as in the recomputing dQ kernel
+      const int size = q_sizes[qb];
+      gm = __bfloat162float(mean_grad[(bh * Qb + qb) * (long long)kD + t]) / (float)(size > 1 ? size : 1);
+      rows_live = size - qsub * kTile;
+    }
+    if (n_live > 0) ok = VSA_WARP_WAIT(bar(DD_ACC_FULL), 0);
+    if (!ok && lane == 0) report_timeout(33);
+    tc_fence_after();
+    bf16* stage = reinterpret_cast<bf16*>(sm + DqdsSmem::ring);     // [64 query rows][128 dims]; every MMA is done
+#pragma unroll
+    for (int hcol = 0; hcol < 2; ++hcol) {
+      uint32_t av[32];
+      if (ok && n_live > 0) {
+        tmem_ld(tmem + lane_addr + hcol * 32, av);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) av[j] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int c = hcol * 32 + j;
+        stage[c * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]) * scale + (c < rows_live ? gm : 0.f));
+      }
+    }
+    named_barrier(1, 128);
+    bf16* og = dq + qrow0 * kD;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int cidx = st + 128 * i;
+      const int row = cidx >> 4, ch = cidx & 15;
+      *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 64);
 }

@@ -42,7 +42,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   // Called by ONE lane per warp (see warp_wait): hundreds of threads polling the same barrier word
   // measurably slowed the shared-memory pipe.  The clock and the abort flag live in global memory and
   // are looked at once per 64 unsuccessful tries only.
@@ -60,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const v
     if (*abort_flag != 0) return false;
     const unsigned long long now = global_ns();
     if (t0 == 0) t0 = now;
-    else if (now - t0 > kWaitLimitNs) return false;
+    else if (now - t0 > limit_ns) return false;
   }
 }
 // Whole-warp wait: lane 0 polls (one try first: the common case is a barrier that has already flipped);
@@ -125,6 +126,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// One 2-D box shared -> global (bulk async-group completion: commit, then wait for the reads of shared memory).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Contiguous bytes global -> shared (16-byte aligned addresses, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -167,6 +181,12 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
 }
 __host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) {
   return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+// High word for an un-swizzled operand (layout type 0): core matrices of 8 rows x 16 bytes stored contiguously;
+// for a K-major operand the leading offset (low word) is the distance between core matrices along K and the
+// stride offset the distance between 8-row groups.
+__host__ __device__ constexpr uint32_t desc_hi_noswizzle(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14);
 }
 __device__ __forceinline__ uint64_t desc_pack(uint32_t lo, uint32_t hi) {
   uint64_t d;

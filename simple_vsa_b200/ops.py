@@ -14,6 +14,7 @@ device memory, the current stream and autograd only.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Sequence, Tuple, Union
 
 import torch
@@ -124,14 +125,76 @@ def invert_routes(selected: Tensor, key_blocks: int):
     return inverse, offsets, counts
 
 
+def invert_routes_edges(selected: Tensor, key_blocks: int):
+    """``invert_routes`` with every in-edge recorded as ``(query_block << 11) | slot`` (slot = position of the
+    key block in that query block's row of ``selected``), which names the edge for the stored-dS backward."""
+    B, H, Qb, tk = selected.shape
+    dev = selected.device
+    counts = torch.empty((B, H, key_blocks), device=dev, dtype=torch.int32)
+    offsets = torch.empty_like(counts)
+    cursor = torch.empty_like(counts)
+    inverse = torch.empty((B, H, Qb * tk), device=dev, dtype=torch.int32)
+    call("vsa_route_invert_edges", selected.data_ptr(), counts.data_ptr(), offsets.data_ptr(), inverse.data_ptr(),
+         cursor.data_ptr(), B * H, Qb, key_blocks, tk, _stream(dev))
+    return inverse, offsets, counts
+
+
+def _ds_workspace_cap() -> int:
+    """Upper bound in bytes for the dS workspace of one group of slices (``VSA_B200_DS_WORKSPACE_GB``, default 16)."""
+    return int(float(os.environ.get("VSA_B200_DS_WORKSPACE_GB", "16")) * (1 << 30))
+
+
+def _sparse_backward_stored_ds(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale, pooled_grads, dt, st):
+    """delta, then per group of slices: key-owned dK/dV pass that also stores dS, query-owned dQ = scale * dS K.
+
+    The scores and dP are formed once instead of once per pass; the price is the dS workspace (8 KB per query
+    tile x selected key tile), which is why the slices are walked in groups that keep it under a fixed size."""
+    B, H, Lq, D = q.shape
+    Lkv = k.shape[2]
+    BH, Qb, Kb, tk = B * H, Lq // be, Lkv // be, selected.shape[-1]
+    inverse, offsets, counts = invert_routes_edges(selected, Kb)
+    delta = torch.empty_like(lse)
+    call("vsa_sparse_bwd_delta", out_s.data_ptr(), dout.data_ptr(), delta.data_ptr(), BH, Lq, D, dt, st)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    per_slice = int(_lib.lib.vsa_sparse_bwd_ds_workspace_bytes(1, Lq, be, tk))
+    group = max(1, min(BH, _ds_workspace_cap() // max(1, per_slice)))
+    ws = torch.empty(group * per_slice, device=q.device, dtype=torch.uint8)
+    dqc = dkc = dvc = q_sizes = None
+    if pooled_grads is not None:
+        dqc, dkc, dvc, q_sizes = pooled_grads
+
+    def at(t, s0, *shape):          # address of slice s0 of a [B, H, ...] tensor
+        return None if t is None else t.view(BH, *shape)[s0].data_ptr()
+
+    for s0 in range(0, BH, group):
+        n = min(group, BH - s0)
+        call("vsa_sparse_bwd_dkdv_ds", at(dout, s0, Lq, D), at(q, s0, Lq, D), at(k, s0, Lkv, D), at(v, s0, Lkv, D),
+             at(lse, s0, Lq), at(delta, s0, Lq), at(counts, s0, Kb), at(offsets, s0, Kb), at(inverse, s0, Qb * tk),
+             kv_sizes.data_ptr(), at(dk, s0, Lkv, D), at(dv, s0, Lkv, D), at(dkc, s0, Kb, D), at(dvc, s0, Kb, D),
+             ws.data_ptr(), n, Lq, Lkv, D, be, tk, scale, dt, st)
+        call("vsa_sparse_bwd_dq_from_ds", at(k, s0, Lkv, D), at(selected, s0, Qb, tk), kv_sizes.data_ptr(),
+             ws.data_ptr(), at(dq, s0, Lq, D), at(dqc, s0, Qb, D), _ptr(q_sizes), n, Lq, Lkv, D, be, tk, scale, dt, st)
+    return dq, dk, dv
+
+
 def sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be: int, scale: float, pooled_grads=None):
     """dQ, dK, dV of the fine branch.  ``pooled_grads = (dq_mean, dk_mean, dv_mean, q_sizes)`` folds the
-    block-mean backward of the pooled branch into the same kernels' stores."""
+    block-mean backward of the pooled branch into the same kernels' stores.
+
+    The default is two independent passes that each recompute the scores and dP (a query-owned dQ pass and a
+    key-owned dK/dV pass, like the reference).  ``VSA_B200_BACKWARD=stored_ds`` selects, on the tensor path, the
+    variant that forms dS once (``_sparse_backward_stored_ds``): 16 of 56 tensor-core products per pair of edges
+    fewer, but 8 KB per edge written and read back; on a B200 the extra write traffic slows the key-owned pass by
+    about as much as the dQ pass gains, so it is not the default."""
     B, H, Lq, D = q.shape
     Lkv = k.shape[2]
     dt = _check_device_dtype(q, k, v)
     st = _stream(q.device)
     tk = selected.shape[-1]
+    if os.environ.get("VSA_B200_BACKWARD", "") == "stored_ds" and \
+            _lib.lib.vsa_sparse_bwd_ds_supported(D, be, tk, dt):
+        return _sparse_backward_stored_ds(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale, pooled_grads,
+                                          dt, st)
     inverse, offsets, counts = invert_routes(selected, Lkv // be)
     delta = torch.empty_like(lse)
     dq = torch.empty_like(q)

@@ -5,7 +5,8 @@ Same names, arguments and returned keys as the reference's ``vsa/fastvideo_tilin
 against it keeps working.  The index tensors are built with closed-form arithmetic (no Python loop
 over tiles); on CUDA tensors the moves themselves run in one gather kernel of the library
 (``vsa_gather_rows``), which also writes the zero padding, instead of an index-put into a zeroed
-buffer plus two advanced-indexing gathers.
+buffer plus two advanced-indexing gathers.  The moves are differentiable (the backward is the same
+kernel with the opposite map); tensors that are not on a GPU take the reference's index expressions.
 """
 
 from __future__ import annotations
@@ -63,19 +64,57 @@ def build_vsa_metadata(dit_seq_shape: Tuple[int, int, int], tile_size: Tuple[int
             "tile_map": tile_map, "untile_map": untile_map}
 
 
-def _gather(x: Tensor, row_map: Tensor, dst_rows: int) -> Tensor:
-    if not x.is_cuda:
-        raise ValueError("the B200 implementation requires CUDA tensors")
+def _gather_cuda(x: Tensor, row_map: Tensor, dst_rows: int) -> Tensor:
     from . import _lib
     x = x.contiguous()
     batch, src_rows = x.shape[0], x.shape[1]
     row_bytes = (x.numel() // max(1, batch * src_rows)) * x.element_size()
     out = torch.empty((batch, dst_rows) + tuple(x.shape[2:]), device=x.device, dtype=x.dtype)
-    row_map = row_map.to(device=x.device, dtype=torch.int32).contiguous()
     with torch.cuda.device(x.device):
         _lib.call("vsa_gather_rows", x.data_ptr(), row_map.data_ptr(), out.data_ptr(), batch, src_rows, dst_rows,
                   row_bytes, torch.cuda.current_stream(x.device).cuda_stream)
     return out
+
+
+class _GatherRows(torch.autograd.Function):
+    """``out[:, r] = x[:, row_map[r]]`` (zero where ``row_map[r] < 0``).  No source row is read twice, so the
+    gradient is the same kernel with the opposite map: the gradient of tiling is an un-tiling, and the gradient of
+    un-tiling is a tiling that zero-fills the padding rows."""
+
+    @staticmethod
+    def forward(ctx, x, row_map, back_map):
+        ctx.save_for_backward(back_map)
+        return _gather_cuda(x, row_map, row_map.numel())
+
+    @staticmethod
+    def backward(ctx, grad):
+        (back_map,) = ctx.saved_tensors
+        return _gather_cuda(grad, back_map, back_map.numel()), None, None
+
+
+def _inverse_map(row_map: Tensor, src_rows: int) -> Tensor:
+    inv = torch.full((src_rows,), -1, dtype=torch.int32, device=row_map.device)
+    live = (row_map >= 0).nonzero().flatten()
+    inv[row_map[live].long()] = live.to(torch.int32)
+    return inv
+
+
+def _gather(x: Tensor, row_map: Tensor, back_map: Tensor = None) -> Tensor:
+    """Row gather along dim 1 with zero fill.  CUDA tensors go through ``vsa_gather_rows`` (differentiable);
+    tensors elsewhere use the reference's index expressions (``vsa/fastvideo_tiling.py:128-145``), so metadata
+    and layout code can be exercised without a GPU."""
+    row_map = row_map.to(device=x.device, dtype=torch.int32).contiguous()
+    if not x.is_cuda:
+        live = row_map >= 0
+        out = x.new_zeros((x.shape[0], row_map.numel()) + tuple(x.shape[2:]))
+        out[:, live] = x[:, row_map[live].long()]
+        return out
+    if back_map is None:
+        back_map = _inverse_map(row_map, x.shape[1])
+    back_map = back_map.to(device=x.device, dtype=torch.int32).contiguous()
+    if torch.is_grad_enabled() and x.requires_grad:
+        return _GatherRows.apply(x, row_map, back_map)
+    return _gather_cuda(x, row_map, row_map.numel())
 
 
 def tile(x: Tensor, tile_partition_indices: Tensor, non_pad_index: Tensor, num_blocks: int,
@@ -84,20 +123,20 @@ def tile(x: Tensor, tile_partition_indices: Tensor, non_pad_index: Tensor, num_b
     rows = num_blocks * max_block_size
     row_map = torch.full((rows,), -1, dtype=torch.int32, device=x.device)
     row_map[non_pad_index.to(x.device)] = tile_partition_indices.to(device=x.device, dtype=torch.int32)
-    return _gather(x, row_map, rows)
+    return _gather(x, row_map)
 
 
 def untile(x: Tensor, non_pad_index: Tensor, reverse_tile_partition_indices: Tensor) -> Tensor:
     """Inverse of :func:`tile`."""
     row_map = non_pad_index.to(x.device)[reverse_tile_partition_indices.to(x.device)]
-    return _gather(x, row_map, row_map.numel())
+    return _gather(x, row_map)
 
 
 def tile_with(meta: Dict[str, object], x: Tensor) -> Tensor:
-    """:func:`tile` with the cached row map of ``build_vsa_metadata`` (no index arithmetic per call)."""
-    return _gather(x, meta["tile_map"], meta["tile_map"].numel())
+    """:func:`tile` with the cached row maps of ``build_vsa_metadata`` (no index arithmetic per call)."""
+    return _gather(x, meta["tile_map"], meta["untile_map"])
 
 
 def untile_with(meta: Dict[str, object], x: Tensor) -> Tensor:
-    """:func:`untile` with the cached row map of ``build_vsa_metadata``."""
-    return _gather(x, meta["untile_map"], meta["untile_map"].numel())
+    """:func:`untile` with the cached row maps of ``build_vsa_metadata``."""
+    return _gather(x, meta["untile_map"], meta["tile_map"])

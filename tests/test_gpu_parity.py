@@ -271,7 +271,10 @@ def test_whole_operator_against_reference_vectors(name):
     differ, unexplained = O.topk_mismatch_report(torch.from_numpy(gold["scores"]), aux["selected"], case["topk"])
     assert unexplained == 0, f"{unexplained} rows pick a block the reference scores exclude"
     same_routes = differ == 0
-    _assert_close(aux["out_compress"], gold["out_c_blocks"], **_fwd_tol(case["dtype"]))
+    _assert_close(aux["out_compress_blocks"], gold["out_c_blocks"], **_fwd_tol(case["dtype"]))
+    # the reference's own key holds the same values repeated on the tokens of each query block
+    assert aux["out_compress"].shape == out.shape
+    assert torch.equal(aux["out_compress"][:, :, ::O.block_elements(case["block_size"])], aux["out_compress_blocks"])
     if same_routes:
         _assert_close(out, gold["out"], **_fwd_tol(case["dtype"]))
     # against the oracle on the routes the kernel chose (removes tie ambiguity)
@@ -603,3 +606,110 @@ def test_compression_gate_trains_through_the_operator():
     want.square().mean().backward()
     _assert_close(out.detach(), want.detach(), atol=1e-5, rtol=1e-5)
     _assert_close(grad, layer_c.to_gate_compress.weight.grad, atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("kernels", ["auto", "mma", "scalar"])
+def test_route_ids_outside_the_key_table_count_as_empty_blocks(kernels, monkeypatch):
+    """A caller-supplied routing table may hold ids that are not key blocks (negative, or >= Kb).  Every consumer
+    treats them like a block with no valid token -- the same way route inversion drops them -- so forward, dQ and
+    dK/dV stay finite and agree with the table that points those entries at an all-padding block instead."""
+    V = _V()
+    monkeypatch.setenv("VSA_B200_KERNELS", kernels)
+    torch.manual_seed(91)
+    be, nb, D, tk = 64, 10, 128, 4
+    q, k, v, dout = (torch.randn(1, 2, be * nb, D, device=DEV).to(torch.bfloat16) for _ in range(4))
+    sizes = torch.full((nb,), be)
+    sizes[nb - 1] = 0                                   # an all-padding block that nothing below selects by itself
+    pool = torch.arange(nb - 1)
+    good = torch.stack([pool[torch.randperm(nb - 1)[:tk]] for _ in range(2 * nb)]).view(1, 2, nb, tk).to(torch.int32)
+    bad = good.clone()
+    bad[0, 0, 3, 1] = -7
+    bad[0, 1, 5, 0] = nb + 3
+    bad[0, 1, 0, 3] = 2 ** 30
+    stand_in = bad.clone()
+    stand_in[(bad < 0) | (bad >= nb)] = nb - 1
+    results = []
+    for table in (bad, stand_in):
+        leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+        out = V.b200_sparse_attention(*leaves, table.to(DEV), sizes, block_size=(1, 1, be))
+        out.backward(dout)
+        results.append([out.detach()] + [t.grad for t in leaves])
+    for a, b in zip(*results):
+        assert torch.isfinite(a.float()).all()
+        torch.testing.assert_close(a.float(), b.float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+
+
+@pytest.mark.parametrize("be,nb,tk,ragged", [(64, 24, 6, True), (64, 33, 5, False), (256, 8, 3, True)])
+def test_backward_that_stores_ds_equals_the_recomputing_backward(be, nb, tk, ragged, monkeypatch):
+    """``VSA_B200_BACKWARD=stored_ds`` forms dS once (key-owned pass stores it, query-owned pass multiplies it by K);
+    the default backward forms it twice, once per pass.  Same dQ up to the rounding point of the scale (before or
+    after bf16), same dK/dV, with the pooled gradients folded in and without, and with the slices walked in groups
+    smaller than the batch."""
+    from simple_vsa_b200 import ops
+    torch.manual_seed(93)
+    B, H, D = 1, 3, 128
+    L = be * nb
+    q, k, v, dout = (torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16) for _ in range(4))
+    kv_sizes = torch.full((nb,), be, dtype=torch.int32, device=DEV)
+    q_sizes = kv_sizes.clone()
+    if ragged:
+        kv_sizes[1], kv_sizes[nb // 2], kv_sizes[-1] = 1, be // 2 + 3, 0
+        q_sizes[2] = be - 5
+    selected = _zipf_routes(B, H, nb, nb, tk, 19).to(DEV)
+    scale = 1.0 / math.sqrt(D)
+    out_s, lse = ops.sparse_forward(q, k, v, selected, kv_sizes, be, scale, True)
+    pooled = tuple(torch.randn(B, H, nb, D, device=DEV).to(torch.bfloat16) for _ in range(3)) + (q_sizes,)
+    for pg in (None, pooled):
+        monkeypatch.delenv("VSA_B200_BACKWARD", raising=False)
+        want = ops.sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale, pooled_grads=pg)
+        monkeypatch.setenv("VSA_B200_BACKWARD", "stored_ds")
+        for cap in ("16", "1e-9"):                 # one group of slices, then one slice per group
+            monkeypatch.setenv("VSA_B200_DS_WORKSPACE_GB", cap)
+            got = ops.sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale, pooled_grads=pg)
+            for name, g, w in zip(("dq", "dk", "dv"), got, want):
+                assert torch.isfinite(g.float()).all(), name
+                _assert_close(g, w, atol=2e-2, rtol=2e-2)
+    # and against the oracle
+    ol = [t.cpu().float().requires_grad_() for t in (q, k, v)]
+    O.sparse_attention(*ol, selected.cpu(), kv_sizes.cpu(), be, scale).backward(dout.cpu().float())
+    for g, leaf in zip(got if pg is None else ops.sparse_backward(dout, q, k, v, out_s, lse, selected, kv_sizes, be, scale),
+                       ol):
+        _assert_close(g, leaf.grad, atol=3e-2, rtol=3e-2)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_later_kernels_drain():
+    """The failure path of the tcgen05 kernels, walked without making anything fail: a self-test warp waits 1 ms on
+    a barrier nothing arrives at and gives up.  The code must reach the status word, kernels launched while the
+    word is set must return without writing, the Python check must raise, and after the clear the same launch works."""
+    from simple_vsa_b200 import _lib
+    torch.manual_seed(95)
+    be, nb, D, tk = 64, 6, 128, 2
+    q, k, v = (torch.randn(1, 1, be * nb, D).to(torch.bfloat16) for _ in range(3))
+    sizes = torch.full((nb,), be)
+    selected = torch.stack([torch.randperm(nb)[:tk] for _ in range(nb)]).view(1, 1, nb, tk).to(torch.int32)
+    want = O.sparse_attention(q, k, v, selected, sizes, be)
+    qd, kd, vd, sd, zd = q.to(DEV), k.to(DEV), v.to(DEV), selected.to(DEV), sizes.to(DEV, torch.int32)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def forward(out, lse):
+        _lib.call("vsa_sparse_fwd", qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), sd.data_ptr(), zd.data_ptr(),
+                  out.data_ptr(), lse.data_ptr(), 1, be * nb, be * nb, D, be, tk, 1.0 / math.sqrt(D), _lib.VSA_BF16, st)
+
+    gave_up = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _lib.call("vsa_selftest_wait_timeout", 1_000_000, gave_up.data_ptr(), st)
+    torch.cuda.synchronize()
+    assert int(gave_up) == 1
+    out = torch.full((1, 1, be * nb, D), 7.0, device=DEV, dtype=torch.bfloat16)
+    lse = torch.zeros((1, 1, be * nb), device=DEV)
+    forward(out, lse)
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all()) and bool((lse == 0).all())      # drained: nothing was written
+    with pytest.raises(_lib.VsaError, match="code 201"):
+        _lib.raise_on_device_timeout("test")
+    assert _lib.device_status() == 0                                  # the check cleared the word
+    forward(out, lse)
+    torch.cuda.synchronize()
+    _assert_close(out, want, atol=2e-2, rtol=2e-2)
+    with pytest.raises(ValueError, match="limit"):
+        _lib.call("vsa_selftest_wait_timeout", 10, gave_up.data_ptr(), st)

@@ -64,3 +64,66 @@ def test_tile_untile_kernel(path, dtype, width):
     if width == 3 and dtype == torch.float32:
         y = torch.arange(2 * seq * 3, dtype=torch.float32).reshape(2, seq, 3).cuda()
         np.testing.assert_array_equal(tile_with(meta, y).cpu().numpy(), gold["tiled"])
+
+
+@pytest.mark.parametrize("path", FILES[:2])
+def test_tile_untile_on_cpu_tensors_follow_the_reference_expressions(path):
+    """Tensors that are not on a GPU go through plain index operations: same values as the reference-made
+    vectors, and autograd flows through them."""
+    from simple_vsa_b200 import build_vsa_metadata, tile, tile_with, untile, untile_with
+    shape, tsz, gold = _case(path)
+    meta = build_vsa_metadata(shape, tile_size=tsz, device="cpu")
+    seq = math.prod(shape)
+    x = torch.arange(2 * seq * 3, dtype=torch.float32).reshape(2, seq, 3).requires_grad_()
+    nb = math.prod(meta["num_tiles"])
+    tiled = tile(x, meta["tile_partition_indices"], meta["non_pad_index"], nb, meta["max_block_size"])
+    np.testing.assert_array_equal(tiled.detach().numpy(), gold["tiled"])
+    assert torch.equal(tile_with(meta, x), tiled)
+    back = untile(tiled, meta["non_pad_index"], meta["reverse_tile_partition_indices"])
+    np.testing.assert_array_equal(back.detach().numpy(), gold["untiled"])
+    assert torch.equal(untile_with(meta, tiled), back)
+    w = torch.randn_like(tiled)
+    (tiled * w).sum().backward()
+    assert torch.equal(x.grad, untile_with(meta, w))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", FILES)
+def test_gradient_flows_through_tile_and_untile(path):
+    """tile -> (anything) -> untile stays attached to the graph, and the gradients equal those of the index-op form
+    (``vsa/fastvideo_tiling.py:128-145`` of the reference); padding rows receive no gradient from untile."""
+    from simple_vsa_b200 import build_vsa_metadata, tile, tile_with, untile, untile_with
+    shape, tsz, _ = _case(path)
+    meta = build_vsa_metadata(shape, tile_size=tsz, device="cuda:0")
+    seq = math.prod(shape)
+    nb = math.prod(meta["num_tiles"])
+    torch.manual_seed(5)
+    x = torch.randn(2, seq, 2, 16, device="cuda:0")
+    w = torch.randn(2, nb * meta["max_block_size"], 2, 16, device="cuda:0")
+    tpi, npi, rev = meta["tile_partition_indices"], meta["non_pad_index"], meta["reverse_tile_partition_indices"]
+
+    def reference_form(x_):
+        buf = torch.zeros_like(w)
+        buf[:, npi] = x_[:, tpi]
+        y = (buf * w).tanh()
+        return y[:, npi][:, rev]
+
+    for variant in ("explicit", "cached"):
+        a = x.clone().requires_grad_()
+        if variant == "explicit":
+            y = untile((tile(a, tpi, npi, nb, meta["max_block_size"]) * w).tanh(), npi, rev)
+        else:
+            y = untile_with(meta, (tile_with(meta, a) * w).tanh())
+        b = x.clone().requires_grad_()
+        z = reference_form(b)
+        assert torch.equal(y, z)
+        g = torch.randn_like(y)
+        y.backward(g)
+        z.backward(g)
+        assert torch.equal(a.grad, b.grad)
+    # the gradient of untile alone puts zeros on the padding rows
+    t = torch.randn_like(w).requires_grad_()
+    untile_with(meta, t).sum().backward()
+    pad = torch.ones(w.shape[1], dtype=torch.bool, device="cuda:0")
+    pad[npi] = False
+    assert float(t.grad[:, pad].abs().sum()) == 0.0 and float(t.grad[:, ~pad].min()) == 1.0
