@@ -15,13 +15,15 @@ ranks with inputs resident in HBM (useful FLOPs = 14*B*H*L*topk*be*D per call);
 ``e2e`` = the same through the public API with pinned host buffers copied in and the
 results copied out inside the timed region; ``roofline`` for the dominant kernel
 from CUDA events recorded around every launch of the timed steps; ``cpu_baseline``
-= the CPU oracle timed on a bounded sample of the same workload; SM clocks sampled
-during the timed region.
+= the reference's own ``vsa.torch_vsa`` (installed copy under ``baseline/_ref``; the
+oracle port when that copy is absent) timed on a bounded sample of the same workload
+with all host cores and with one; ``e2e.copy_floor_ms`` = the end-to-end step's copy
+schedule with the operator left out; SM clocks sampled during the timed region; and,
+at one GPU, ``gpu_reference`` = the installed reference copy's own Triton kernels
+timed on the same tensors for the same number of steps.
 
-``--impl reference`` times the CPU restatement of the reference algorithm (the
-oracle) on the host cores on a bounded sample of the same workload.
-``--impl reference_triton`` (extra, optional) times the unmodified reference package's own
-Triton kernels on the GPU when ``baseline/_ref`` holds an installed copy.
+``--impl reference`` times that CPU implementation alone (rank 0 only under torchrun).
+``--impl reference_triton`` (extra) times only the reference copy's Triton kernels.
 """
 
 from __future__ import annotations
@@ -208,7 +210,7 @@ def cpu_sample_setup(cfg, q_blocks: int):
     return step, flops, sample, ("reference" if ref is not None else "port")
 
 
-def run_cpu(cfg, steps: int, warmup: int, q_blocks: int = 64):
+def run_cpu(cfg, steps: int, warmup: int, q_blocks: int = 16):
     """Times the CPU sample with every core this process may use, and once more on one thread."""
     import torch
     cores = len(os.sched_getaffinity(0))
@@ -233,12 +235,18 @@ def run_cpu(cfg, steps: int, warmup: int, q_blocks: int = 64):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
+def workload_dtype(cfg):
+    import torch
+    return torch.float32 if cfg.get("dtype") == "f32" else torch.bfloat16
+
+
 def make_slices(cfg, first: int, count: int, device, rows=None, salt: int = 0):
     """q, k, v, dout (and gate) for ``count`` (batch, head) slices starting at ``first``: [1, count, rows, D]."""
     import torch
     L, D = (rows or cfg["L"]), cfg["D"]
     names = ["q", "k", "v", "dout"] + (["gate"] if cfg["gate"] else [])
-    out = {n: torch.empty((1, count, L, D), device=device, dtype=torch.bfloat16) for n in names}
+    dt = workload_dtype(cfg)
+    out = {n: torch.empty((1, count, L, D), device=device, dtype=dt) for n in names}
     gen = torch.Generator(device=device)
     for i in range(count):
         gen.manual_seed(SEED + first + i + 1000003 * salt)
@@ -246,7 +254,7 @@ def make_slices(cfg, first: int, count: int, device, rows=None, salt: int = 0):
             x = torch.randn((L, D), generator=gen, device=device, dtype=torch.float32)
             if n == "gate":
                 x = torch.sigmoid(x)
-            out[n][0, i] = x.to(torch.bfloat16)
+            out[n][0, i] = x.to(dt)
     return out
 
 
@@ -276,6 +284,46 @@ class KernelTimer:
         return out
 
 
+def time_reference_triton(inputs, cfg, tk, steps, flops_total, own_ms, gpu_index):
+    """The UNMODIFIED reference package's own GPU kernels (``vsa.triton_vsa``, ``vsa/triton_impl.py:1734-1765``, from
+    the installed copy under ``baseline/_ref``) on the tensors this run has just used: same call, same step count,
+    CUDA events (the method of ``examples/bench_full.py:36-48``), clocks sampled alongside."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "vsa")):
+        return {"impl": "reference_triton", "unavailable": "baseline/_ref holds no installed copy of the reference"}
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    try:
+        import torch
+        from vsa import triton_vsa
+        q, k, v = (inputs[n].clone().requires_grad_() for n in ("q", "k", "v"))
+        gate, dout = inputs["gate"], inputs["dout"]
+        sizes = inputs["sizes"].to(torch.int64)
+
+        def step():
+            q.grad = k.grad = v.grad = None
+            triton_vsa(q, k, v, sizes, sizes, tk, cfg["block_size"], gate).backward(dout)
+
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(gpu_index)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ms = e0.elapsed_time(e1) / steps
+        return {"impl": "reference_triton", "ms_per_step": ms, "value": flops_total / (ms * 1e-3) / 1e12,
+                "unit": "TFLOP/s", "steps": steps, "clocks": clocks, "speedup": ms / own_ms,
+                "what": "vsa.triton_vsa of the installed reference copy, same tensors and step count, this GPU"}
+    except Exception as exc:        # noqa: BLE001 - reported, not raised: this leg is a comparison, not the product
+        return {"impl": "reference_triton", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+
 def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -286,6 +334,8 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    from simple_vsa_b200.host import bind_to_gpu_numa_node
+    numa_node = bind_to_gpu_numa_node(local_rank)      # before any pinned host memory is allocated
     if world > 1:
         opts = None
         try:        # NCCL's kernels on a high-priority stream: they must find SMs between our long one-CTA-per-SM kernels
@@ -322,7 +372,20 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         for t in (q, k, v):
             t[:, :, pad] = 0
     routes = None
-    if cfg.get("routes") == "zipf":
+    if cfg.get("routes") in ("uniform", "local", "hotset"):
+        # the generators of the reference's component bench (examples/bench_components.py:51-63)
+        if cfg["routes"] == "uniform":
+            gen = torch.Generator(device=dev)
+            routes = torch.empty((1, count, nb, tk), device=dev, dtype=torch.int32)
+            for i in range(count):
+                gen.manual_seed(SEED + 7919 * (first + i))
+                routes[0, i] = torch.randn((nb, nb), generator=gen, device=dev).topk(tk, dim=-1).indices.to(torch.int32)
+        else:
+            qi = torch.arange(nb, device=dev)[:, None]
+            slots = torch.arange(tk, device=dev)[None, :]
+            one = (qi + slots) % nb if cfg["routes"] == "local" else slots.expand(nb, -1)
+            routes = one[None, None].expand(1, count, -1, -1).to(torch.int32).contiguous()
+    elif cfg.get("routes") == "zipf":
         gen = torch.Generator(device=dev)
         routes = torch.empty((1, count, nb, tk), device=dev, dtype=torch.int32)
         logw = -1.1 * torch.log(torch.arange(1, nb + 1, device=dev, dtype=torch.float32))
@@ -376,23 +439,35 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     launches = _lib.lib.vsa_launch_count() - launches_before
     ms_dev = t_start.elapsed_time(t_stop) / args.steps
     kernels = timer.summary()
+    _lib.raise_on_device_timeout("bench (timed steps)")      # a drained kernel must not pass for a fast one
 
     # ---- end to end: pinned host buffers in, results out, inside the timed region ----
     names = ["q", "k", "v", "dout"] + (["gate"] if gate is not None else [])
-    host_in = {n: torch.empty(data[n].shape, dtype=torch.bfloat16, pin_memory=True) for n in names}
+    dt = workload_dtype(cfg)
+    host_in = {n: torch.empty(data[n].shape, dtype=dt, pin_memory=True) for n in names}
     for n in names:
         host_in[n].copy_(data[n].detach())
     out_names = ["out", "dq", "dk", "dv"] + (["dgate"] if gate is not None else [])
-    host_out = {n: torch.empty(q.shape, dtype=torch.bfloat16, pin_memory=True) for n in out_names}
+    host_out = {n: torch.empty(q.shape, dtype=dt, pin_memory=True) for n in out_names}
+    ref_inputs = None
+    if world == 1 and not args.no_gpu_reference and not sp and routes is None:
+        ref_inputs = dict(q=q.detach(), k=k.detach(), v=v.detach(), dout=dout, gate=None if gate is None else gate.detach(),
+                          sizes=sizes)
     del data, q, k, v, dout, gate, leaves, gl
     torch.cuda.empty_cache()
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    e2e_steps = max(1, args.steps if args.e2e_steps is None else args.e2e_steps)
 
     from simple_vsa_b200.host import vsa_step_from_host
 
-    def e2e_step():
-        if routes is not None or sp:     # route-explicit executor / sequence-parallel: plain copy in / call / copy out
+    pipelined = routes is None and not sp
+
+    def e2e_step(copy_schedule_only=False):
+        if not pipelined:     # route-explicit executor / sequence-parallel: plain copy in / call / copy out
             dv_ = {n: host_in[n].to(dev, non_blocking=True) for n in names}
+            if copy_schedule_only:
+                for n, src in zip(("out", "dq", "dk", "dv"), ("q", "k", "v", "dout")):
+                    host_out[n].copy_(dv_[src], non_blocking=True)
+                return
             ql, kl, vl = (dv_[n].requires_grad_() for n in ("q", "k", "v"))
             out = fwd_bwd(ql, kl, vl, None, dv_["dout"])
             for n, t in (("out", out.detach()), ("dq", ql.grad), ("dk", kl.grad), ("dv", vl.grad)):
@@ -401,24 +476,30 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         # the public host-resident step: chunks of slices, copies overlapped with the kernels
         vsa_step_from_host(host_in["q"], host_in["k"], host_in["v"], host_in["dout"], sizes, sizes, tk,
                            cfg["block_size"], host_in.get("gate"), out=host_out, device=dev,
-                           slices_per_chunk=args.e2e_chunk)
+                           slices_per_chunk=args.e2e_chunk, copy_schedule_only=copy_schedule_only)
 
-    e2e_step()
-    barrier()
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e_stop.record()
-    barrier()
-    ms_e2e = e_start.elapsed_time(e_stop) / e2e_steps
+    def timed(fn, n):
+        fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        barrier()
+        return a.elapsed_time(b) / n
+
+    ms_e2e = timed(e2e_step, e2e_steps)
     checksum = float(host_out["out"][0, 0, :64].float().abs().sum())
+    _lib.raise_on_device_timeout("bench (end-to-end steps)")
+    # the same copies on the same streams with the operator left out: what the transfers alone cost on this machine
+    ms_floor = timed(lambda: e2e_step(copy_schedule_only=True), max(1, min(3, e2e_steps)))
 
     # ---- max over ranks ----
     if world > 1:
-        t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_dev, ms_e2e, ms_floor], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_dev, ms_e2e = float(t[0]), float(t[1])
+        ms_dev, ms_e2e, ms_floor = float(t[0]), float(t[1]), float(t[2])
         lt = torch.tensor([launches], device=dev, dtype=torch.int64)
         dist.all_reduce(lt, op=dist.ReduceOp.SUM)
         launches = int(lt[0])
@@ -453,8 +534,14 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     step_total = sum(kv["total_ms"] for kv in kernels.values())
     shares = {n: round(kv["total_ms"] / step_total, 4) for n, kv in sorted(kernels.items())}
 
+    gpu_ref = None
+    if ref_inputs is not None:
+        gpu_ref = time_reference_triton(ref_inputs, cfg, tk, args.steps, flops_total, ms_dev, local_rank)
+        del ref_inputs
     cpu = run_cpu(cfg, steps=args.cpu_steps, warmup=1) if world == 1 and not args.no_cpu else None
-    T = count * l_loc * D * 2
+    es = 4 if cfg.get("dtype") == "f32" else 2
+    T = total_slices * L * D * es          # bytes of one q-shaped tensor over all ranks
+    T_rank = count * l_loc * D * es        # ... and on this rank
     n_in, n_out = len(names), len(out_names)
     line = {
         "metric": "VSA fwd+bwd useful TFLOPS, 92k tok blk64 bf16" if args.workload == DEFAULT_WORKLOAD
@@ -466,7 +553,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         "higher_is_better": True,
         "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "bf16",
+        "dtype": "f32" if cfg.get("dtype") == "f32" else "bf16",
         "data": "synthetic N(0,1), seeded per (batch,head) slice; random routes come from the operator's own Top-K",
         "collectives": ("all-gather K,V + reduce-scatter dK,dV over NCCL (sequence parallel)" if sp else "none"),
         "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], L, D], "block_elements": be,
@@ -474,12 +561,16 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
                    "routes": cfg.get("routes", "operator Top-K"),
                    "parallelism": (f"sequence split over {world} GPU(s): L/W = {l_loc} tokens per rank" if sp else
                                    f"(batch,head) slices partitioned over {world} GPU(s), no collective"),
-                   "l2": "inputs per GPU (%.2f GB) are larger than L2; no flush" % (4 * T / 1e9),
+                   "l2": "inputs per GPU (%.2f GB) are larger than L2; no flush" % (4 * T_rank / 1e9),
                    "useful_flops_per_call": flops_total},
         "impl": "b200",
         "e2e": {"value": flops_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "steps": e2e_steps, "h2d_bytes_per_step": n_in * T, "d2h_bytes_per_step": n_out * T,
-                "checksum": checksum},
+                "checksum": checksum, "copy_floor_ms": ms_floor,
+                "copy_floor_note": "same chunked host<->device copy schedule with the operator left out, max over ranks; "
+                                   "the end-to-end step cannot be faster than this on this machine",
+                "copy_gbs_per_direction_per_gpu": n_in * T_rank / (ms_floor * 1e-3) / 1e9,
+                "numa_node_bound": numa_node},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["tflops"],
@@ -494,6 +585,8 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if gpu_ref is not None:
+        line["gpu_reference"] = gpu_ref
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -603,8 +696,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_triton"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
-    ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--e2e-steps", type=int, default=None, help="end-to-end steps (default: --steps)")
+    ap.add_argument("--cpu-steps", type=int, default=2)
+    ap.add_argument("--no-gpu-reference", action="store_true",
+                    help="skip timing the installed reference copy's Triton kernels after the own run (1 GPU only)")
     ap.add_argument("--e2e-chunk", type=int, default=4, help="(batch,head) slices per pipelined chunk of the host-resident step")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -618,17 +713,17 @@ def main():
             return
         import torch
         from oracle import vsa_oracle as O
-        res = run_cpu(cfg, steps=max(1, args.steps), warmup=max(1, min(args.warmup, 2)))
+        res = run_cpu(cfg, steps=max(1, min(args.steps, 3)), warmup=1)
         be = O.block_elements(cfg["block_size"])
         line = {"metric": "VSA fwd+bwd useful TFLOPS, 92k tok blk64 bf16" if args.workload == DEFAULT_WORKLOAD
                 else f"VSA fwd+bwd useful TFLOPS ({args.workload})",
                 "value": res["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic N(0,1), seeded",
-                "impl": "reference",
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32" if cfg.get("dtype") == "f32" else "bf16",
+                "data": "synthetic N(0,1), seeded", "impl": "reference",
                 "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], cfg["L"], cfg["D"]],
                            "block_elements": be, "topk": cfg["topk"], "gate": cfg["gate"]},
-                "cpu_baseline": {k_: res[k_] for k_ in ("value", "unit", "cores", "kind", "sample")},
+                "cpu_baseline": {k_: res[k_] for k_ in ("value", "unit", "cores", "kind", "sample", "one_thread_value")},
                 "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         print(json.dumps(line), flush=True)

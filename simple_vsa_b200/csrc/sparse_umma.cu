@@ -36,19 +36,6 @@ namespace vsa {
 
 __device__ int g_device_status = 0;
 
-// Optional timeline of the CTA in the middle of the grid, compiled in only with -DVSA_TRACE (a development
-// aid).  Slots 0-13 hold clock64, slots 14/15 the global nanosecond timer at the points of slots 0/9, which
-// gives the SM clock the kernel really ran at.
-#ifdef VSA_TRACE
-__device__ long long g_trace[16 * 128];
-#define VSA_TRACE_AT(slot, p) do { if (blockIdx.x == gridDim.x / 2 && blockIdx.y == gridDim.y / 2 && (p) < 128) { \
-    g_trace[(slot) * 128 + (p)] = clock64(); \
-    if ((slot) == 0) g_trace[14 * 128 + (p)] = (long long)umma::global_ns(); \
-    if ((slot) == 9) g_trace[15 * 128 + (p)] = (long long)umma::global_ns(); } } while (0)
-#else
-#define VSA_TRACE_AT(slot, p) do { } while (0)
-#endif
-
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -393,12 +380,10 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int s = p % kFwdKStages, b = p % kSBufs;
         ok = VSA_WAIT(bar(K_FULL + s), (p / kFwdKStages) & 1) && VSA_WAIT(bar(S_EMPTY + b), ((p / kSBufs) & 1) ^ 1);
         if (!ok) break;
-        VSA_TRACE_AT(0, p);
         tc_fence_after();
         issue_kmajor(tmem_s0 + b * 64, base + FwdSmem::k + s * kPairBytes, base + FwdSmem::q);
         mma_commit(bar(K_EMPTY + s));
         mma_commit(bar(S_FULL + b));
-        VSA_TRACE_AT(1, p);
       }
       if (!ok) report_timeout(2);
     }
@@ -409,15 +394,12 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         ok = VSA_WAIT(bar(V_FULL + s), ph);
-        VSA_TRACE_AT(2, j);
         ok = ok && VSA_WAIT(bar(P_FULL + s), ph);
         if (!ok) break;
-        VSA_TRACE_AT(3, j);
         tc_fence_after();
         issue_mnmajor(tmem_o, base + FwdSmem::v + s * kPairBytes, base + FwdSmem::p + s * kPairHalf, j > 0);
         mma_commit(bar(V_EMPTY + s));
         mma_commit(bar(P_EMPTY + s));
-        VSA_TRACE_AT(4, j);
       }
       if (ok) mma_commit(bar(O_FULL));
       if (!ok) report_timeout(5);
@@ -450,7 +432,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // the score accumulator and the free P buffer (released by the O^T MMA two pairs back) in one round trip
       ok = VSA_WARP_WAIT2(bar(S_FULL + sb), (p / kSBufs) & 1, bar(P_EMPTY + s), ph ^ 1);
       if (!ok) break;
-      if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
       uint32_t sv[kEwCols];
       tmem_ld(tmem_s0 + sb * 64 + lane_addr + c0, sv);
@@ -458,7 +439,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(S_EMPTY + sb));
-      if (tid == 128) VSA_TRACE_AT(6, p);
 
       if (p == 0) {   // exact column maxima of the first live pair: warp shuffle, then across the lane quarters
 #pragma unroll
@@ -495,8 +475,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         packed[2 * j4] = pack_bf16(p0, p1);
         packed[2 * j4 + 1] = pack_bf16(p2, p3);
       }
-      if (tid == 128) VSA_TRACE_AT(7, p);
-      if (tid == 128) VSA_TRACE_AT(8, p);
       uint8_t* prow = sm + FwdSmem::p + s * kPairHalf + t * 128;
 #pragma unroll
       for (int ch = 0; ch < kEwCols / 8; ++ch)     // this thread's query rows are 16-byte chunks of row t
@@ -505,7 +483,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(P_FULL + s));
-      if (tid == 128) VSA_TRACE_AT(9, p);
     }
     if (!ok) report_timeout(3);
 
@@ -774,12 +751,6 @@ int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream
   umma_selftest_kernel<<<1, 128, smem, st>>>(ma, mb, (const bf16*)b, out, mode);
   return check_launch("umma_selftest_kernel");
 }
-
-#ifdef VSA_TRACE
-extern "C" int vsa_debug_trace(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 16 * 128) == cudaSuccess ? 0 : -3;
-}
-#endif
 
 int wait_timeout_selftest(unsigned long long limit_ns, int* gave_up, cudaStream_t st) {
   wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(limit_ns, gave_up);

@@ -211,12 +211,10 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ok = VSA_WAIT(bar(DQ_K_FULL + ks), (p / kDqKStages) & 1) &&
              VSA_WAIT(bar(DQ_S_EMPTY + b), ((p / kDqBufs) & 1) ^ 1);
         if (!ok) break;
-        VSA_TRACE_AT(0, p);
         tc_fence_after();
         // S^T is signalled on its own: the elementwise warps turn it into 2^(S c - lse) while dP^T still runs
         issue_kmajor(tmem + b * 128, base + DqSmem::k + ks * kPairBytes, base + DqSmem::q);
         mma_commit(bar(DQ_S_FULL + b));
-        VSA_TRACE_AT(1, p);
       }
       if (!ok) report_timeout(12);
     }
@@ -240,12 +238,10 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int ks = p % kDqKStages;
         ok = VSA_WAIT(bar(DQ_K_FULL + ks), (p / kDqKStages) & 1) && VSA_WAIT(bar(DQ_DS_FULL), p & 1);
         if (!ok) break;
-        VSA_TRACE_AT(3, p);
         tc_fence_after();
         issue_mnmajor(tmem_acc, base + DqSmem::k + ks * kPairBytes, base + DqSmem::ds, p > 0);
         mma_commit(bar(DQ_K_EMPTY + ks));
         mma_commit(bar(DQ_DS_EMPTY));
-        VSA_TRACE_AT(4, p);
       }
       if (ok) mma_commit(bar(DQ_ACC_FULL));
       if (!ok) report_timeout(13);
@@ -266,12 +262,10 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const bool live = r < valid;
       ok = VSA_WARP_WAIT(bar(DQ_S_FULL + b), (p / kDqBufs) & 1);
       if (!ok) break;
-      if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
       uint32_t sv[kBwCols];
       tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
       tmem_ld_wait();
-      if (tid == 128) VSA_TRACE_AT(6, p);
       // rows of K beyond a ragged tile's size (and the repeated tile of an odd tail) must be finite zeros:
       // they meet dS = 0 in the dQ product, where 0 * NaN would poison the sum.  S(p) has completed.
       if (!live && cg == 0) {
@@ -314,10 +308,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
         for (int j = 0; j < kBwCols / 2; ++j) packed[j] = 0u;
       }
-      if (tid == 128) VSA_TRACE_AT(7, p);
       if (!ds_free) ok = VSA_WARP_WAIT(bar(DQ_DS_EMPTY), (p & 1) ^ 1);
       if (!ok) break;
-      if (tid == 128) VSA_TRACE_AT(8, p);
       uint8_t* drow = sm + DqSmem::ds + t * 128;
 #pragma unroll
       for (int ch = 0; ch < kBwCols / 8; ++ch)
@@ -326,7 +318,6 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DQ_DS_FULL));
-      if (tid == 128) VSA_TRACE_AT(9, p);
     }
     if (!ok && lane == 0) report_timeout(14);
     if (ok && n_pairs > 0) ok = VSA_WARP_WAIT(bar(DQ_ACC_FULL), 0);
@@ -538,11 +529,9 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) &&
              VSA_WAIT(bar(DK_S_EMPTY + b), ((p / kDkBufs) & 1) ^ 1);
         if (!ok) break;
-        VSA_TRACE_AT(0, p);
         tc_fence_after();
         issue_kmajor(tmem + b * 128, base + DkSmem::q + qs * kPairBytes, base + DkSmem::k);
         mma_commit(bar(DK_S_FULL + b));
-        VSA_TRACE_AT(1, p);
       }
       if (!ok) report_timeout(22);
     }
@@ -567,20 +556,16 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t ph = (p >> 1) & 1;
         ok = VSA_WAIT(bar(DK_DO_FULL + s), ph) && VSA_WAIT(bar(DK_P_FULL), p & 1);
         if (!ok) break;
-        VSA_TRACE_AT(3, p);
         tc_fence_after();
         issue_mnmajor(tmem_dv, base + DkSmem::d_o + s * kPairBytes, base + DkSmem::p, p > 0);
         mma_commit(bar(DK_P_EMPTY));
         mma_commit(bar(DK_DO_EMPTY + s));      // second of two arrivals: the other issuer commits its dP reads of the stage
-        VSA_TRACE_AT(4, p);
         ok = VSA_WAIT(bar(DK_Q_FULL + qs), (p / kDkQStages) & 1) && VSA_WAIT(bar(DK_DS_FULL), p & 1);
         if (!ok) break;
-        VSA_TRACE_AT(10, p);
         tc_fence_after();
         issue_mnmajor(tmem_dk, base + DkSmem::q + qs * kPairBytes, base + DkSmem::ds, p > 0);
         mma_commit(bar(DK_Q_EMPTY + qs));
         mma_commit(bar(DK_DS_EMPTY));
-        VSA_TRACE_AT(11, p);
       }
       if (ok) mma_commit(bar(DK_ACC_FULL));
       if (!ok) report_timeout(23);
@@ -627,12 +612,10 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       bool p_free, ds_free;       // looked at together with the blocking waits: usually already true
       ok = VSA_WARP_WAIT_TEST(bar(DK_S_FULL + b), (p / kDkBufs) & 1, bar(DK_P_EMPTY), (p & 1) ^ 1, &p_free);
       if (!ok) break;
-      if (tid == 128) VSA_TRACE_AT(5, p);
       tc_fence_after();
       uint32_t sv[kBwCols];
       tmem_ld(tmem + b * 128 + lane_addr + c0, sv);
       tmem_ld_wait();
-      if (tid == 128) VSA_TRACE_AT(6, p);
       float pf[kBwCols];
       if (!ragged) {
 #pragma unroll
@@ -642,10 +625,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int j = 0; j < kBwCols; ++j)
           pf[j] = (c0 + j) < valid ? fast_exp2(fmaf(__uint_as_float(sv[j]), c, -lse)) : 0.f;
       }
-      if (tid == 128) VSA_TRACE_AT(7, p);
       if (!p_free) ok = VSA_WARP_WAIT(bar(DK_P_EMPTY), (p & 1) ^ 1);      // dV^T of the previous pair has read the buffer
       if (!ok) break;
-      if (tid == 128) VSA_TRACE_AT(8, p);
 #pragma unroll
       for (int ch = 0; ch < kBwCols / 8; ++ch)
         *reinterpret_cast<uint4*>(prow + ((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
@@ -654,11 +635,9 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DK_P_FULL));
-      if (tid == 128) VSA_TRACE_AT(9, p);
       // ---- dS = P * (dP - delta)
       ok = VSA_WARP_WAIT_TEST(bar(DK_DP_FULL + b), (p / kDkBufs) & 1, bar(DK_DS_EMPTY), (p & 1) ^ 1, &ds_free);
       if (!ok) break;
-      if (tid == 128) VSA_TRACE_AT(12, p);
       tc_fence_after();
       uint32_t dvv[kBwCols];
       tmem_ld(tmem + b * 128 + 64 + lane_addr + c0, dvv);
@@ -695,7 +674,6 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DK_DS_FULL));
-      if (tid == 128) VSA_TRACE_AT(13, p);
     }
     if (!ok && lane == 0) report_timeout(24);
     if (ok) ok = VSA_WARP_WAIT(bar(DK_ACC_FULL), 0);
