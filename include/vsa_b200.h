@@ -140,6 +140,17 @@ int vsa_sparse_fwd(const void* q, const void* k, const void* v,
                    int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                    float scale, int dtype, void* stream);
 
+/* vsa_sparse_fwd with the gated combine folded into the store of the fine output: out_s (kept: the
+ * backward's delta needs it) and out = out_s + out_c[block] * gate (gate may be NULL) leave the kernel
+ * together, bit-identical to vsa_sparse_fwd followed by vsa_combine_fwd, one pass over out_s fewer.
+ * Replaces the forward kernels PLUS _combine_forward_kernel: vsa/triton_impl.py:358-473,1720-1726,
+ * vsa/fused_common.py:175-199,259-295. */
+int vsa_sparse_fwd_combine(const void* q, const void* k, const void* v,
+                           const int32_t* selected, const int32_t* kv_sizes,
+                           void* out_s, float* lse2, const void* out_c, const void* gate, void* out,
+                           int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                           float scale, int dtype, void* stream);
+
 /* CSR of key block -> query blocks from the routing table, built on the device
  * by count / scan / scatter with exactly Qb*topk stored edges per BH slice.
  * cursor_ws is int32 scratch [BH,Kb].  Order inside a key row is unspecified.

@@ -28,6 +28,7 @@ SIGNATURES = {
     "vsa_topk": [P, P, L, I, I, I, P],
     "vsa_coarse_bwd": [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, F, I, P],
     "vsa_sparse_fwd": [P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_fwd_combine": [P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_route_invert": [P, P, P, P, P, L, I, I, I, P],
     "vsa_route_invert_static": [P, P, P, P, L, I, I, I, P],
     "vsa_sparse_bwd_dq": [P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],

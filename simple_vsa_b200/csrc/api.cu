@@ -165,25 +165,46 @@ static int check_sparse(int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int 
   return VSA_OK;
 }
 
+static int sparse_fwd_dispatch(const void* q, const void* k, const void* v, const int32_t* selected,
+                               const int32_t* kv_sizes, void* out, float* lse2, const void* out_c, const void* gate,
+                               void* out_comb, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                               float scale, int dtype, cudaStream_t st) {
+  int rc;
+  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype)) {
+    if (lse2 && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk)) {
+      rc = sparse_fwd_umma(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, st, out_c, gate, out_comb);
+      if (rc) return rc;
+      // exact recomputation of the (normally zero) tiles the fixed-shift softmax marked as out of range
+      return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, true, st, out_c, gate,
+                           out_comb);
+    }
+    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, false, st, out_c, gate,
+                         out_comb);
+  }
+  rc = sparse_fwd_scalar(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype, st);
+  if (rc || !out_comb) return rc;
+  return combine_fwd(out, out_c, gate, out_comb, BH, Lq, D, be, dtype, st);
+}
+
 int vsa_sparse_fwd(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                    void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale,
                    int dtype, void* stream) {
   int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
   if (rc) return rc;
   VSA_REQUIRE(q && k && v && selected && kv_sizes && out, "sparse forward: null pointer");
-  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype)) {
-    if (lse2 && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk)) {
-      rc = sparse_fwd_umma(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, (cudaStream_t)stream);
-      if (rc) return rc;
-      // exact recomputation of the (normally zero) tiles the fixed-shift softmax marked as out of range
-      return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, true,
-                           (cudaStream_t)stream);
-    }
-    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, false,
-                         (cudaStream_t)stream);
-  }
-  return sparse_fwd_scalar(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype,
-                           (cudaStream_t)stream);
+  return sparse_fwd_dispatch(q, k, v, selected, kv_sizes, out, lse2, nullptr, nullptr, nullptr, BH, Lq, Lkv, D, be, topk,
+                             scale, dtype, (cudaStream_t)stream);
+}
+
+int vsa_sparse_fwd_combine(const void* q, const void* k, const void* v, const int32_t* selected,
+                           const int32_t* kv_sizes, void* out_s, float* lse2, const void* out_c, const void* gate,
+                           void* out, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale,
+                           int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(q && k && v && selected && kv_sizes && out_s && out_c && out, "sparse forward + combine: null pointer");
+  return sparse_fwd_dispatch(q, k, v, selected, kv_sizes, out_s, lse2, out_c, gate, out, BH, Lq, Lkv, D, be, topk, scale,
+                             dtype, (cudaStream_t)stream);
 }
 
 int vsa_route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets, int32_t* inverse,

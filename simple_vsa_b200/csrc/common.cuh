@@ -68,6 +68,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Gated combine of eight bf16 values: out = out_s + out_c * gate (gate optional) in fp32, one rounding -- the
+// arithmetic of the stand-alone combine pass, so fusing it into a kernel's store changes no bit.
+__device__ __forceinline__ uint4 combine_bf16x8(const uint4& s_raw, const uint4& c_raw, const uint4& g_raw, bool has_gate) {
+  uint4 o_raw;
+  const __nv_bfloat16* se = reinterpret_cast<const __nv_bfloat16*>(&s_raw);
+  const __nv_bfloat16* ce = reinterpret_cast<const __nv_bfloat16*>(&c_raw);
+  const __nv_bfloat16* ge = reinterpret_cast<const __nv_bfloat16*>(&g_raw);
+  __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o_raw);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float cv = __bfloat162float(ce[i]);
+    if (has_gate) cv *= __bfloat162float(ge[i]);
+    oe[i] = __float2bfloat16_rn(__bfloat162float(se[i]) + cv);
+  }
+  return o_raw;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -45,9 +45,11 @@ int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const voi
 bool sparse_tc_eligible(int D, int be, int dtype);
 // redo_only: recompute only the 64-row query tiles whose first lse2 entry is NaN (the marker the
 // tcgen05 forward leaves on a tile whose fixed softmax shift ran out of range).
+// out_comb (optional): out_s + out_c[block] * gate is written there as well (gate may be null)
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                  bool redo_only, cudaStream_t st);
+                  bool redo_only, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
+                  void* out_comb = nullptr);
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
                  const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
                  int64_t Lkv, int be, int topk, float scale, cudaStream_t st);
@@ -60,7 +62,7 @@ int sparse_dkdv_tc(const void* dout, const void* q, const void* k, const void* v
 bool sparse_umma_eligible(int D, int be, int dtype, int topk);
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                    cudaStream_t st);
+                    cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr, void* out_comb = nullptr);
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
                    int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,

@@ -70,8 +70,13 @@ __device__ __forceinline__ float quad_sum(float x) {
 
 // Write a warp's 16x128 fp32 accumulator (8x2 n-tiles of mma layout) as bf16 into its
 // rows of a swizzled tile, then copy those rows to global memory with 16-byte stores.
+// With `comb` the gated combine with the pooled branch (pooled_row = the query block's pooled output row, gate_g
+// optional) is written beside it.
 __device__ __forceinline__ void store_warp_rows(uint8_t* tile, uint32_t tile_u32, const float (&acc)[16][4], float mul0,
-                                                float mul1, bf16* __restrict__ g, int warp, int lane) {
+                                                float mul1, bf16* __restrict__ g, int warp, int lane,
+                                                const bf16* __restrict__ pooled_row = nullptr,
+                                                const bf16* __restrict__ gate_g = nullptr,
+                                                bf16* __restrict__ comb = nullptr) {
   const int gq = lane >> 2, t = lane & 3;
   const int r0 = warp * 16 + gq, r1 = r0 + 8;
 #pragma unroll
@@ -86,6 +91,12 @@ __device__ __forceinline__ void store_warp_rows(uint8_t* tile, uint32_t tile_u32
     const int row = warp * 16 + (c >> 4), ch = c & 15;
     const uint4 val = *reinterpret_cast<const uint4*>(tile + tile_off(row, ch));
     *reinterpret_cast<uint4*>(g + row * kD + ch * 8) = val;
+    if (comb != nullptr) {
+      const uint4 cv = *reinterpret_cast<const uint4*>(pooled_row + ch * 8);
+      uint4 gv = make_uint4(0, 0, 0, 0);
+      if (gate_g != nullptr) gv = *reinterpret_cast<const uint4*>(gate_g + row * kD + ch * 8);
+      *reinterpret_cast<uint4*>(comb + row * kD + ch * 8) = combine_bf16x8(val, cv, gv, gate_g != nullptr);
+    }
   }
   (void)tile_u32;
 }
@@ -97,7 +108,8 @@ template <int SUB>
 __global__ void __launch_bounds__(kThreads, 2)
 sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
-                      bf16* __restrict__ out, float* __restrict__ lse2, long long Lq, long long Lkv, int topk,
+                      bf16* __restrict__ out, float* __restrict__ lse2, const bf16* __restrict__ out_c,
+                      const bf16* __restrict__ gate, bf16* __restrict__ out_comb, long long Lq, long long Lkv, int topk,
                       float scale, int redo_only) {
   extern __shared__ __align__(128) uint8_t smem[];
   if (redo_only) {   // only tiles the tcgen05 forward marked with a NaN statistic are recomputed
@@ -245,8 +257,13 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
     row_sum[r] = quad_sum(row_sum[r]);
     inv[r] = 1.f / row_sum[r];
   }
-  bf16* og = out + (bh * Lq + (long long)qtile * kTile) * kD;
-  store_warp_rows(smem, sQ, o, inv[0], inv[1], og, warp, lane);
+  const long long row0 = bh * Lq + (long long)qtile * kTile;
+  bf16* og = out + row0 * kD;
+  if (out_comb != nullptr)
+    store_warp_rows(smem, sQ, o, inv[0], inv[1], og, warp, lane, out_c + (bh * Qb + qb) * (long long)kD,
+                    gate != nullptr ? gate + row0 * kD : nullptr, out_comb + row0 * kD);
+  else
+    store_warp_rows(smem, sQ, o, inv[0], inv[1], og, warp, lane);
   if (lse2 && t == 0) {
     float* lg = lse2 + bh * Lq + (long long)qtile * kTile + warp * 16 + gq;
     lg[0] = row_max[0] + log2f(row_sum[0]);
@@ -566,7 +583,7 @@ bool sparse_tc_eligible(int D, int be, int dtype) { return dtype == VSA_BF16 && 
 
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                  bool redo_only, cudaStream_t st) {
+                  bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
   dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
@@ -574,11 +591,13 @@ int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* se
   if (be == 64) {
     if ((rc = set_smem(sparse_fwd_mma_kernel<1>, kFwdSmem, "sparse forward"))) return rc;
     sparse_fwd_mma_kernel<1><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
-                                                               kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
+                                                               kv_sizes, (bf16*)out, lse2, (const bf16*)out_c, (const bf16*)gate,
+                                                               (bf16*)out_comb, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
   } else {
     if ((rc = set_smem(sparse_fwd_mma_kernel<4>, kFwdSmem, "sparse forward"))) return rc;
     sparse_fwd_mma_kernel<4><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
-                                                               kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
+                                                               kv_sizes, (bf16*)out, lse2, (const bf16*)out_c, (const bf16*)gate,
+                                                               (bf16*)out_comb, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
   }
   return check_launch("sparse_fwd_mma_kernel");
 }

@@ -256,6 +256,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int32_t* __restrict__ selected,
                        const int32_t* __restrict__ kv_sizes, bf16* __restrict__ out, float* __restrict__ lse2,
+                       const bf16* __restrict__ out_c, const bf16* __restrict__ gate, bf16* __restrict__ out_comb,
                        long long Lq, long long Lkv, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;   // an earlier wait ran out: drain without touching anything
@@ -520,12 +521,20 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (!finite) *flag = 1u;
     named_barrier(1, kEwThreads);
     const bool redo = (*flag != 0u) && ok;
-    bf16* og = out + (bh * Lq + (long long)qtile * kTile) * kD;
+    const long long row0 = bh * Lq + (long long)qtile * kTile;
+    bf16* og = out + row0 * kD;
 #pragma unroll
     for (int i = 0; i < 1024 / kEwThreads; ++i) {
       const int cidx = st + kEwThreads * i;         // 1024 chunks of 16 bytes
       const int row = cidx >> 4, ch = cidx & 15;
-      *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
+      const uint4 sv = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
+      *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = sv;
+      if (out_comb != nullptr) {   // gated combine with the pooled branch on the way out (the fine output is kept: delta needs it)
+        const uint4 cv = *reinterpret_cast<const uint4*>(out_c + (bh * Qb + qb) * (long long)kD + ch * 8);
+        uint4 gv = make_uint4(0, 0, 0, 0);
+        if (gate != nullptr) gv = *reinterpret_cast<const uint4*>(gate + (row0 + row) * kD + ch * 8);
+        *reinterpret_cast<uint4*>(out_comb + (row0 + row) * kD + ch * 8) = combine_bf16x8(sv, cv, gv, gate != nullptr);
+      }
     }
     if (st < 64) {
       const float l = l_col[st];
@@ -552,7 +561,7 @@ bool sparse_umma_eligible(int D, int be, int dtype, int topk) {
 
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                    cudaStream_t st) {
+                    cudaStream_t st, const void* out_c, const void* gate, void* out_comb) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
   CUtensorMap mq, mk, mv;
@@ -566,11 +575,13 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
   if (be == 64) {
     e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
-    sparse_fwd_umma_kernel<1><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale);
+    sparse_fwd_umma_kernel<1><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, (const bf16*)out_c,
+                                                               (const bf16*)gate, (bf16*)out_comb, Lq, Lkv, topk, scale);
   } else {
     e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
-    sparse_fwd_umma_kernel<4><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, Lq, Lkv, topk, scale);
+    sparse_fwd_umma_kernel<4><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, (const bf16*)out_c,
+                                                               (const bf16*)gate, (bf16*)out_comb, Lq, Lkv, topk, scale);
   }
   return check_launch("sparse_fwd_umma_kernel");
 }

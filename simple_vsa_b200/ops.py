@@ -97,13 +97,22 @@ def _ptr(t: Optional[Tensor]):
 # --------------------------------------------------------------------------------------------
 # thin launch wrappers (no autograd); every tensor is dense and on one device
 # --------------------------------------------------------------------------------------------
-def sparse_forward(q, k, v, selected, kv_sizes, be: int, scale: float, want_lse: bool):
+def sparse_forward(q, k, v, selected, kv_sizes, be: int, scale: float, want_lse: bool, combine_with=None):
+    """Fine branch.  ``combine_with = (out_c, gate_or_None)`` also returns ``out = out_s + out_c[block] * gate``,
+    written by the same kernel on its way out (third element of the result)."""
     B, H, Lq, D = q.shape
     Lkv = k.shape[2]
     dt = _check_device_dtype(q, k, v)
     out = torch.empty_like(q)
     # the statistic buffer is always handed over: the tcgen05 forward needs it as scratch (4 bytes per row)
     lse = torch.empty((B, H, Lq), device=q.device, dtype=torch.float32)
+    if combine_with is not None:
+        out_c, gate = combine_with
+        total = torch.empty_like(q)
+        call("vsa_sparse_fwd_combine", q.data_ptr(), k.data_ptr(), v.data_ptr(), selected.data_ptr(),
+             kv_sizes.data_ptr(), out.data_ptr(), _ptr(lse), out_c.data_ptr(), _ptr(gate), total.data_ptr(), B * H, Lq,
+             Lkv, D, be, selected.shape[-1], scale, dt, _stream(q.device))
+        return out, (lse if want_lse else None), total
     call("vsa_sparse_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), selected.data_ptr(), kv_sizes.data_ptr(),
          out.data_ptr(), _ptr(lse), B * H, Lq, Lkv, D, be, selected.shape[-1], scale, dt, _stream(q.device))
     return out, (lse if want_lse else None)
@@ -297,10 +306,8 @@ class _VideoSparseAttention(torch.autograd.Function):
         dt = _check_device_dtype(q, k, v)
         st = _stream(q.device)
         qc, kc, vc, scores, probs, out_c, selected = pooled_forward(q, k, v, kv_sizes, q_sizes, be, scale, topk)
-        out_s, lse = sparse_forward(q, k, v, selected, kv_sizes, be, scale, need_grad)
-        out = torch.empty_like(q)
-        call("vsa_combine_fwd", out_s.data_ptr(), out_c.data_ptr(), _ptr(gate), out.data_ptr(), B * H, Lq, D, be,
-             dt, st)
+        # the gated combine rides on the store of the fine output (no separate pass over out_s)
+        out_s, lse, out = sparse_forward(q, k, v, selected, kv_sizes, be, scale, need_grad, combine_with=(out_c, gate))
         if need_grad:
             saved = [q, k, v, out_s, lse, selected, kv_sizes, q_sizes, qc, kc, vc, probs, out_c]
             if gate is not None:

@@ -713,3 +713,36 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_later_kernels_drain():
     _assert_close(out, want, atol=2e-2, rtol=2e-2)
     with pytest.raises(ValueError, match="limit"):
         _lib.call("vsa_selftest_wait_timeout", 10, gave_up.data_ptr(), st)
+
+
+@pytest.mark.parametrize("kernels", ["auto", "mma", "scalar"])
+@pytest.mark.parametrize("with_gate", [False, True])
+def test_forward_with_the_combine_folded_in_equals_the_two_step_form(kernels, with_gate, monkeypatch):
+    """vsa_sparse_fwd_combine = vsa_sparse_fwd followed by vsa_combine_fwd, bit for bit: block 64 and 256, ragged
+    sizes, and a key block scaled so that the tcgen05 forward hands some tiles to the exact redo kernel (which must
+    then redo their combined rows as well)."""
+    from simple_vsa_b200 import _lib, ops
+    monkeypatch.setenv("VSA_B200_KERNELS", kernels)
+    torch.manual_seed(97)
+    st = torch.cuda.current_stream().cuda_stream
+    for be, nb, tk in ((64, 12, 4), (256, 5, 2)):
+        B, H, D = 1, 2, 128
+        L = be * nb
+        q, k, v = (torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16) for _ in range(3))
+        k[:, :, 5 * 64:6 * 64] *= 40.0            # scores far above the first pair's maximum whenever selected late
+        out_c = torch.randn(B, H, nb, D, device=DEV).to(torch.bfloat16)
+        gate = torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16) if with_gate else None
+        sizes = torch.full((nb,), be, dtype=torch.int32, device=DEV)
+        sizes[1], sizes[nb - 1] = be // 2 + 1, 3
+        selected = torch.stack([torch.randperm(nb)[:tk] for _ in range(B * H * nb)]).view(B, H, nb, tk).to(torch.int32).to(DEV)
+        scale = 1.0 / math.sqrt(D)
+        out_s, lse = ops.sparse_forward(q, k, v, selected, sizes, be, scale, True)
+        want = torch.empty_like(q)
+        _lib.call("vsa_combine_fwd", out_s.data_ptr(), out_c.data_ptr(), gate.data_ptr() if with_gate else None,
+                  want.data_ptr(), B * H, L, D, be, _lib.VSA_BF16, st)
+        out_s2, lse2, got = ops.sparse_forward(q, k, v, selected, sizes, be, scale, True, combine_with=(out_c, gate))
+        assert torch.equal(out_s2, out_s) and torch.equal(lse2, lse)
+        assert torch.isfinite(got.float()).all()
+        assert torch.equal(got, want)
+        _assert_close(want, O.combine(out_s.cpu(), out_c.cpu(), gate.cpu() if with_gate else None, be, torch.bfloat16),
+                      atol=2e-2, rtol=2e-2)
