@@ -513,7 +513,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
     # dominant kernel by total device time
     # GEMM FLOPs a kernel's algorithm performs per edge (units of be^2*D): forward S,O = 4; recomputing dQ pass S,dP,dQ = 6;
     # dK/dV pass S,dP,dK,dV = 8 (with or without the dS stores); dQ from stored dS = 2
-    gemm_units = {"vsa_sparse_fwd": 4, "vsa_sparse_bwd_dq": 6, "vsa_sparse_bwd_dkdv": 8, "vsa_sparse_bwd_dkdv_ds": 8,
+    gemm_units = {"vsa_sparse_fwd": 4, "vsa_sparse_fwd_combine": 4, "vsa_sparse_bwd_dq": 6, "vsa_sparse_bwd_dkdv": 8, "vsa_sparse_bwd_dkdv_ds": 8,
                   "vsa_sparse_bwd_dq_from_ds": 2}
     fine = {n: kernels[n] for n in gemm_units if n in kernels}
     top = max(fine, key=lambda n: fine[n]["total_ms"])

@@ -725,11 +725,14 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 // The key-owned pass above has already formed every dS tile; this query-owned pass only streams, per selected
 // key tile, the K tile (16 KB) and the dS tile (8 KB) and issues four M128 x N64 x K16 MMAs: no scores, no
 // exponentials, no elementwise stage.  It is bound by how fast TMA brings the 24 KB in, so the ring is deep.
-// Roles: warp 0 = TMA producer (three lanes, one box each), warp 1 = MMA issuer (owns the tensor memory; the
-// whole warp zero-fills the padding rows of a ragged K tile first), warps 2-5 = epilogue.
+// Roles: warp 0 = TMA producer of the K tiles (two lanes, one box each), warp 1 = MMA issuer (owns the tensor
+// memory; the whole warp zero-fills the padding rows of a ragged K tile first), warps 2-5 = epilogue, warps 6-7 =
+// loaders of the dS tiles with plain asynchronous 16-byte copies: one SM's TMA unit moves ~50 bytes per clock in
+// 8 KB boxes, the load/store path adds its own bandwidth beside it, and a dS tile is a verbatim 8 KB copy.
 constexpr int kDsStages = 8;
 constexpr int kDsStageBytes = 3 * kSlab;        // K head-dim half 0 | K head-dim half 1 | dS
-constexpr int kDsThreads = 192;
+constexpr int kDsLoaders = 64;                  // threads that copy dS tiles
+constexpr int kDsThreads = 192 + kDsLoaders;
 struct DqdsSmem {
   static constexpr uint32_t ring = 0;
   static constexpr uint32_t tile_row = ring + kDsStages * kDsStageBytes;   // int32 [kMaxTiles]
@@ -769,7 +772,7 @@ sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const bf16* 
 
   if (tid == 0) {
     for (int i = 0; i < kDsStages; ++i) {
-      mbar_init(bar(DD_FULL + i), 3);
+      mbar_init(bar(DD_FULL + i), 2 + kDsLoaders);     // two TMA lanes and every loader thread
       mbar_init(bar(DD_EMPTY + i), 1);
     }
     mbar_init(bar(DD_ACC_FULL), 1);
@@ -820,49 +823,71 @@ sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const bf16* 
       const int s = i % kDsStages;
       ok = VSA_WARP_WAIT(bar(DD_EMPTY + s), ((i / kDsStages) & 1) ^ 1);
       if (!ok) break;
-      if (lane < 3) {
+      if (lane < 2) {
         const uint32_t dst = base + DqdsSmem::ring + s * kDsStageBytes + lane * kSlab;
         mbar_arrive_expect_tx(bar(DD_FULL + s), kSlab);
-        if (lane < 2) {
-          tma_load_2d(dst, &map_k, lane * 64, (int)(kv_row_base + tile_row[i]), bar(DD_FULL + s));
-        } else {
-          const int it = tile_it[i];
-          const long long tile = ((edge0 + it / SUB) * SUB + qsub) * SUB + (it % SUB);
-          bulk_load_1d(dst, ds_ws + tile * (kTile * kTile), kSlab, bar(DD_FULL + s));
-        }
+        tma_load_2d(dst, &map_k, lane * 64, (int)(kv_row_base + tile_row[i]), bar(DD_FULL + s));
       }
     }
     if (!ok && lane == 0) report_timeout(31);
+  } else if (warp >= 6) {
+    const int lt = tid - 192;                          // 64 threads x 8 copies of 16 bytes = one 8 KB tile
+    for (int i = 0; i < n_live; ++i) {
+      const int s = i % kDsStages;
+      ok = VSA_WARP_WAIT(bar(DD_EMPTY + s), ((i / kDsStages) & 1) ^ 1);
+      if (!ok) break;
+      const int it = tile_it[i];
+      const long long tile = ((edge0 + it / SUB) * SUB + qsub) * SUB + (it % SUB);
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(ds_ws + tile * (kTile * kTile)) + lt * 16;
+      const uint32_t dst = base + DqdsSmem::ring + s * kDsStageBytes + 2 * kSlab + lt * 16;
+#pragma unroll
+      for (int j = 0; j < kSlab / (16 * kDsLoaders); ++j) cp_async16(dst + j * 16 * kDsLoaders, src + j * 16 * kDsLoaders);
+      cp_async_arrive_noinc(bar(DD_FULL + s));
+    }
+    if (!ok && lane == 0) report_timeout(34);
   } else if (warp == 1) {
     constexpr uint32_t idesc = instr_desc(128, 64, 1, 0);     // A = K^T (dims contiguous), B = dS (keys contiguous)
     constexpr uint32_t hi = desc_hi(1024);
     // B: un-swizzled K-major, core matrices of 8 query rows x 16 bytes; the next 8 rows 128 bytes on, the next
     // 8 key tokens (chunk) 1024 bytes on; one MMA consumes two chunks
     constexpr uint32_t hi_b = desc_hi_noswizzle(128);
-    for (int i = 0; i < n_live; ++i) {
-      const int s = i % kDsStages;
-      ok = VSA_WARP_WAIT(bar(DD_FULL + s), (i / kDsStages) & 1);
+    // Two tiles per trip: a wait on an mbarrier costs a shared-memory round trip of a few hundred cycles however
+    // long ago it flipped, more than the four MMAs of a tile; two lanes look at two stages at once.
+    for (int i0 = 0; i0 < n_live; i0 += 2) {
+      const int n_here = n_live - i0 >= 2 ? 2 : 1;
+      const int s0 = i0 % kDsStages, s1 = (i0 + 1) % kDsStages;
+      if (n_here == 2)
+        ok = VSA_WARP_WAIT2(bar(DD_FULL + s0), (i0 / kDsStages) & 1, bar(DD_FULL + s1), ((i0 + 1) / kDsStages) & 1);
+      else
+        ok = VSA_WARP_WAIT(bar(DD_FULL + s0), (i0 / kDsStages) & 1);
       if (!ok) break;
-      const uint32_t stage = base + DqdsSmem::ring + s * kDsStageBytes;
-      const int valid = tile_valid[i];
-      if (valid < kTile) {
-        // rows of K beyond a ragged tile's size meet dS = 0 in the product; they must be finite zeros (0 * NaN)
-        uint8_t* kst = sm + DqdsSmem::ring + s * kDsStageBytes;
-        for (int r = valid + (lane >> 4); r < kTile; r += 2) {
-          const int ch = lane & 15;                 // 16 chunks of 16 bytes: both head-dim halves of the row
-          *reinterpret_cast<uint4*>(kst + (ch >> 3) * kSlab + r * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+      for (int h = 0; h < n_here; ++h) {
+        const int valid = tile_valid[i0 + h];
+        if (valid < kTile) {
+          // rows of K beyond a ragged tile's size meet dS = 0 in the product; they must be finite zeros (0 * NaN)
+          uint8_t* kst = sm + DqdsSmem::ring + (h ? s1 : s0) * kDsStageBytes;
+          for (int r = valid + (lane >> 4); r < kTile; r += 2) {
+            const int ch = lane & 15;                 // 16 chunks of 16 bytes: both head-dim halves of the row
+            *reinterpret_cast<uint4*>(kst + (ch >> 3) * kSlab + r * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          __syncwarp();
         }
-        fence_proxy_async_smem();
-        __syncwarp();
       }
       if (lane == 0) {
+        // the dS tiles were written by ordinary asynchronous copies (and padding rows by this warp); the tensor
+        // core reads through the async proxy
+        fence_proxy_async_smem();
         tc_fence_after();
-        const uint32_t a0 = desc_lo(stage, kSlab), b0 = desc_lo(stage + 2 * kSlab, 1024);
+        for (int h = 0; h < n_here; ++h) {
+          const int s = h ? s1 : s0;
+          const uint32_t stage = base + DqdsSmem::ring + s * kDsStageBytes;
+          const uint32_t a0 = desc_lo(stage, kSlab), b0 = desc_lo(stage + 2 * kSlab, 1024);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem, desc_pack(a0 + (uint32_t)(ks * 128), hi), desc_pack(b0 + (uint32_t)(ks * 128), hi_b), idesc,
-                 (i > 0 || ks > 0) ? 1u : 0u);
-        mma_commit(bar(DD_EMPTY + s));
+          for (int ks = 0; ks < 4; ++ks)
+            mma_ss(tmem, desc_pack(a0 + (uint32_t)(ks * 128), hi), desc_pack(b0 + (uint32_t)(ks * 128), hi_b), idesc,
+                   (i0 + h > 0 || ks > 0) ? 1u : 0u);
+          mma_commit(bar(DD_EMPTY + s));
+        }
       }
       __syncwarp();
     }

@@ -115,6 +115,12 @@ __device__ __forceinline__ bool warp_wait_and_test(uint32_t bar_a, uint32_t pari
   return __all_sync(0xffffffffu, ok) != 0;
 }
 
+// The executing thread's earlier cp.async copies arrive on the barrier when they have landed (the arrival is one
+// of the barrier's expected count, not an extra one).
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // ---- fences ----------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
