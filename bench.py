@@ -270,7 +270,9 @@ class KernelTimer:
     def __call__(self, name, phase, stream):
         ev = self.torch.cuda.Event(enable_timing=True)
         ev.record(self.torch.cuda.current_stream())
-        name = name.replace("_fused", "")      # the backward entry points with the block-mean backward folded in
+        # one name per kernel: the entry points with the block-mean backward folded in, and the shard-major forms of
+        # the sequence-parallel mode, launch the same kernels
+        name = name.replace("_fused", "").replace("_sharded", "")
         if phase == "start":
             self.pending[name] = ev
         else:

@@ -265,6 +265,44 @@ int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int3
                               int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                               float scale, int dtype, void* stream);
 
+/* ---- shard-major K/V: the fine kernels of the sequence-parallel mode ----------------------------------
+ * (No counterpart in the reference, whose kernels index every (batch, head) slice of one GPU's tensors:
+ * vsa/triton_impl.py:83-86.)  After an all-gather over W ranks the K/V shards lie one after another,
+ * [W][BH][Lkv/W][D].  These entry points read k_sh, v_sh -- and write dk_sh, dv_sh -- in that layout in
+ * place: row of (slice bh, token t) = ((t / kv_shard) * BH + bh) * kv_shard + t % kv_shard, kv_shard = Lkv/W
+ * tokens (a multiple of be).  So no re-layout copy follows the gather, and the partial dK/dV are contiguous
+ * per owner rank, ready for the reduce-scatter.  q, out, dq ... are this rank's [BH, Lq, D] as usual;
+ * selected holds GLOBAL key-block ids; kv_sizes lists all Kb = Lkv/be blocks.  Tensor path only (bf16,
+ * D = 128, be = 64 or 256), VSA_ERR_UNSUPPORTED otherwise.  kv_shard = Lkv is the ordinary layout. */
+
+/* 1 if the three entry points below cover (D, be, topk, dtype) in this process, else 0. */
+int vsa_sparse_sharded_supported(int D, int be, int topk, int dtype);
+
+/* vsa_sparse_fwd_combine on shard-major K/V; out_c, gate and out may all be NULL (fine output only). */
+int vsa_sparse_fwd_combine_sharded(const void* q, const void* k_sh, const void* v_sh,
+                                   const int32_t* selected, const int32_t* kv_sizes,
+                                   void* out_s, float* lse2, const void* out_c, const void* gate, void* out,
+                                   int64_t BH, int64_t Lq, int64_t Lkv, int64_t kv_shard, int D, int be, int topk,
+                                   float scale, int dtype, void* stream);
+
+/* vsa_sparse_bwd_dq_fused on shard-major K/V; dq_mean and q_sizes may both be NULL. */
+int vsa_sparse_bwd_dq_sharded(const void* dout, const void* q, const void* k_sh, const void* v_sh,
+                              const void* out_s, const float* lse2,
+                              const int32_t* selected, const int32_t* kv_sizes,
+                              float* delta, void* dq, const void* dq_mean, const int32_t* q_sizes,
+                              int64_t BH, int64_t Lq, int64_t Lkv, int64_t kv_shard, int D, int be, int topk,
+                              float scale, int dtype, void* stream);
+
+/* vsa_sparse_bwd_dkdv_fused on shard-major K/V, writing shard-major dK/dV (this rank's partial sums over its
+ * own query blocks, all Kb key blocks); dk_mean and dv_mean ([BH, Kb, D], global block order) may both be NULL. */
+int vsa_sparse_bwd_dkdv_sharded(const void* dout, const void* q, const void* k_sh, const void* v_sh,
+                                const float* lse2, const float* delta,
+                                const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                                const int32_t* kv_sizes, void* dk_sh, void* dv_sh,
+                                const void* dk_mean, const void* dv_mean,
+                                int64_t BH, int64_t Lq, int64_t Lkv, int64_t kv_shard, int D, int be, int topk,
+                                float scale, int dtype, void* stream);
+
 /* dst[b, r, :] = map[r] >= 0 ? src[b, map[r], :] : 0 for rows of row_bytes bytes (even; 16-byte
  * multiples take the vector path).  With the maps of the tiling metadata this is the raster ->
  * zero-padded tile layout move and its inverse.

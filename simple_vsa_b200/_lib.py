@@ -39,6 +39,9 @@ SIGNATURES = {
     "vsa_sparse_bwd_delta": [P, P, P, L, L, I, I, P],
     "vsa_sparse_bwd_dkdv_ds": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dq_from_ds": [P, P, P, P, P, P, P, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_fwd_combine_sharded": [P, P, P, P, P, P, P, P, P, P, L, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_bwd_dq_sharded": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_bwd_dkdv_sharded": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, I, I, I, F, I, P],
     "vsa_combine_fwd": [P, P, P, P, L, L, I, I, I, P],
     "vsa_gather_rows": [P, P, P, L, L, L, L, P],
     "vsa_selftest_umma": [P, P, P, I, P],
@@ -49,6 +52,7 @@ SIGNATURES = {
 PLAIN = {"vsa_last_error_string": ([], c_char_p), "vsa_version": ([], c_int),
          "vsa_launch_count": ([], c_int64),
          "vsa_sparse_bwd_ds_supported": ([I, I, I, I], c_int),
+         "vsa_sparse_sharded_supported": ([I, I, I, I], c_int),
          "vsa_sparse_bwd_ds_workspace_bytes": ([L, L, I, I], c_int64)}
 
 

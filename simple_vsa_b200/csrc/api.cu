@@ -357,6 +357,70 @@ int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int3
                                 dq_mean, q_sizes);
 }
 
+// ---- shard-major K/V (sequence-parallel mode) --------------------------------------------------------------
+// After an all-gather over W ranks the K/V shards lie one after another, [W][BH][Lkv/W][D].  These three entry
+// points read (and, for dK/dV, write) that layout in place: row of (slice, token) = ((token / shard) * BH + slice)
+// * shard + token % shard with shard = kv_shard tokens, so no re-layout copy follows the gather and the partial
+// dK/dV are ready for the reduce-scatter.  Tensor path only (bf16, D = 128, block volume 64 or 256).
+static int check_sharded(int64_t Lkv, int64_t kv_shard, int D, int be, int topk, int dtype, const char* what) {
+  VSA_REQUIRE(kv_shard > 0 && Lkv % kv_shard == 0 && kv_shard % be == 0,
+              "%s: kv_shard must divide Lkv and be a multiple of block_elements=%d", what, be);
+  if (scalar_forced() || mma_forced() || !sparse_umma_eligible(D, be, dtype, topk))
+    return fail(VSA_ERR_UNSUPPORTED, "%s: the shard-major layout needs bf16, head dim 128, block volume 64 or 256", what);
+  return VSA_OK;
+}
+
+int vsa_sparse_sharded_supported(int D, int be, int topk, int dtype) {
+  return !scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk) ? 1 : 0;
+}
+
+int vsa_sparse_fwd_combine_sharded(const void* q, const void* k_sh, const void* v_sh, const int32_t* selected,
+                                   const int32_t* kv_sizes, void* out_s, float* lse2, const void* out_c,
+                                   const void* gate, void* out, int64_t BH, int64_t Lq, int64_t Lkv, int64_t kv_shard,
+                                   int D, int be, int topk, float scale, int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(q && k_sh && v_sh && selected && kv_sizes && out_s && lse2, "sparse forward (sharded): null pointer");
+  VSA_REQUIRE((out == nullptr) == (out_c == nullptr), "sparse forward (sharded): give out_c and out together, or neither");
+  if ((rc = check_sharded(Lkv, kv_shard, D, be, topk, dtype, "sparse forward (sharded)"))) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  rc = sparse_fwd_umma(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, st, out_c, gate, out,
+                       kv_shard);
+  if (rc) return rc;
+  return sparse_fwd_tc(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, true, st, out_c, gate,
+                       out, kv_shard);
+}
+
+int vsa_sparse_bwd_dq_sharded(const void* dout, const void* q, const void* k_sh, const void* v_sh, const void* out_s,
+                              const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta,
+                              void* dq, const void* dq_mean, const int32_t* q_sizes, int64_t BH, int64_t Lq,
+                              int64_t Lkv, int64_t kv_shard, int D, int be, int topk, float scale, int dtype,
+                              void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && q && k_sh && v_sh && out_s && lse2 && selected && kv_sizes && delta && dq,
+              "sparse dQ (sharded): null pointer");
+  VSA_REQUIRE((dq_mean == nullptr) == (q_sizes == nullptr), "sparse dQ (sharded): give the pooled gradient and the query sizes, or neither");
+  if ((rc = check_sharded(Lkv, kv_shard, D, be, topk, dtype, "sparse dQ (sharded)"))) return rc;
+  return sparse_dq_umma(dout, q, k_sh, v_sh, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
+                        (cudaStream_t)stream, dq_mean, q_sizes, kv_shard);
+}
+
+int vsa_sparse_bwd_dkdv_sharded(const void* dout, const void* q, const void* k_sh, const void* v_sh, const float* lse2,
+                                const float* delta, const int32_t* counts, const int32_t* offsets,
+                                const int32_t* inverse, const int32_t* kv_sizes, void* dk_sh, void* dv_sh,
+                                const void* dk_mean, const void* dv_mean, int64_t BH, int64_t Lq, int64_t Lkv,
+                                int64_t kv_shard, int D, int be, int topk, float scale, int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && q && k_sh && v_sh && lse2 && delta && counts && offsets && inverse && kv_sizes && dk_sh && dv_sh,
+              "sparse dK/dV (sharded): null pointer");
+  VSA_REQUIRE((dk_mean == nullptr) == (dv_mean == nullptr), "sparse dK/dV (sharded): give both pooled gradients or neither");
+  if ((rc = check_sharded(Lkv, kv_shard, D, be, topk, dtype, "sparse dK/dV (sharded)"))) return rc;
+  return sparse_dkdv_umma(dout, q, k_sh, v_sh, lse2, delta, counts, offsets, inverse, kv_sizes, dk_sh, dv_sh, BH, Lq, Lkv, be,
+                          topk, scale, (cudaStream_t)stream, dk_mean, dv_mean, nullptr, kv_shard);
+}
+
 int vsa_gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
                     int64_t row_bytes, void* stream) {
   VSA_REQUIRE(src && map && dst, "gather rows: null pointer");

@@ -68,6 +68,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Row of token `token` of slice `bh` in a K/V-shaped tensor.  Ordinary tensors are [BH][Lkv][D] (shard == Lkv).  A
+// sequence-parallel all-gather leaves the shards of the W ranks one after another, [W][BH][Lkv/W][D]; with
+// shard = Lkv/W the same formula addresses that buffer in place, so nothing has to be re-laid-out after the gather
+// (and partial dK/dV written the same way are ready for the reduce-scatter).  A 64-token tile never straddles two
+// shards because the shard length is a multiple of the block volume.
+__device__ __forceinline__ long long kv_tensor_row(long long bh, long long BH, long long token, long long shard) {
+  const long long r = token / shard;
+  return (r * BH + bh) * shard + (token - r * shard);
+}
+
 // Gated combine of eight bf16 values: out = out_s + out_c * gate (gate optional) in fp32, one rounding -- the
 // arithmetic of the stand-alone combine pass, so fusing it into a kernel's store changes no bit.
 __device__ __forceinline__ uint4 combine_bf16x8(const uint4& s_raw, const uint4& c_raw, const uint4& g_raw, bool has_gate) {

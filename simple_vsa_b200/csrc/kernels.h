@@ -49,7 +49,7 @@ bool sparse_tc_eligible(int D, int be, int dtype);
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
                   bool redo_only, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
-                  void* out_comb = nullptr);
+                  void* out_comb = nullptr, int64_t kv_shard = 0);
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
                  const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
                  int64_t Lkv, int be, int topk, float scale, cudaStream_t st);
@@ -62,16 +62,17 @@ int sparse_dkdv_tc(const void* dout, const void* q, const void* k, const void* v
 bool sparse_umma_eligible(int D, int be, int dtype, int topk);
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                    cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr, void* out_comb = nullptr);
+                    cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr, void* out_comb = nullptr,
+                    int64_t kv_shard = 0);   // kv_shard: tokens per shard of a shard-major K/V buffer (0 = ordinary layout)
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
                    int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
-                   const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr);
+                   const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr, int64_t kv_shard = 0);
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
                      float scale, cudaStream_t st, const void* dk_mean = nullptr, const void* dv_mean = nullptr,
-                     void* ds_ws = nullptr);
+                     void* ds_ws = nullptr, int64_t kv_shard = 0);
 // the backward that forms dS once: the key-owned pass (above, with ds_ws and packed edges) stores it, this
 // query-owned pass multiplies it by K
 int64_t sparse_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk);

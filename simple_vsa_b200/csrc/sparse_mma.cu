@@ -109,8 +109,8 @@ __global__ void __launch_bounds__(kThreads, 2)
 sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
                       bf16* __restrict__ out, float* __restrict__ lse2, const bf16* __restrict__ out_c,
-                      const bf16* __restrict__ gate, bf16* __restrict__ out_comb, long long Lq, long long Lkv, int topk,
-                      float scale, int redo_only) {
+                      const bf16* __restrict__ gate, bf16* __restrict__ out_comb, long long Lq, long long Lkv,
+                      long long kv_shard, int topk, float scale, int redo_only) {
   extern __shared__ __align__(128) uint8_t smem[];
   if (redo_only) {   // only tiles the tcgen05 forward marked with a NaN statistic are recomputed
     const float mark = lse2[(long long)blockIdx.y * Lq + (long long)blockIdx.x * kTile];
@@ -126,8 +126,8 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
   const int Qb = (int)(Lq / (kTile * SUB));
   const int qb = qtile / SUB;
   const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
-  const bf16* kbase = k + bh * Lkv * kD;
-  const bf16* vbase = v + bh * Lkv * kD;
+  // rows of a key tile in the K/V tensors (a sequence-parallel gather leaves them shard-major: see kv_tensor_row)
+  auto kv_row = [&](long long token) -> long long { return kv_tensor_row(bh, gridDim.y, token, kv_shard); };
   const int n_iter = topk * SUB;
   const float c = scale * kLog2e;
 
@@ -150,9 +150,9 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
   int kvb = 0, valid = 0;
   int it = next_live(0, kvb, valid);
   if (it < n_iter) {
-    const long long row0 = (long long)kvb * (kTile * SUB) + (it % SUB) * kTile;
-    stage_tile(sK, kbase + row0 * kD, kTile, tid);
-    stage_tile(sV, vbase + row0 * kD, valid, tid);
+    const long long row0 = kv_row((long long)kvb * (kTile * SUB) + (it % SUB) * kTile);
+    stage_tile(sK, k + row0 * kD, kTile, tid);
+    stage_tile(sV, v + row0 * kD, valid, tid);
   }
   cp_async_commit();
 
@@ -168,9 +168,9 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
     int nkvb = 0, nvalid = 0;
     const int nxt = next_live(it + 1, nkvb, nvalid);
     if (nxt < n_iter) {
-      const long long row0 = (long long)nkvb * (kTile * SUB) + (nxt % SUB) * kTile;
-      stage_tile(sK + (stage ^ 1) * kTileBytes, kbase + row0 * kD, kTile, tid);
-      stage_tile(sV + (stage ^ 1) * kTileBytes, vbase + row0 * kD, nvalid, tid);
+      const long long row0 = kv_row((long long)nkvb * (kTile * SUB) + (nxt % SUB) * kTile);
+      stage_tile(sK + (stage ^ 1) * kTileBytes, k + row0 * kD, kTile, tid);
+      stage_tile(sV + (stage ^ 1) * kTileBytes, v + row0 * kD, nvalid, tid);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -583,8 +583,9 @@ bool sparse_tc_eligible(int D, int be, int dtype) { return dtype == VSA_BF16 && 
 
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                  bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb) {
+                  bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard) {
   if (BH == 0 || Lq == 0) return VSA_OK;
+  if (kv_shard <= 0) kv_shard = Lkv;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
   dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
   int rc;
@@ -592,12 +593,12 @@ int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* se
     if ((rc = set_smem(sparse_fwd_mma_kernel<1>, kFwdSmem, "sparse forward"))) return rc;
     sparse_fwd_mma_kernel<1><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
                                                                kv_sizes, (bf16*)out, lse2, (const bf16*)out_c, (const bf16*)gate,
-                                                               (bf16*)out_comb, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
+                                                               (bf16*)out_comb, Lq, Lkv, kv_shard, topk, scale, redo_only ? 1 : 0);
   } else {
     if ((rc = set_smem(sparse_fwd_mma_kernel<4>, kFwdSmem, "sparse forward"))) return rc;
     sparse_fwd_mma_kernel<4><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
                                                                kv_sizes, (bf16*)out, lse2, (const bf16*)out_c, (const bf16*)gate,
-                                                               (bf16*)out_comb, Lq, Lkv, topk, scale, redo_only ? 1 : 0);
+                                                               (bf16*)out_comb, Lq, Lkv, kv_shard, topk, scale, redo_only ? 1 : 0);
   }
   return check_launch("sparse_fwd_mma_kernel");
 }

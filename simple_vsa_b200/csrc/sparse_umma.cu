@@ -257,7 +257,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const int32_t* __restrict__ selected,
                        const int32_t* __restrict__ kv_sizes, bf16* __restrict__ out, float* __restrict__ lse2,
                        const bf16* __restrict__ out_c, const bf16* __restrict__ gate, bf16* __restrict__ out_comb,
-                       long long Lq, long long Lkv, int topk, float scale) {
+                       long long Lq, long long Lkv, long long kv_shard, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;   // an earlier wait ran out: drain without touching anything
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -306,7 +306,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // an id outside the table is an empty tile, as route inversion treats it
     const int left = (unsigned)kvb < (unsigned)(Lkv / (kTile * SUB)) ? kv_sizes[kvb] - (it % SUB) * kTile : 0;
     tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
-    tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
+    tile_row[it] = left > 0 ? (int)kv_tensor_row(bh, gridDim.y, (long long)kvb * (kTile * SUB) + (it % SUB) * kTile, kv_shard) : 0;
   }
   __syncthreads();
   if (warp == 2) {   // ... then one warp squeezes out the empty ones in place, keeping the routing order
@@ -338,7 +338,6 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_live = (int)misc[1];
   const int n_pairs = (n_live + 1) >> 1;
   const uint32_t tmem_s0 = tmem, tmem_o = tmem + 64 * kSBufs;   // S^T buffers first, then O^T
-  const long long kv_row_base = bh * Lkv;
   bool ok = true;
 
   if (warp == 0 || warp == 1) {
@@ -363,7 +362,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t ph = (p / depth) & 1;
         int idx = 2 * p + which;
         if (idx >= n_live) idx = 2 * p;                     // odd tail: repeat the first tile (masked later)
-        const int row = (int)(kv_row_base + tile_row[idx]);
+        const int row = tile_row[idx];                        // row of the tile in the K/V tensors
         ok = VSA_WARP_WAIT(bar(empty0 + s), ph ^ 1);
         if (!ok) break;
         if (lane < 4) {
@@ -559,10 +558,19 @@ bool sparse_umma_eligible(int D, int be, int dtype, int topk) {
   return false;
 }
 
+static int check_kv_shard(int64_t Lkv, int be, int64_t* kv_shard, const char* what) {
+  if (*kv_shard <= 0) *kv_shard = Lkv;
+  if (Lkv % *kv_shard || *kv_shard % be)
+    return fail(VSA_ERR_BAD_ARGUMENT, "%s: the K/V shard length %lld must divide Lkv = %lld and be a multiple of the block volume %d",
+                what, (long long)*kv_shard, (long long)Lkv, be);
+  return VSA_OK;
+}
+
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                    cudaStream_t st, const void* out_c, const void* gate, void* out_comb) {
+                    cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard) {
   if (BH == 0 || Lq == 0) return VSA_OK;
+  { const int rc0 = check_kv_shard(Lkv, be, &kv_shard, "sparse forward"); if (rc0) return rc0; }
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
   CUtensorMap mq, mk, mv;
   int rc;
@@ -576,12 +584,12 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
     e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
     sparse_fwd_umma_kernel<1><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, (const bf16*)out_c,
-                                                               (const bf16*)gate, (bf16*)out_comb, Lq, Lkv, topk, scale);
+                                                               (const bf16*)gate, (bf16*)out_comb, Lq, Lkv, kv_shard, topk, scale);
   } else {
     e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
     sparse_fwd_umma_kernel<4><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, (const bf16*)out_c,
-                                                               (const bf16*)gate, (bf16*)out_comb, Lq, Lkv, topk, scale);
+                                                               (const bf16*)gate, (bf16*)out_comb, Lq, Lkv, kv_shard, topk, scale);
   }
   return check_launch("sparse_fwd_umma_kernel");
 }
@@ -596,9 +604,10 @@ static int reserve_smem(Kern kern, int bytes, const char* what) {
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
                    int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
-                   const void* dq_mean, const int32_t* q_sizes) {
+                   const void* dq_mean, const int32_t* q_sizes, int64_t kv_shard) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dQ: batch*heads %lld exceeds 65535", (long long)BH);
+  { const int rc0 = check_kv_shard(Lkv, be, &kv_shard, "sparse dQ"); if (rc0) return rc0; }
   CUtensorMap mq, mdo, mk, mv;
   int rc;
   if ((rc = make_map(&mq, q, BH * Lq, "sparse dQ (q)"))) return rc;
@@ -611,12 +620,12 @@ int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v
     if ((rc = reserve_smem(sparse_dq_umma_kernel<1>, smem, "sparse dQ"))) return rc;
     sparse_dq_umma_kernel<1><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const bf16*)dout, (const bf16*)out_s, lse2,
                                                               selected, kv_sizes, delta, (bf16*)dq, (const bf16*)dq_mean, q_sizes, Lq, Lkv,
-                                                              topk, scale);
+                                                              kv_shard, topk, scale);
   } else {
     if ((rc = reserve_smem(sparse_dq_umma_kernel<4>, smem, "sparse dQ"))) return rc;
     sparse_dq_umma_kernel<4><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const bf16*)dout, (const bf16*)out_s, lse2,
                                                               selected, kv_sizes, delta, (bf16*)dq, (const bf16*)dq_mean, q_sizes, Lq, Lkv,
-                                                              topk, scale);
+                                                              kv_shard, topk, scale);
   }
   return check_launch("sparse_dq_umma_kernel");
 }
@@ -629,9 +638,11 @@ int64_t sparse_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk) {
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                     float scale, cudaStream_t st, const void* dk_mean, const void* dv_mean, void* ds_ws) {
+                     float scale, cudaStream_t st, const void* dk_mean, const void* dv_mean, void* ds_ws,
+                     int64_t kv_shard) {
   if (BH == 0 || Lkv == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: batch*heads %lld exceeds 65535", (long long)BH);
+  { const int rc0 = check_kv_shard(Lkv, be, &kv_shard, "sparse dK/dV"); if (rc0) return rc0; }
   if (ds_ws && topk > (1 << kEdgeSlotBits))
     return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: packed edges hold at most %d routes per query block", 1 << kEdgeSlotBits);
   CUtensorMap mq, mdo, mk, mv;
@@ -648,7 +659,7 @@ int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void*
     if ((rc = reserve_smem(kern, smem, "sparse dK/dV"))) return rc;
     kern<<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse, kv_sizes, (bf16*)dk,
                                           (bf16*)dv, (const bf16*)dk_mean, (const bf16*)dv_mean, (bf16*)ds_ws, Lq, Lkv,
-                                          topk, scale);
+                                          kv_shard, topk, scale);
     return check_launch("sparse_dkdv_umma_kernel");
   };
   if (be == 64) return ds_ws ? launch(sparse_dkdv_umma_kernel<1, true>) : launch(sparse_dkdv_umma_kernel<1, false>);

@@ -63,7 +63,8 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const bf16* __restrict__ dout, const bf16* __restrict__ out_s, const float* __restrict__ lse2,
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
                       float* __restrict__ delta, bf16* __restrict__ dq, const bf16* __restrict__ mean_grad,
-                      const int32_t* __restrict__ q_sizes, long long Lq, long long Lkv, int topk, float scale) {
+                      const int32_t* __restrict__ q_sizes, long long Lq, long long Lkv, long long kv_shard, int topk,
+                      float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -112,7 +113,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // an id outside the table is an empty tile, as route inversion treats it
     const int left = (unsigned)kvb < (unsigned)(Lkv / (kTile * SUB)) ? kv_sizes[kvb] - (it % SUB) * kTile : 0;
     tile_valid[it] = (uint8_t)(left < 0 ? 0 : (left > kTile ? kTile : left));
-    tile_row[it] = kvb * (kTile * SUB) + (it % SUB) * kTile;
+    tile_row[it] = left > 0 ? (int)kv_tensor_row(bh, gridDim.y, (long long)kvb * (kTile * SUB) + (it % SUB) * kTile, kv_shard) : 0;
   }
   if (warp >= 4 && warp < kDpWarp) {   // delta = rowsum(out_s * dout) and the saved statistic, eight threads per query row
     constexpr int kPer = kBwEwThreads / 64;            // threads per row
@@ -172,7 +173,6 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const int n_live = (int)misc[1];
   const int n_pairs = (n_live + 1) >> 1;
   const uint32_t tmem_acc = tmem + 128 * kDqBufs;
-  const long long kv_row_base = bh * Lkv;
   bool ok = true;
 
   if (warp == 0 || warp == 1) {
@@ -194,7 +194,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const uint32_t ph = (p / depth) & 1;
       int idx = 2 * p + which;
       if (idx >= n_live) idx = 2 * p;
-      const int row = (int)(kv_row_base + tile_row[idx]);
+      const int row = tile_row[idx];                          // row of the tile in the K/V tensors
       ok = VSA_WARP_WAIT(bar(empty0 + s), ph ^ 1);
       if (!ok) break;
       if (lane < 4) {
@@ -401,7 +401,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
                         bf16* __restrict__ dk, bf16* __restrict__ dv, const bf16* __restrict__ mean_grad_k,
                         const bf16* __restrict__ mean_grad_v, bf16* __restrict__ ds_ws, long long Lq, long long Lkv,
-                        int topk, float scale) {
+                        long long kv_shard, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -413,7 +413,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int kvb = ktile / SUB, sub = ktile % SUB;
   int valid = kv_sizes[kvb] - sub * kTile;
   valid = valid < 0 ? 0 : (valid > kTile ? kTile : valid);
-  const long long krow0 = bh * Lkv + (long long)ktile * kTile;
+  const long long krow0 = kv_tensor_row(bh, gridDim.y, (long long)ktile * kTile, kv_shard);   // K, V, dK, dV rows of this tile
   const int cnt = counts[bh * Kb + kvb];
   const int32_t* inv = inverse + bh * (long long)Qb * topk + offsets[bh * Kb + kvb];
   const int n_tiles = valid > 0 ? cnt * SUB : 0;

@@ -348,6 +348,132 @@ class _VideoSparseAttention(torch.autograd.Function):
         return dq, dk, dv, dgate, None, None, None, None, None, None
 
 
+class _ShardedVideoSparseAttention(torch.autograd.Function):
+    """One rank's part of the sequence-parallel operator: its own queries against the all-gathered K/V, read in the
+    shard-major layout the gather leaves (``[W, B, H, L/W, D]``), with the pooled keys/values of ALL blocks given.
+
+    The gradients returned for the gathered K/V are this rank's partial sums over its query blocks, in the same
+    shard-major layout (ready for a reduce-scatter); the pooled-branch gradients of the keys/values are folded into
+    them by the dK/dV kernel, so the pooled tensors themselves need no gradient path of their own."""
+
+    @staticmethod
+    def forward(ctx, q, k_sh, v_sh, gate, kc, vc, kv_sizes, q_sizes, topk, be, scale, need_grad):
+        B, H, Lq, D = q.shape
+        W, shard = k_sh.shape[0], k_sh.shape[3]
+        Lkv = W * shard
+        Qb, Kb = Lq // be, Lkv // be
+        dt = _check_device_dtype(q, k_sh, v_sh)
+        st = _stream(q.device)
+        dev, ty = q.device, q.dtype
+        qc = torch.empty((B, H, Qb, D), device=dev, dtype=ty)
+        call("vsa_block_mean_fwd", q.data_ptr(), q_sizes.data_ptr(), qc.data_ptr(), B * H, Lq, D, be, dt, st)
+        scores = torch.empty((B, H, Qb, Kb), device=dev, dtype=ty)
+        probs = torch.empty_like(scores)
+        out_c = torch.empty((B, H, Qb, D), device=dev, dtype=ty)
+        call("vsa_coarse_fwd", qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), scores.data_ptr(), probs.data_ptr(),
+             out_c.data_ptr(), B * H, Qb, Kb, D, scale, dt, st)
+        selected = torch.empty((B, H, Qb, topk), device=dev, dtype=torch.int32)
+        call("vsa_topk", scores.data_ptr(), selected.data_ptr(), B * H * Qb, Kb, topk, dt, st)
+        del scores
+        out_s, out = torch.empty_like(q), torch.empty_like(q)
+        lse = torch.empty((B, H, Lq), device=dev, dtype=torch.float32)
+        call("vsa_sparse_fwd_combine_sharded", q.data_ptr(), k_sh.data_ptr(), v_sh.data_ptr(), selected.data_ptr(),
+             kv_sizes.data_ptr(), out_s.data_ptr(), lse.data_ptr(), out_c.data_ptr(), _ptr(gate), out.data_ptr(), B * H,
+             Lq, Lkv, shard, D, be, topk, scale, dt, st)
+        if need_grad:
+            saved = [q, k_sh, v_sh, out_s, lse, selected, kv_sizes, q_sizes, qc, kc, vc, probs, out_c]
+            if gate is not None:
+                saved.append(gate)
+            ctx.save_for_backward(*saved)
+            ctx.has_gate = gate is not None
+            ctx.be, ctx.scale = be, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        saved = ctx.saved_tensors
+        q, k_sh, v_sh, out_s, lse, selected, kv_sizes, q_sizes, qc, kc, vc, probs, out_c = saved[:13]
+        gate = saved[13] if ctx.has_gate else None
+        be, scale = ctx.be, ctx.scale
+        B, H, Lq, D = q.shape
+        W, shard = k_sh.shape[0], k_sh.shape[3]
+        Lkv = W * shard
+        Qb, Kb, tk = Lq // be, Lkv // be, selected.shape[-1]
+        with torch.cuda.device(q.device):
+            dt = _check_device_dtype(q, k_sh, v_sh)
+            st = _stream(q.device)
+            dout = _dense(dout)
+            d_out_c = torch.empty_like(out_c)
+            dgate = torch.empty_like(gate) if gate is not None else None
+            call("vsa_combine_bwd", dout.data_ptr(), _ptr(gate), out_c.data_ptr(), d_out_c.data_ptr(), _ptr(dgate),
+                 B * H, Lq, D, be, dt, st)
+            ds_ws = torch.empty_like(probs)
+            rowdot = torch.empty((B, H, Qb), device=q.device, dtype=torch.float32)
+            dqc, dkc, dvc = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
+            call("vsa_coarse_bwd", d_out_c.data_ptr(), out_c.data_ptr(), qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                 probs.data_ptr(), ds_ws.data_ptr(), rowdot.data_ptr(), dqc.data_ptr(), dkc.data_ptr(),
+                 dvc.data_ptr(), B * H, Qb, Kb, D, scale, dt, st)
+            del ds_ws
+            inverse, offsets, counts = invert_routes(selected, Kb)
+            delta = torch.empty_like(lse)
+            dq = torch.empty_like(q)
+            dk_sh, dv_sh = torch.empty_like(k_sh), torch.empty_like(v_sh)
+            call("vsa_sparse_bwd_dq_sharded", dout.data_ptr(), q.data_ptr(), k_sh.data_ptr(), v_sh.data_ptr(),
+                 out_s.data_ptr(), lse.data_ptr(), selected.data_ptr(), kv_sizes.data_ptr(), delta.data_ptr(),
+                 dq.data_ptr(), dqc.data_ptr(), q_sizes.data_ptr(), B * H, Lq, Lkv, shard, D, be, tk, scale, dt, st)
+            # dkc / dvc are this rank's share of the pooled gradients of ALL key blocks: folded into its partial dK/dV
+            call("vsa_sparse_bwd_dkdv_sharded", dout.data_ptr(), q.data_ptr(), k_sh.data_ptr(), v_sh.data_ptr(),
+                 lse.data_ptr(), delta.data_ptr(), counts.data_ptr(), offsets.data_ptr(), inverse.data_ptr(),
+                 kv_sizes.data_ptr(), dk_sh.data_ptr(), dv_sh.data_ptr(), dkc.data_ptr(), dvc.data_ptr(), B * H, Lq, Lkv,
+                 shard, D, be, tk, scale, dt, st)
+        return dq, dk_sh, dv_sh, dgate, None, None, None, None, None, None, None, None
+
+
+def sharded_supported(q: Tensor, be: int, topk: int) -> bool:
+    """Whether the shard-major kernels cover these tensors (bf16, head dim 128, block volume 64 or 256, CUDA)."""
+    return bool(q.is_cuda and q.dtype == torch.bfloat16 and
+                _lib.lib.vsa_sparse_sharded_supported(q.shape[-1], be, topk, _lib.VSA_BF16))
+
+
+def vsa_on_gathered_shards(q, k_sh, v_sh, kc, vc, variable_block_sizes, q_variable_block_sizes, topk: int,
+                           block_size: BlockSize = 64, compress_attn_weight: Optional[Tensor] = None) -> Tensor:
+    """The operator for one rank of a sequence-parallel group: ``q [B,H,l,D]`` (this rank's queries),
+    ``k_sh, v_sh [W,B,H,l,D]`` (the all-gathered shards, rank-major, as the collective left them), ``kc, vc
+    [B,H,Kb,D]`` (pooled keys/values of all ``Kb = W*l/be`` blocks in global order, no gradient needed),
+    ``variable_block_sizes [Kb]``, ``q_variable_block_sizes [l/be]``.  Differentiable in q, k_sh, v_sh and the gate."""
+    be = as_block_elements(block_size)
+    B, H, Lq, D = q.shape
+    W, shard = k_sh.shape[0], k_sh.shape[3]
+    if tuple(k_sh.shape) != (W, B, H, shard, D) or v_sh.shape != k_sh.shape:
+        raise ValueError("k_sh and v_sh must have shape [world, batch, heads, shard_len, dim]")
+    Lkv = W * shard
+    if Lq % be or shard % be:
+        raise ValueError(f"q/kv sequence lengths must be divisible by block_elements={be}")
+    if variable_block_sizes.numel() != Lkv // be:
+        raise ValueError(f"variable_block_sizes must have length {Lkv // be}, got {variable_block_sizes.numel()}")
+    if q_variable_block_sizes.numel() != Lq // be:
+        raise ValueError(f"q_variable_block_sizes must have length {Lq // be}, got {q_variable_block_sizes.numel()}")
+    if not 1 <= topk <= Lkv // be:
+        raise ValueError(f"topk must be in [1, {Lkv // be}]")
+    if tuple(kc.shape) != (B, H, Lkv // be, D) or vc.shape != kc.shape:
+        raise ValueError("kc and vc must have shape [batch, heads, key_blocks, dim]")
+    gate = compress_attn_weight
+    if gate is not None and gate.shape != q.shape:
+        raise ValueError("compress_attn_weight must have the same shape as q")
+    if not sharded_supported(q, be, topk):
+        raise ValueError("the shard-major path needs bfloat16 CUDA tensors with head dim 128 and block volume 64 or 256")
+    scale = 1.0 / math.sqrt(D)
+    with torch.cuda.device(q.device):
+        q, k_sh, v_sh = _dense(q), _dense(k_sh), _dense(v_sh)
+        gate = _dense(gate.to(q.dtype)) if gate is not None else None
+        kv_sizes = _sizes(variable_block_sizes, q.device)
+        q_sizes = _sizes(q_variable_block_sizes, q.device)
+        need_grad = torch.is_grad_enabled() and any(
+            t is not None and t.requires_grad for t in (q, k_sh, v_sh, gate))
+        return _ShardedVideoSparseAttention.apply(q, k_sh, v_sh, gate, _dense(kc.detach()), _dense(vc.detach()),
+                                                  kv_sizes, q_sizes, int(topk), be, scale, need_grad)
+
+
 def vsa_forward_full(q, k, v, variable_block_sizes, q_variable_block_sizes, topk: int, block_size: BlockSize = 64,
                      compress_attn_weight: Optional[Tensor] = None, sm_scale: Optional[float] = None
                      ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:

@@ -6,11 +6,16 @@ Two modes, neither of which exists in the reference project (its kernels index e
 * **head sharding** -- the ``batch*heads`` slices are cut into contiguous ranges, one per rank, and
   each rank runs the ordinary operator on its range.  No data-path collective.
 * **sequence parallelism** (long sequences) -- each rank owns ``L/W`` query tokens and the matching
-  K/V shard.  K and V are all-gathered into local HBM (NCCL over NVLink), the rank then runs the
-  ordinary operator with its local queries against the full keys (``Lq != Lkv``: pooled scores
-  ``[Qb/W, Kb]``, Top-K and the fine kernels all work on global key-block ids), and the backward
-  reduce-scatters the partial dK/dV to their owners.  Remote data is always copied into the GPU's
-  own memory first; no kernel reads a peer's memory.
+  K/V shard.  K and V are all-gathered into local HBM (NCCL over NVLink) and stay in the rank-major
+  layout ``[W, B, H, L/W, D]`` the collective leaves: the fine kernels address that layout in place
+  (no re-layout copy after the gather), and write their partial dK/dV the same way, so that the
+  backward's reduce-scatter takes them as they are.  The pooled keys/values are not recomputed from
+  the gathered tokens: every rank pools its own shard and the small ``[B, H, Kb/W, D]`` results are
+  all-gathered.  The rank then runs pooled scores ``[Qb/W, Kb]``, Top-K and the fine kernels with its
+  local queries on global key-block ids (``Lq != Lkv``).  Remote data is always copied into the GPU's
+  own memory first; no kernel reads a peer's memory.  Tensors the shard-major kernels do not cover
+  (anything but bf16 / head dim 128 / block volume 64 or 256, and CPU ranks with a stand-in operator)
+  take the generic form: gather, re-lay-out to ``[B, H, L, D]``, ordinary operator.
 """
 
 from __future__ import annotations
@@ -65,6 +70,47 @@ class _GatherSequence(torch.autograd.Function):
         return out, None
 
 
+class _GatherShards(torch.autograd.Function):
+    """all-gather that keeps the collective's own layout: ``[B,H,l,D]`` shards -> ``[W,B,H,l,D]`` (rank-major).
+    The backward reduce-scatters a gradient of that shape, which is already contiguous per owner rank."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group) -> Tensor:
+        world = dist.get_world_size(group)
+        ctx.group, ctx.world = group, world
+        x = x.contiguous()
+        gathered = torch.empty((world,) + tuple(x.shape), device=x.device, dtype=x.dtype)
+        dist.all_gather_into_tensor(gathered.view((world * x.shape[0],) + tuple(x.shape[1:])), x, group=group)
+        return gathered
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        world, group = ctx.world, ctx.group
+        grad = grad.contiguous()
+        out = torch.empty(tuple(grad.shape[1:]), device=grad.device, dtype=grad.dtype)
+        dist.reduce_scatter_tensor(out, grad.view((world * grad.shape[1],) + tuple(grad.shape[2:])),
+                                   op=dist.ReduceOp.SUM, group=group)
+        return out, None
+
+
+def gather_shards(x: Tensor, group=None) -> Tensor:
+    """Differentiable all-gather of ``[B,H,L/W,D]`` shards into the rank-major ``[W,B,H,L/W,D]``."""
+    return _GatherShards.apply(x, group)
+
+
+def gather_pooled(x_local: Tensor, sizes_local: Tensor, block_elements: int, group=None) -> Tensor:
+    """Block means of this rank's shard, all-gathered into ``[B,H,Kb,D]`` in global block order (no gradient:
+    the pooled-branch gradients reach K and V through the dK/dV kernel of the shard-major operator)."""
+    from .ops import block_mean
+    world = dist.get_world_size(group)
+    with torch.no_grad():
+        mean = block_mean(x_local.detach(), sizes_local, block_elements)            # [B,H,Kb/W,D]
+        B, H, nbl, D = mean.shape
+        out = torch.empty((world * B, H, nbl, D), device=mean.device, dtype=mean.dtype)
+        dist.all_gather_into_tensor(out, mean.contiguous(), group=group)
+        return out.view(world, B, H, nbl, D).permute(1, 2, 0, 3, 4).reshape(B, H, world * nbl, D)
+
+
 def gather_sequence(x: Tensor, group=None) -> Tensor:
     """Differentiable all-gather of ``[B,H,L/W,D]`` shards into ``[B,H,L,D]`` (rank order = sequence order)."""
     return _GatherSequence.apply(x, group)
@@ -95,11 +141,19 @@ def sequence_parallel_vsa(q_local: Tensor, k_local: Tensor, v_local: Tensor, var
     operator and exists so that the glue can be exercised on CPU ranks with a stand-in.  The heads are
     processed in ``head_chunks`` groups so that the collectives of one group overlap the kernels of another.
     """
+    sharded = False
     if local_op is None:
         from . import b200_vsa as local_op
+        from .ops import as_block_elements, sharded_supported
+        sharded = sharded_supported(q_local, as_block_elements(block_size), topk) and \
+            dist.get_backend(group) == "nccl"
     H = q_local.shape[1]
     spans = _head_chunks(H, head_chunks)
     on_gpu = q_local.is_cuda
+    if sharded:
+        return _sequence_parallel_sharded(q_local, k_local, v_local, variable_block_sizes,
+                                          q_variable_block_sizes_local, topk, block_size,
+                                          compress_attn_weight_local, group, spans)
     if len(spans) == 1 or not on_gpu:
         outs = []
         for h0, h1 in spans:     # same arithmetic as the overlapped form below, on one stream
@@ -138,6 +192,44 @@ def sequence_parallel_vsa(q_local: Tensor, k_local: Tensor, v_local: Tensor, var
         outs.append(local_op(q_local[:, h0:h1], kf, vf, variable_block_sizes, q_variable_block_sizes_local, topk,
                              block_size, gate))
     return torch.cat(outs, dim=1)
+
+
+def _sequence_parallel_sharded(q_local, k_local, v_local, variable_block_sizes, q_sizes_local, topk, block_size,
+                               gate_local, group, spans):
+    """The GPU form: per head group, K/V shards and pooled blocks are gathered on a side stream one group ahead of
+    the compute and consumed in the layout the collective leaves."""
+    from .ops import as_block_elements, vsa_on_gathered_shards
+    be = as_block_elements(block_size)
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    nbl = k_local.shape[2] // be
+    sizes_local = variable_block_sizes[rank * nbl:(rank + 1) * nbl]
+    main = torch.cuda.current_stream(q_local.device)
+    comm = _comm_stream(q_local.device)
+
+    def start_gather(h0, h1):
+        comm.wait_stream(main)
+        with torch.cuda.stream(comm):
+            k_sh = gather_shards(k_local[:, h0:h1], group)
+            v_sh = gather_shards(v_local[:, h0:h1], group)
+            kc = gather_pooled(k_local[:, h0:h1], sizes_local, be, group)
+            vc = gather_pooled(v_local[:, h0:h1], sizes_local, be, group)
+            done = torch.cuda.Event()
+            done.record(comm)
+        return k_sh, v_sh, kc, vc, done
+
+    pending = [start_gather(*spans[0])]
+    outs = []
+    for i, (h0, h1) in enumerate(spans):
+        if i + 1 < len(spans):
+            pending.append(start_gather(*spans[i + 1]))
+        k_sh, v_sh, kc, vc, done = pending[i]
+        main.wait_event(done)
+        for t in (k_sh, v_sh, kc, vc):
+            t.record_stream(main)
+        gate = gate_local[:, h0:h1] if gate_local is not None else None
+        outs.append(vsa_on_gathered_shards(q_local[:, h0:h1], k_sh, v_sh, kc, vc, variable_block_sizes, q_sizes_local,
+                                           topk, block_size, gate))
+    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
 
 
 _COMM_STREAMS = {}

@@ -746,3 +746,45 @@ def test_forward_with_the_combine_folded_in_equals_the_two_step_form(kernels, wi
         assert torch.equal(got, want)
         _assert_close(want, O.combine(out_s.cpu(), out_c.cpu(), gate.cpu() if with_gate else None, be, torch.bfloat16),
                       atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("be,nb,tk,W", [(64, 16, 5, 2), (64, 24, 6, 4), (256, 8, 3, 2)])
+def test_shard_major_kv_layout_equals_the_ordinary_layout(be, nb, tk, W):
+    """The kernels of the sequence-parallel mode read K/V (and write dK/dV) in the rank-major layout an all-gather
+    leaves, ``[W,B,H,L/W,D]``.  One GPU, no collective: the same operator on the same numbers in both layouts, a
+    rank's share of the queries against all keys, ragged blocks, a gate, and a scaled key block so that the exact
+    redo kernel takes part."""
+    V = _V()
+    from simple_vsa_b200 import ops
+    torch.manual_seed(99)
+    B, H, D = 1, 3, 128
+    L = be * nb
+    l = L // W
+    q_all, k, v = (torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16) for _ in range(3))
+    k[:, :, 5 * 64:6 * 64] *= 30.0
+    sizes = torch.full((nb,), be)
+    sizes[1], sizes[nb - 2] = be // 2 + 3, 7
+    for rank in (0, W - 1):
+        sl = slice(rank * l, (rank + 1) * l)
+        q = q_all[:, :, sl].contiguous()
+        gate = torch.randn(B, H, l, D, device=DEV).to(torch.bfloat16)
+        dout = torch.randn(B, H, l, D, device=DEV).to(torch.bfloat16)
+        q_sizes = sizes[rank * (nb // W):(rank + 1) * (nb // W)]
+        a = [t.clone().requires_grad_() for t in (q, k, v, gate)]
+        out_a = V.b200_vsa(a[0], a[1], a[2], sizes, q_sizes, tk, (1, 1, be), a[3])
+        out_a.backward(dout)
+        k_sh = k.view(B, H, W, l, D).permute(2, 0, 1, 3, 4).contiguous().requires_grad_()
+        v_sh = v.view(B, H, W, l, D).permute(2, 0, 1, 3, 4).contiguous().requires_grad_()
+        kc, vc = V.block_mean(k, sizes, be), V.block_mean(v, sizes, be)
+        b = [q.clone().requires_grad_(), gate.clone().requires_grad_()]
+        out_b = ops.vsa_on_gathered_shards(b[0], k_sh, v_sh, kc, vc, sizes, q_sizes, tk, (1, 1, be), b[1])
+        out_b.backward(dout)
+        assert torch.isfinite(out_b.float()).all()
+        assert torch.equal(out_b, out_a)                       # same routes, same tiles, same order
+        assert torch.equal(b[0].grad, a[0].grad) and torch.equal(b[1].grad, a[3].grad)
+        for got_sh, want in ((k_sh.grad, a[1].grad), (v_sh.grad, a[2].grad)):
+            got = got_sh.permute(1, 2, 0, 3, 4).reshape(B, H, L, D)
+            _assert_close(got, want, atol=2e-2, rtol=2e-2)     # CSR rows are unordered: fp32 sums in another order
+    with pytest.raises(ValueError, match="shard-major"):
+        ops.vsa_on_gathered_shards(q.float(), k_sh.detach().float(), v_sh.detach().float(), kc.float(), vc.float(),
+                                   sizes, q_sizes, tk, (1, 1, be))
