@@ -68,6 +68,20 @@ int64_t vsa_launch_count(void);
  * pointers and the stream before calling; the status word is per device.  No reference counterpart. */
 int vsa_device_status(int* status);
 
+/* Size in bytes of a scratch or intermediate buffer the caller must provide (nothing is allocated by the
+ * library): which = one of vsa_scratch.  -1 for an unknown buffer, dtype or a negative extent.
+ * No reference counterpart (it allocates with torch inside its launchers). */
+typedef enum vsa_scratch {
+  VSA_SCRATCH_SCORES = 0,    /* scores, probs, dscores_ws: [BH, Qb, Kb] of dtype                    */
+  VSA_SCRATCH_ROWDOT = 1,    /* rowdot_ws: [BH, Qb] fp32                                             */
+  VSA_SCRATCH_ROW_STATS = 2, /* lse2, delta: [BH, Lq] fp32                                           */
+  VSA_SCRATCH_CSR_ROWS = 3,  /* counts, offsets, cursor_ws: [BH, Kb] int32                           */
+  VSA_SCRATCH_CSR_EDGES = 4, /* inverse / inverse_edges: [BH, Qb*topk] int32                         */
+  VSA_SCRATCH_POOLED = 5,    /* q_mean and its gradient: [BH, Qb, D] of dtype (Kb for k_mean, v_mean) */
+  VSA_SCRATCH_DS_TILES = 6   /* ds_ws of the stored-dS backward (= vsa_sparse_bwd_ds_workspace_bytes) */
+} vsa_scratch;
+int64_t vsa_workspace_bytes(int which, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, int dtype);
+
 /* Exercises the time-out path without making anything fail: one warp waits up to limit_ns
  * (1 us .. 100 ms) on a barrier nothing arrives at, gives up, records code 201 in the status word, writes
  * 1 to *gave_up (a device pointer) and returns.  For tests of the reporting path. */
@@ -167,6 +181,8 @@ int vsa_route_invert(const int32_t* selected, int32_t* counts, int32_t* offsets,
  * the array's device address (cudaGetSymbolAddress), so make that first call before any stream
  * capture.  All calls share the one array: calls that overlap on the same GPU race and must be
  * serialised by the caller; no state carries over between calls (every entry used is rewritten).
+ * The looked-up address is kept per device ordinal (ordinals 0..63) for the life of the process: after a
+ * cudaDeviceReset, or any other re-creation of the device's primary context, reload the library.
  * No counterpart in the reference (it always allocates with torch). */
 int vsa_route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offsets,
                             int32_t* inverse, int64_t BH, int Qb, int Kb, int topk, void* stream);

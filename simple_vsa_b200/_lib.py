@@ -51,6 +51,7 @@ SIGNATURES = {
 }
 PLAIN = {"vsa_last_error_string": ([], c_char_p), "vsa_version": ([], c_int),
          "vsa_launch_count": ([], c_int64),
+         "vsa_workspace_bytes": ([I, L, L, L, I, I, I, I], c_int64),
          "vsa_sparse_bwd_ds_supported": ([I, I, I, I], c_int),
          "vsa_sparse_sharded_supported": ([I, I, I, I], c_int),
          "vsa_sparse_bwd_ds_workspace_bytes": ([L, L, I, I], c_int64)}

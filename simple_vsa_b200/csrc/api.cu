@@ -433,6 +433,22 @@ int vsa_selftest_umma(const void* a, const void* b, float* out, int mode, void* 
   return umma_selftest(a, b, out, mode, (cudaStream_t)stream);
 }
 
+int64_t vsa_workspace_bytes(int which, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, int dtype) {
+  if (BH < 0 || Lq < 0 || Lkv < 0 || D < 1 || be < 1 || topk < 0) return -1;
+  if (dtype != VSA_BF16 && dtype != VSA_F32 && dtype != VSA_F16) return -1;
+  const int64_t es = dtype == VSA_F32 ? 4 : 2, Qb = Lq / be, Kb = Lkv / be;
+  switch (which) {
+    case VSA_SCRATCH_SCORES: return BH * Qb * Kb * es;
+    case VSA_SCRATCH_ROWDOT: return BH * Qb * 4;
+    case VSA_SCRATCH_ROW_STATS: return BH * Lq * 4;
+    case VSA_SCRATCH_CSR_ROWS: return BH * Kb * 4;
+    case VSA_SCRATCH_CSR_EDGES: return BH * Qb * (int64_t)topk * 4;
+    case VSA_SCRATCH_POOLED: return BH * Qb * (int64_t)D * es;
+    case VSA_SCRATCH_DS_TILES: return be % 64 == 0 ? sparse_ds_workspace_bytes(BH, Lq, be, topk) : -1;
+    default: return -1;
+  }
+}
+
 int vsa_selftest_wait_timeout(int64_t limit_ns, int* gave_up, void* stream) {
   VSA_REQUIRE(gave_up, "wait self-test: null pointer");
   VSA_REQUIRE(limit_ns >= 1000 && limit_ns <= 100000000LL, "wait self-test: the limit must lie in [1 us, 100 ms]");

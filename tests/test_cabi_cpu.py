@@ -100,3 +100,38 @@ def test_compression_gate_shape_layout_and_argument_check():
     assert torch.equal(gate[1, 2, 5], want[1, 5, 2 * head_dim:3 * head_dim])
     with pytest.raises(ValueError, match="divisible"):
         V.CompressionGate(dim=10, num_heads=3)
+
+
+def test_workspace_sizes_and_support_queries_need_no_gpu():
+    import simple_vsa_b200._lib as L
+    lib = L.lib
+    BH, Lq, Lkv, D, be, tk = 80, 92160, 92160, 128, 64, 180
+    Qb = Kb = Lq // be
+    assert lib.vsa_workspace_bytes(0, BH, Lq, Lkv, D, be, tk, L.VSA_BF16) == BH * Qb * Kb * 2
+    assert lib.vsa_workspace_bytes(1, BH, Lq, Lkv, D, be, tk, L.VSA_BF16) == BH * Qb * 4
+    assert lib.vsa_workspace_bytes(2, BH, Lq, Lkv, D, be, tk, L.VSA_F32) == BH * Lq * 4
+    assert lib.vsa_workspace_bytes(3, BH, Lq, Lkv, D, be, tk, L.VSA_BF16) == BH * Kb * 4
+    assert lib.vsa_workspace_bytes(4, BH, Lq, Lkv, D, be, tk, L.VSA_BF16) == BH * Qb * tk * 4
+    assert lib.vsa_workspace_bytes(5, BH, Lq, Lkv, D, be, tk, L.VSA_F16) == BH * Qb * D * 2
+    assert lib.vsa_workspace_bytes(6, BH, Lq, Lkv, D, be, tk, L.VSA_BF16) == BH * Qb * tk * 8192 == \
+        lib.vsa_sparse_bwd_ds_workspace_bytes(BH, Lq, be, tk)
+    assert lib.vsa_workspace_bytes(6, 1, 1024, 1024, D, 256, 3, L.VSA_BF16) == 4 * 3 * 16 * 8192
+    assert lib.vsa_workspace_bytes(9, BH, Lq, Lkv, D, be, tk, L.VSA_BF16) == -1
+    assert lib.vsa_workspace_bytes(0, BH, Lq, Lkv, D, be, tk, 7) == -1
+    assert lib.vsa_sparse_bwd_ds_workspace_bytes(1, 1024, 48, 3) == -1
+    # the tensor path covers bf16, head dim 128, block volume 64 or 256 only
+    assert lib.vsa_sparse_sharded_supported(128, 64, 180, L.VSA_BF16) == 1
+    assert lib.vsa_sparse_sharded_supported(64, 64, 4, L.VSA_BF16) == 0
+    assert lib.vsa_sparse_bwd_ds_supported(128, 256, 20, L.VSA_BF16) == 1
+    assert lib.vsa_sparse_bwd_ds_supported(128, 64, 180, L.VSA_F32) == 0
+
+
+def test_host_step_helpers():
+    from simple_vsa_b200.host import _chunk_spans, _parse_cpulist
+    for total, per in ((80, 4), (10, 4), (1, 8), (7, 3), (40, 40)):
+        spans = _chunk_spans(total, per)
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert max(hi - lo for lo, hi in spans) <= max(1, min(per, total))
+    assert _parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert _parse_cpulist("") == set()
