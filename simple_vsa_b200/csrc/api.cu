@@ -67,7 +67,7 @@ extern "C" {
 
 const char* vsa_last_error_string(void) { return g_error; }
 
-int vsa_version(void) { return 100; }
+int vsa_version(void) { return 200; }
 
 int64_t vsa_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 

@@ -26,6 +26,9 @@
 // device status word, stops issuing work, frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -558,6 +561,13 @@ bool sparse_umma_eligible(int D, int be, int dtype, int topk) {
   return false;
 }
 
+template <typename Kern>
+static int reserve_smem(Kern kern, int bytes, const char* what) {
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "%s: shared memory: %s", what, cudaGetErrorString(e));
+  return VSA_OK;
+}
+
 static int check_kv_shard(int64_t Lkv, int be, int64_t* kv_shard, const char* what) {
   if (*kv_shard <= 0) *kv_shard = Lkv;
   if (Lkv % *kv_shard || *kv_shard % be)
@@ -592,13 +602,6 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
                                                                (const bf16*)gate, (bf16*)out_comb, Lq, Lkv, kv_shard, topk, scale);
   }
   return check_launch("sparse_fwd_umma_kernel");
-}
-
-template <typename Kern>
-static int reserve_smem(Kern kern, int bytes, const char* what) {
-  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "%s: shared memory: %s", what, cudaGetErrorString(e));
-  return VSA_OK;
 }
 
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,

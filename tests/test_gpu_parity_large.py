@@ -256,3 +256,35 @@ def _whole_operator_sampled(V, B, H, L, D, be, tk, *, block_size, ragged_frac, w
                 s = max(1.0, float(w.float().abs().max()) / 8.0)
                 _close(leaf.grad[:, h:h + 1, krows.to(DEV)], w, 3e-2 * s, 3e-2,
                        f"{name} (head {h}, in-degrees {[int(counts[p]) for p in picks]})")
+
+
+def test_shard_major_layout_at_92k_tokens_eight_shards():
+    """The long-sequence layout of the sequence-parallel mode at its real proportions: 92,160 key tokens in eight
+    rank-major shards of 11,520, one rank's 11,520 queries, topk 180 -- against the ordinary layout on the same
+    numbers (itself checked against the oracle above).  Output and dQ must be bit-identical (same routes, same tiles,
+    same order); dK/dV agree up to the order of the fp32 sums."""
+    V = _V()
+    from simple_vsa_b200 import ops
+    B, H, L, D, be, tk, W = 1, 2, 92160, 128, 64, 180, 8
+    l, nb = L // W, L // be
+    k, v = (_randn((B, H, L, D), 500 + i) for i in range(2))
+    sizes = torch.full((nb,), be)
+    rank = 5
+    q = _randn((B, H, l, D), 510)
+    dout = _randn((B, H, l, D), 511)
+    q_sizes = sizes[rank * (nb // W):(rank + 1) * (nb // W)]
+    a = [t.clone().requires_grad_() for t in (q, k, v)]
+    out_a = V.b200_vsa(a[0], a[1], a[2], sizes, q_sizes, tk, (4, 4, 4))
+    out_a.backward(dout)
+    k_sh = k.view(B, H, W, l, D).permute(2, 0, 1, 3, 4).contiguous().requires_grad_()
+    v_sh = v.view(B, H, W, l, D).permute(2, 0, 1, 3, 4).contiguous().requires_grad_()
+    kc, vc = V.block_mean(k, sizes, be), V.block_mean(v, sizes, be)
+    qb_ = q.clone().requires_grad_()
+    out_b = ops.vsa_on_gathered_shards(qb_, k_sh, v_sh, kc, vc, sizes, q_sizes, tk, (4, 4, 4))
+    out_b.backward(dout)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out_b.float()).all()
+    assert torch.equal(out_b, out_a) and torch.equal(qb_.grad, a[0].grad)
+    for got_sh, want in ((k_sh.grad, a[1].grad), (v_sh.grad, a[2].grad)):
+        got = got_sh.permute(1, 2, 0, 3, 4).reshape(B, H, L, D)
+        _close(got, want, 2e-2, 2e-2, "shard-major dK/dV")
