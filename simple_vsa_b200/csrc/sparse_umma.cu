@@ -548,6 +548,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
+#include "sparse_umma_fwd_persistent.inl"
 #include "sparse_umma_bwd.inl"
 #include "coarse_umma.inl"
 
@@ -587,6 +588,30 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
   if ((rc = make_map(&mq, q, BH * Lq, "sparse forward (q)"))) return rc;
   if ((rc = make_map(&mk, k, BH * Lkv, "sparse forward (k)"))) return rc;
   if ((rc = make_map(&mv, v, BH * Lkv, "sparse forward (v)"))) return rc;
+  // Two schedules of the same arithmetic.  One CTA per query tile is faster when a tile walks many pairs (the
+  // headline shape: 90); with short routes the per-CTA set-up and drain are a large share of a CTA's life and the
+  // persistent form (one CTA per SM, next tile's list, loads and first S^T MMAs under the current tile's epilogue)
+  // wins: measured -7 % at 16 pairs per tile, -9 % at 8, +1 % at 40, +4 % at 90.  VSA_B200_FWD=classic|persistent
+  // overrides the choice.
+  const char* fwd_env = std::getenv("VSA_B200_FWD");
+  bool persistent = topk * (be / kTile) <= 48;
+  if (fwd_env && std::strcmp(fwd_env, "persistent") == 0) persistent = true;
+  if (fwd_env && std::strcmp(fwd_env, "classic") == 0) persistent = false;
+  if (persistent) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return fail(VSA_ERR_LAUNCH, "sparse forward: cannot read the SM count of the current device");
+    const long long items = (Lq / kTile) * BH;
+    const unsigned ctas = (unsigned)std::min<long long>(items, sms);
+    const int psmem = FwdPSmem::total + 1024;
+    auto launch = [&](auto kern) -> int {
+      if ((rc = reserve_smem(kern, psmem, "sparse forward"))) return rc;
+      kern<<<ctas, kFwdPThreads, psmem, st>>>(mq, mk, mv, selected, kv_sizes, (bf16*)out, lse2, (const bf16*)out_c,
+                                              (const bf16*)gate, (bf16*)out_comb, (long long)BH, Lq, Lkv, kv_shard, topk, scale);
+      return check_launch("sparse_fwd_umma_persistent_kernel");
+    };
+    return be == 64 ? launch(sparse_fwd_umma_persistent_kernel<1>) : launch(sparse_fwd_umma_persistent_kernel<4>);
+  }
   const int smem = FwdSmem::total + 1024;
   dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
   cudaError_t e;

@@ -788,3 +788,34 @@ def test_shard_major_kv_layout_equals_the_ordinary_layout(be, nb, tk, W):
     with pytest.raises(ValueError, match="shard-major"):
         ops.vsa_on_gathered_shards(q.float(), k_sh.detach().float(), v_sh.detach().float(), kc.float(), vc.float(),
                                    sizes, q_sizes, tk, (1, 1, be))
+
+
+@pytest.mark.parametrize("be,nb,tk", [(64, 40, 7), (64, 24, 24), (256, 6, 3)])
+def test_the_two_schedules_of_the_forward_give_the_same_bits(be, nb, tk, monkeypatch):
+    """One CTA per query tile and the persistent form (one CTA per SM walking the query tiles, chosen for short
+    routes) run the same arithmetic in the same order: outputs, statistics and combined outputs are bit-identical,
+    with ragged blocks, an odd number of live tiles, an empty route and more query tiles than SMs."""
+    from simple_vsa_b200 import ops
+    torch.manual_seed(101)
+    B, H, D = 1, 5, 128
+    L = be * nb
+    q, k, v = (torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16) for _ in range(3))
+    out_c = torch.randn(B, H, nb, D, device=DEV).to(torch.bfloat16)
+    gate = torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16)
+    sizes = torch.full((nb,), be, dtype=torch.int32, device=DEV)
+    sizes[1], sizes[3], sizes[nb - 1] = be // 2 + 1, 0, 5
+    selected = torch.stack([torch.randperm(nb)[:tk] for _ in range(B * H * nb)]).view(B, H, nb, tk).to(torch.int32).to(DEV)
+    selected[0, 2, 4, :] = 3                       # a query block whose whole route is the empty block
+    scale = 1.0 / math.sqrt(D)
+    results = {}
+    for mode in ("classic", "persistent"):
+        monkeypatch.setenv("VSA_B200_FWD", mode)
+        results[mode] = ops.sparse_forward(q, k, v, selected, sizes, be, scale, True, combine_with=(out_c, gate))
+    for a, b in zip(results["classic"], results["persistent"]):
+        assert torch.equal(torch.nan_to_num(a.float(), nan=7.0), torch.nan_to_num(b.float(), nan=7.0))
+    out_s = results["persistent"][0]
+    live = torch.ones(B, H, L, dtype=torch.bool)
+    live[0, 2, 4 * be:5 * be] = False                # the rows of the empty route are NaN in both, as in the oracle
+    want = O.sparse_attention(q.cpu(), k.cpu(), v.cpu(), selected.cpu(), sizes.cpu(), be)
+    _assert_close(out_s.cpu()[live], want[live], atol=2e-2, rtol=2e-2)
+    assert torch.isnan(out_s.float().cpu()[~live]).all()
