@@ -572,6 +572,9 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
                 "copy_floor_note": "same chunked host<->device copy schedule with the operator left out, max over ranks; "
                                    "the end-to-end step cannot be faster than this on this machine",
                 "copy_gbs_per_direction_per_gpu": n_in * T_rank / (ms_floor * 1e-3) / 1e9,
+                # what the end-to-end step can at best be: the slower of the device-resident step and the copies alone
+                "bound": "host<->device copies" if ms_floor > ms_dev else "kernels",
+                "over_bound": ms_e2e / max(ms_floor, ms_dev),
                 "numa_node_bound": numa_node},
         "gpu_launches": launches,
         "clocks": clocks,
