@@ -819,3 +819,49 @@ def test_the_two_schedules_of_the_forward_give_the_same_bits(be, nb, tk, monkeyp
     want = O.sparse_attention(q.cpu(), k.cpu(), v.cpu(), selected.cpu(), sizes.cpu(), be)
     _assert_close(out_s.cpu()[live], want[live], atol=2e-2, rtol=2e-2)
     assert torch.isnan(out_s.float().cpu()[~live]).all()
+
+
+@pytest.mark.parametrize("seed", list(range(10)))
+def test_random_shapes_tensor_path_matches_cuda_core_path(seed, monkeypatch):
+    """Seeded random problems (block 64 or 256, 1..40 blocks, any topk, query length != key length, random ragged
+    and empty blocks, with and without a gate): the whole operator on the tcgen05 kernels against the same call on
+    the CUDA-core kernels, forward and every gradient.  The routes are fixed by the first run's Top-K (pooled scores
+    are computed by the same kernels in both runs)."""
+    V = _V()
+    g = torch.Generator().manual_seed(1000 + seed)
+    ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+    be = 64 if ri(0, 3) else 256
+    Kb = ri(1, 40 if be == 64 else 10)
+    Qb = ri(1, 24 if be == 64 else 6)
+    tk = ri(1, Kb)
+    B, H, D = ri(1, 2), ri(1, 3), 128
+    q = torch.randn(B, H, Qb * be, D, generator=g).to(torch.bfloat16)
+    k, v = (torch.randn(B, H, Kb * be, D, generator=g).to(torch.bfloat16) for _ in range(2))
+    dout = torch.randn(B, H, Qb * be, D, generator=g).to(torch.bfloat16)
+    gate = torch.randn(B, H, Qb * be, D, generator=g).to(torch.bfloat16) if ri(0, 1) else None
+    kv_sizes = torch.full((Kb,), be)
+    q_sizes = torch.full((Qb,), be)
+    for sizes in (kv_sizes, q_sizes):
+        for _ in range(ri(0, 3)):
+            sizes[ri(0, sizes.numel() - 1)] = ri(0, be)
+    if int(kv_sizes.sum()) == 0:
+        kv_sizes[0] = 1
+    results = {}
+    for mode in ("auto", "scalar"):
+        monkeypatch.setenv("VSA_B200_KERNELS", mode)
+        leaves = [t.to(DEV).requires_grad_() for t in (q, k, v)]
+        gl = gate.to(DEV).requires_grad_() if gate is not None else None
+        out, aux = V.video_sparse_attn(*leaves, kv_sizes, q_sizes, tk, (1, 1, be), gl, return_aux=True)
+        out.backward(dout.to(DEV))
+        results[mode] = [out.detach(), aux["selected"]] + [t.grad for t in leaves] + ([gl.grad] if gl is not None else [])
+    a, b = results["auto"], results["scalar"]
+    same_routes = torch.equal(a[1], b[1])
+    assert same_routes, "the pooled branch must not depend on the fine kernels' path"
+    # a query block whose selected blocks are all empty has no defined output (NaN in both paths, as in the reference)
+    finite = torch.isfinite(b[0].float())
+    assert torch.equal(finite, torch.isfinite(a[0].float()))
+    _assert_close(torch.where(finite, a[0].float(), torch.zeros(())), torch.where(finite, b[0].float(), torch.zeros(())),
+                  atol=2e-2, rtol=2e-2)
+    if bool(finite.all()):
+        for x, y in zip(a[2:], b[2:]):
+            _assert_close(x, y, atol=3e-2, rtol=3e-2)
