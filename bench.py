@@ -65,6 +65,8 @@ WORKLOADS = {
     "c4_92k_routes_local": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="local"),
     "c4_92k_routes_hotset": dict(B=1, H=40, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=False, routes="hotset"),
     # the reference's own CPU-runnable case: fp32, 16 full blocks of 64, head dim 64, topk 4 (fp32 runs on the CUDA-core kernels)
+    # the profiling case in fp16: the same tcgen05 kernels instantiated for the other 16-bit input format
+    "mid_92k_h8_tk180_gate_fp16": dict(B=1, H=8, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=True, dtype="f16"),
     "c1_1k_be64_tk4_fp32": dict(B=1, H=2, L=1024, D=64, block_size=(1, 1, 64), topk=4, gate=False, dtype="f32"),
 }
 DEFAULT_WORKLOAD = "c5_92k_be64_tk180"
@@ -177,7 +179,7 @@ def cpu_sample_setup(cfg, q_blocks: int):
 
     be = O.block_elements(cfg["block_size"])
     L, D, tk = cfg["L"], cfg["D"], cfg["topk"]
-    dt = torch.float32 if cfg.get("dtype") == "f32" else torch.bfloat16
+    dt = workload_dtype(cfg)
     whole = cfg["B"] * cfg["H"] * (L // be) <= 64
     slices = cfg["B"] * cfg["H"] if whole else 1
     q_blocks = L // be if whole else min(q_blocks, L // be)
@@ -205,7 +207,7 @@ def cpu_sample_setup(cfg, q_blocks: int):
     sample = (f"{what}: " + ("the whole workload" if whole else
               f"1 of {cfg['B'] * cfg['H']} (batch,head) slices, the first {q_blocks} of {L // be} query blocks "
               f"against all {L // be} key blocks") +
-              f" (topk {tk}, block {be}, D {D}, {'fp32' if dt == torch.float32 else 'bf16 inputs, fp32 fine math'}), "
+              f" (topk {tk}, block {be}, D {D}, {'fp32' if dt == torch.float32 else dtype_name(cfg) + ' inputs, fp32 fine math'}), "
               "forward+backward; throughput = the sample's useful FLOPs / its time")
     return step, flops, sample, ("reference" if ref is not None else "port")
 
@@ -237,7 +239,11 @@ def run_cpu(cfg, steps: int, warmup: int, q_blocks: int = 16):
 # --------------------------------------------------------------------------------------------
 def workload_dtype(cfg):
     import torch
-    return torch.float32 if cfg.get("dtype") == "f32" else torch.bfloat16
+    return {"f32": torch.float32, "f16": torch.float16}.get(cfg.get("dtype"), torch.bfloat16)
+
+
+def dtype_name(cfg):
+    return cfg.get("dtype", "bf16")
 
 
 def make_slices(cfg, first: int, count: int, device, rows=None, salt: int = 0):
@@ -555,7 +561,7 @@ def run_gpu(args, cfg, rank: int, world: int, local_rank: int):
         "higher_is_better": True,
         "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "f32" if cfg.get("dtype") == "f32" else "bf16",
+        "dtype": dtype_name(cfg),
         "data": "synthetic N(0,1), seeded per (batch,head) slice; random routes come from the operator's own Top-K",
         "collectives": ("all-gather K,V + reduce-scatter dK,dV over NCCL (sequence parallel)" if sp else "none"),
         "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], L, D], "block_elements": be,
@@ -724,7 +730,7 @@ def main():
                 else f"VSA fwd+bwd useful TFLOPS ({args.workload})",
                 "value": res["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "f32" if cfg.get("dtype") == "f32" else "bf16",
+                "scaling": "strong", "vs_baseline": None, "dtype": dtype_name(cfg),
                 "data": "synthetic N(0,1), seeded", "impl": "reference",
                 "config": {"workload": args.workload, "shape_BHLD": [cfg["B"], cfg["H"], cfg["L"], cfg["D"]],
                            "block_elements": be, "topk": cfg["topk"], "gate": cfg["gate"]},

@@ -49,6 +49,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     nvcc = _nvcc()
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
+        glob.glob(os.path.join(CSRC, "*.inl")) + \
         glob.glob(os.path.join(os.path.dirname(PKG), "include", "*.h"))
     objects = []
     jobs = []

@@ -127,7 +127,7 @@ int vsa_coarse_fwd(const void* q_mean, const void* k_mean, const void* v_mean, v
   VSA_REQUIRE(BH >= 0 && Qb >= 0 && Kb >= 1 && D >= 1, "coarse forward: bad extents");
   VSA_REQUIRE(q_mean && k_mean && v_mean && scores && probs && out_c, "coarse forward: null pointer");
   if (!scalar_forced() && coarse_umma_eligible(Qb, Kb, D, dtype))
-    return coarse_fwd_umma(q_mean, k_mean, v_mean, scores, probs, out_c, BH, Qb, Kb, D, scale, (cudaStream_t)stream);
+    return coarse_fwd_umma(q_mean, k_mean, v_mean, scores, probs, out_c, BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
   return coarse_fwd(q_mean, k_mean, v_mean, scores, probs, out_c, BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
 }
 
@@ -150,7 +150,7 @@ int vsa_coarse_bwd(const void* d_out_c, const void* out_c, const void* q_mean, c
                   dk_mean && dv_mean, "coarse backward: null pointer");
   if (!scalar_forced() && coarse_umma_eligible(Qb, Kb, D, dtype))
     return coarse_bwd_umma(d_out_c, out_c, q_mean, k_mean, v_mean, probs, dscores_ws, rowdot_ws, dq_mean, dk_mean,
-                           dv_mean, BH, Qb, Kb, D, scale, (cudaStream_t)stream);
+                           dv_mean, BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
   return coarse_bwd(d_out_c, out_c, q_mean, k_mean, v_mean, probs, dscores_ws, rowdot_ws, dq_mean, dk_mean, dv_mean,
                     BH, Qb, Kb, D, scale, dtype, (cudaStream_t)stream);
 }
@@ -170,17 +170,17 @@ static int sparse_fwd_dispatch(const void* q, const void* k, const void* v, cons
                                void* out_comb, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                                float scale, int dtype, cudaStream_t st) {
   int rc;
-  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype)) {
-    if (lse2 && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk)) {
-      rc = sparse_fwd_umma(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, st, out_c, gate, out_comb);
-      if (rc) return rc;
-      // exact recomputation of the (normally zero) tiles the fixed-shift softmax marked as out of range
-      return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, true, st, out_c, gate,
-                           out_comb);
-    }
-    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, false, st, out_c, gate,
+  if (lse2 && !scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk)) {
+    rc = sparse_fwd_umma(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, dtype, st, out_c, gate,
                          out_comb);
+    if (rc) return rc;
+    // exact recomputation of the (normally zero) tiles the fixed-shift softmax marked as out of range
+    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, dtype, true, st, out_c,
+                         gate, out_comb);
   }
+  if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
+    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, dtype, false, st, out_c,
+                         gate, out_comb);
   rc = sparse_fwd_scalar(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype, st);
   if (rc || !out_comb) return rc;
   return combine_fwd(out, out_c, gate, out_comb, BH, Lq, D, be, dtype, st);
@@ -230,10 +230,10 @@ int vsa_sparse_bwd_dq(const void* dout, const void* q, const void* k, const void
   VSA_REQUIRE(dout && q && k && v && out_s && lse2 && selected && kv_sizes && delta && dq, "sparse dQ: null pointer");
   if (!scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk))
     return sparse_dq_umma(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
-                          (cudaStream_t)stream);
+                          dtype, (cudaStream_t)stream);
   if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
     return sparse_dq_tc(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
-                        (cudaStream_t)stream);
+                        dtype, (cudaStream_t)stream);
   return sparse_dq_scalar(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, D, be, topk, scale,
                           dtype, (cudaStream_t)stream);
 }
@@ -248,10 +248,10 @@ int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const vo
               "sparse dK/dV: null pointer");
   if (!scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk))
     return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
-                            topk, scale, (cudaStream_t)stream);
+                            topk, scale, dtype, (cudaStream_t)stream);
   if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
     return sparse_dkdv_tc(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
-                          topk, scale, (cudaStream_t)stream);
+                          topk, scale, dtype, (cudaStream_t)stream);
   return sparse_dkdv_scalar(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, D, be,
                             topk, scale, dtype, (cudaStream_t)stream);
 }
@@ -270,7 +270,7 @@ int vsa_sparse_bwd_dq_fused(const void* dout, const void* q, const void* k, cons
               "sparse dQ (fused): null pointer");
   if (!scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk))
     return sparse_dq_umma(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
-                          (cudaStream_t)stream, dq_mean, q_sizes);
+                          dtype, (cudaStream_t)stream, dq_mean, q_sizes);
   rc = vsa_sparse_bwd_dq(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, D, be, topk, scale,
                          dtype, stream);
   if (rc) return rc;
@@ -288,7 +288,7 @@ int vsa_sparse_bwd_dkdv_fused(const void* dout, const void* q, const void* k, co
                   dk_mean && dv_mean, "sparse dK/dV (fused): null pointer");
   if (!scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk))
     return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
-                            topk, scale, (cudaStream_t)stream, dk_mean, dv_mean);
+                            topk, scale, dtype, (cudaStream_t)stream, dk_mean, dv_mean);
   rc = vsa_sparse_bwd_dkdv(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, D, be,
                            topk, scale, dtype, stream);
   if (rc) return rc;
@@ -339,9 +339,9 @@ int vsa_sparse_bwd_dkdv_ds(const void* dout, const void* q, const void* k, const
               "sparse dK/dV (dS stored): null pointer");
   VSA_REQUIRE((dk_mean == nullptr) == (dv_mean == nullptr), "sparse dK/dV (dS stored): give both pooled gradients or neither");
   if (!vsa_sparse_bwd_ds_supported(D, be, topk, dtype))
-    return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV (dS stored): needs bf16, head dim 128, block volume 64 or 256");
+    return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV (dS stored): needs bf16 or fp16, head dim 128, block volume 64 or 256");
   return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse_edges, kv_sizes, dk, dv, BH, Lq, Lkv, be,
-                          topk, scale, (cudaStream_t)stream, dk_mean, dv_mean, ds_ws);
+                          topk, scale, dtype, (cudaStream_t)stream, dk_mean, dv_mean, ds_ws);
 }
 
 int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int32_t* kv_sizes, const void* ds_ws,
@@ -352,21 +352,21 @@ int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int3
   VSA_REQUIRE(k && selected && kv_sizes && ds_ws && dq, "sparse dQ (from dS): null pointer");
   VSA_REQUIRE((dq_mean == nullptr) == (q_sizes == nullptr), "sparse dQ (from dS): give the pooled gradient and the query sizes, or neither");
   if (!vsa_sparse_bwd_ds_supported(D, be, topk, dtype))
-    return fail(VSA_ERR_UNSUPPORTED, "sparse dQ (from dS): needs bf16, head dim 128, block volume 64 or 256");
-  return sparse_dq_from_ds_umma(k, selected, kv_sizes, ds_ws, dq, BH, Lq, Lkv, be, topk, scale, (cudaStream_t)stream,
-                                dq_mean, q_sizes);
+    return fail(VSA_ERR_UNSUPPORTED, "sparse dQ (from dS): needs bf16 or fp16, head dim 128, block volume 64 or 256");
+  return sparse_dq_from_ds_umma(k, selected, kv_sizes, ds_ws, dq, BH, Lq, Lkv, be, topk, scale, dtype,
+                                (cudaStream_t)stream, dq_mean, q_sizes);
 }
 
 // ---- shard-major K/V (sequence-parallel mode) --------------------------------------------------------------
 // After an all-gather over W ranks the K/V shards lie one after another, [W][BH][Lkv/W][D].  These three entry
 // points read (and, for dK/dV, write) that layout in place: row of (slice, token) = ((token / shard) * BH + slice)
 // * shard + token % shard with shard = kv_shard tokens, so no re-layout copy follows the gather and the partial
-// dK/dV are ready for the reduce-scatter.  Tensor path only (bf16, D = 128, block volume 64 or 256).
+// dK/dV are ready for the reduce-scatter.  Tensor path only (bf16 or fp16, D = 128, block volume 64 or 256).
 static int check_sharded(int64_t Lkv, int64_t kv_shard, int D, int be, int topk, int dtype, const char* what) {
   VSA_REQUIRE(kv_shard > 0 && Lkv % kv_shard == 0 && kv_shard % be == 0,
               "%s: kv_shard must divide Lkv and be a multiple of block_elements=%d", what, be);
   if (scalar_forced() || mma_forced() || !sparse_umma_eligible(D, be, dtype, topk))
-    return fail(VSA_ERR_UNSUPPORTED, "%s: the shard-major layout needs bf16, head dim 128, block volume 64 or 256", what);
+    return fail(VSA_ERR_UNSUPPORTED, "%s: the shard-major layout needs bf16 or fp16, head dim 128, block volume 64 or 256", what);
   return VSA_OK;
 }
 
@@ -384,11 +384,11 @@ int vsa_sparse_fwd_combine_sharded(const void* q, const void* k_sh, const void* 
   VSA_REQUIRE((out == nullptr) == (out_c == nullptr), "sparse forward (sharded): give out_c and out together, or neither");
   if ((rc = check_sharded(Lkv, kv_shard, D, be, topk, dtype, "sparse forward (sharded)"))) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  rc = sparse_fwd_umma(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, st, out_c, gate, out,
-                       kv_shard);
-  if (rc) return rc;
-  return sparse_fwd_tc(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, true, st, out_c, gate,
+  rc = sparse_fwd_umma(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, st, out_c, gate,
                        out, kv_shard);
+  if (rc) return rc;
+  return sparse_fwd_tc(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, true, st, out_c,
+                       gate, out, kv_shard);
 }
 
 int vsa_sparse_bwd_dq_sharded(const void* dout, const void* q, const void* k_sh, const void* v_sh, const void* out_s,
@@ -403,7 +403,7 @@ int vsa_sparse_bwd_dq_sharded(const void* dout, const void* q, const void* k_sh,
   VSA_REQUIRE((dq_mean == nullptr) == (q_sizes == nullptr), "sparse dQ (sharded): give the pooled gradient and the query sizes, or neither");
   if ((rc = check_sharded(Lkv, kv_shard, D, be, topk, dtype, "sparse dQ (sharded)"))) return rc;
   return sparse_dq_umma(dout, q, k_sh, v_sh, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
-                        (cudaStream_t)stream, dq_mean, q_sizes, kv_shard);
+                        dtype, (cudaStream_t)stream, dq_mean, q_sizes, kv_shard);
 }
 
 int vsa_sparse_bwd_dkdv_sharded(const void* dout, const void* q, const void* k_sh, const void* v_sh, const float* lse2,
@@ -418,7 +418,7 @@ int vsa_sparse_bwd_dkdv_sharded(const void* dout, const void* q, const void* k_s
   VSA_REQUIRE((dk_mean == nullptr) == (dv_mean == nullptr), "sparse dK/dV (sharded): give both pooled gradients or neither");
   if ((rc = check_sharded(Lkv, kv_shard, D, be, topk, dtype, "sparse dK/dV (sharded)"))) return rc;
   return sparse_dkdv_umma(dout, q, k_sh, v_sh, lse2, delta, counts, offsets, inverse, kv_sizes, dk_sh, dv_sh, BH, Lq, Lkv, be,
-                          topk, scale, (cudaStream_t)stream, dk_mean, dv_mean, nullptr, kv_shard);
+                          topk, scale, dtype, (cudaStream_t)stream, dk_mean, dv_mean, nullptr, kv_shard);
 }
 
 int vsa_gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,

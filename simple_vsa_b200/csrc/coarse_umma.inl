@@ -36,7 +36,7 @@ enum GemmEpilogue { kEpiStore = 0, kEpiScores = 1, kEpiSoftmaxBwd = 2 };
 template <int A_MN, int B_MN, int EPI>
 __global__ void __launch_bounds__(192, 2)
 coarse_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        bf16* __restrict__ C, int M, int N, int K, float scale, const bf16* __restrict__ probs,
+                        elem_t* __restrict__ C, int M, int N, int K, float scale, const elem_t* __restrict__ probs,
                         const float* __restrict__ rowdot) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
@@ -93,7 +93,7 @@ coarse_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(128, 128, A_MN, B_MN);
+      constexpr uint32_t idesc = instr_desc(128, 128, A_MN, B_MN, kInFmt);
       constexpr uint32_t hi = desc_hi(1024);
       for (int kc = 0; kc < nk && ok; ++kc) {
         const int s = kc % kGemmStages;
@@ -138,25 +138,25 @@ coarse_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[j8 * 8 + i]);
           if (EPI == kEpiScores) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(__float2bfloat16_rn(v[i])) * scale;
+            for (int i = 0; i < 8; ++i) v[i] = Elem<elem_t>::to(Elem<elem_t>::from(v[i])) * scale;
           }
           if (EPI == kEpiSoftmaxBwd) {
             if (n + 8 <= N) {
               const uint4 praw = *reinterpret_cast<const uint4*>(probs + row_off + n);
-              const bf16* pe = reinterpret_cast<const bf16*>(&praw);
+              const elem_t* pe = reinterpret_cast<const elem_t*>(&praw);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(pe[i]) * (v[i] - rd) * scale;
+              for (int i = 0; i < 8; ++i) v[i] = Elem<elem_t>::to(pe[i]) * (v[i] - rd) * scale;
             } else {
-              for (int i = 0; i < 8 && n + i < N; ++i) v[i] = __bfloat162float(probs[row_off + n + i]) * (v[i] - rd) * scale;
+              for (int i = 0; i < 8 && n + i < N; ++i) v[i] = Elem<elem_t>::to(probs[row_off + n + i]) * (v[i] - rd) * scale;
             }
           }
           if (n + 8 <= N) {
             uint4 o;
-            o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
-            o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+            o.x = Elem<elem_t>::pack(v[0], v[1]); o.y = Elem<elem_t>::pack(v[2], v[3]);
+            o.z = Elem<elem_t>::pack(v[4], v[5]); o.w = Elem<elem_t>::pack(v[6], v[7]);
             *reinterpret_cast<uint4*>(C + row_off + n) = o;
           } else {
-            for (int i = 0; i < 8 && n + i < N; ++i) C[row_off + n + i] = __float2bfloat16_rn(v[i]);
+            for (int i = 0; i < 8 && n + i < N; ++i) C[row_off + n + i] = Elem<elem_t>::from(v[i]);
           }
         }
       }

@@ -37,12 +37,24 @@ template <> struct Elem<__nv_bfloat16> {
   __device__ __forceinline__ static float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   __device__ __forceinline__ static void st(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
   __device__ __forceinline__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  __device__ __forceinline__ static float to(__nv_bfloat16 x) { return __bfloat162float(x); }
+  __device__ __forceinline__ static __nv_bfloat16 from(float x) { return __float2bfloat16_rn(x); }
+  __device__ __forceinline__ static uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
 };
 
 template <> struct Elem<__half> {
   __device__ __forceinline__ static float ld(const __half* p) { return __half2float(*p); }
   __device__ __forceinline__ static void st(__half* p, float x) { *p = __float2half_rn(x); }
   __device__ __forceinline__ static float round(float x) { return __half2float(__float2half_rn(x)); }
+  __device__ __forceinline__ static float to(__half x) { return __half2float(x); }
+  __device__ __forceinline__ static __half from(float x) { return __float2half_rn(x); }
+  __device__ __forceinline__ static uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
 };
 
 // ---- warp helpers -----------------------------------------------------------------------
@@ -63,10 +75,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return Elem<__nv_bfloat16>::pack(lo, hi); }
 
 // Row of token `token` of slice `bh` in a K/V-shaped tensor.  Ordinary tensors are [BH][Lkv][D] (shard == Lkv).  A
 // sequence-parallel all-gather leaves the shards of the W ranks one after another, [W][BH][Lkv/W][D]; with
@@ -78,19 +87,20 @@ __device__ __forceinline__ long long kv_tensor_row(long long bh, long long BH, l
   return (r * BH + bh) * shard + (token - r * shard);
 }
 
-// Gated combine of eight bf16 values: out = out_s + out_c * gate (gate optional) in fp32, one rounding -- the
+// Gated combine of eight 16-bit values: out = out_s + out_c * gate (gate optional) in fp32, one rounding -- the
 // arithmetic of the stand-alone combine pass, so fusing it into a kernel's store changes no bit.
-__device__ __forceinline__ uint4 combine_bf16x8(const uint4& s_raw, const uint4& c_raw, const uint4& g_raw, bool has_gate) {
+template <typename T>
+__device__ __forceinline__ uint4 combine_x8(const uint4& s_raw, const uint4& c_raw, const uint4& g_raw, bool has_gate) {
   uint4 o_raw;
-  const __nv_bfloat16* se = reinterpret_cast<const __nv_bfloat16*>(&s_raw);
-  const __nv_bfloat16* ce = reinterpret_cast<const __nv_bfloat16*>(&c_raw);
-  const __nv_bfloat16* ge = reinterpret_cast<const __nv_bfloat16*>(&g_raw);
-  __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o_raw);
+  const T* se = reinterpret_cast<const T*>(&s_raw);
+  const T* ce = reinterpret_cast<const T*>(&c_raw);
+  const T* ge = reinterpret_cast<const T*>(&g_raw);
+  T* oe = reinterpret_cast<T*>(&o_raw);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    float cv = __bfloat162float(ce[i]);
-    if (has_gate) cv *= __bfloat162float(ge[i]);
-    oe[i] = __float2bfloat16_rn(__bfloat162float(se[i]) + cv);
+    float cv = Elem<T>::to(ce[i]);
+    if (has_gate) cv *= Elem<T>::to(ge[i]);
+    oe[i] = Elem<T>::from(Elem<T>::to(se[i]) + cv);
   }
   return o_raw;
 }
@@ -125,6 +135,20 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// the same product with fp16 operands
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  mma_bf16(d, a, b0, b1);
+}
+template <> __device__ __forceinline__ void mma_16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  mma_f16(d, a, b0, b1);
 }
 
 }  // namespace vsa

@@ -41,50 +41,52 @@ int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const voi
                        const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
                        int topk, float scale, int dtype, cudaStream_t st);
 
-// ---- tensor-core kernels, bf16, head dim 128, block volume 64 or 256 (sparse_mma.cu) ------
+// ---- tensor-core kernels, bf16 or fp16, head dim 128, block volume 64 or 256 (sparse_mma.cu) ------
 bool sparse_tc_eligible(int D, int be, int dtype);
 // redo_only: recompute only the 64-row query tiles whose first lse2 entry is NaN (the marker the
 // tcgen05 forward leaves on a tile whose fixed softmax shift ran out of range).
 // out_comb (optional): out_s + out_c[block] * gate is written there as well (gate may be null)
+// dtype: the forward also exists for fp16 (it is the exact recomputation behind the fp16 tcgen05 forward)
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                  bool redo_only, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
+                  int dtype, bool redo_only, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
                   void* out_comb = nullptr, int64_t kv_shard = 0);
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
                  const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
-                 int64_t Lkv, int be, int topk, float scale, cudaStream_t st);
+                 int64_t Lkv, int be, int topk, float scale, int dtype, cudaStream_t st);
 int sparse_dkdv_tc(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                    const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                    const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                   float scale, cudaStream_t st);
+                   float scale, int dtype, cudaStream_t st);
 
-// ---- tcgen05 / TMA kernels (sparse_umma.cu) -----------------------------------------------------
+// ---- tcgen05 / TMA kernels, bf16 or fp16 by `dtype` (sparse_umma.cu) -----------------------------------------------------
 bool sparse_umma_eligible(int D, int be, int dtype, int topk);
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                    cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr, void* out_comb = nullptr,
-                    int64_t kv_shard = 0);   // kv_shard: tokens per shard of a shard-major K/V buffer (0 = ordinary layout)
+                    int dtype, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
+                    void* out_comb = nullptr, int64_t kv_shard = 0);   // kv_shard: tokens per shard of a shard-major K/V buffer (0 = ordinary layout)
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
-                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
-                   const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr, int64_t kv_shard = 0);
+                   int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, int dtype,
+                   cudaStream_t st, const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr,
+                   int64_t kv_shard = 0);
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                     float scale, cudaStream_t st, const void* dk_mean = nullptr, const void* dv_mean = nullptr,
-                     void* ds_ws = nullptr, int64_t kv_shard = 0);
+                     float scale, int dtype, cudaStream_t st, const void* dk_mean = nullptr,
+                     const void* dv_mean = nullptr, void* ds_ws = nullptr, int64_t kv_shard = 0);
 // the backward that forms dS once: the key-owned pass (above, with ds_ws and packed edges) stores it, this
 // query-owned pass multiplies it by K
 int64_t sparse_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk);
 int sparse_dq_from_ds_umma(const void* k, const int32_t* selected, const int32_t* kv_sizes, const void* ds_ws, void* dq,
-                           int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
-                           const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr);
+                           int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, int dtype,
+                           cudaStream_t st, const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr);
 bool coarse_umma_eligible(int Qb, int Kb, int D, int dtype);
 int coarse_fwd_umma(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,
-                    int Qb, int Kb, int D, float scale, cudaStream_t st);
+                    int Qb, int Kb, int D, float scale, int dtype, cudaStream_t st);
 int coarse_bwd_umma(const void* d_out_c, const void* out_c, const void* qc, const void* kc, const void* vc,
                     const void* probs, void* ds, float* rowdot, void* dqc, void* dkc, void* dvc, int64_t BH, int Qb,
-                    int Kb, int D, float scale, cudaStream_t st);
+                    int Kb, int D, float scale, int dtype, cudaStream_t st);
 int umma_selftest(const void* a, const void* b, float* out, int mode, cudaStream_t st);
 int wait_timeout_selftest(unsigned long long limit_ns, int* gave_up, cudaStream_t st);
 int device_status_fetch_and_clear(int* status);

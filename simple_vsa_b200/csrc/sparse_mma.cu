@@ -18,7 +18,6 @@
 namespace vsa {
 namespace {
 
-using bf16 = __nv_bfloat16;
 constexpr int kD = 128;
 constexpr int kTile = 64;
 constexpr int kTileBytes = kTile * kD * 2;   // 16384
@@ -29,7 +28,8 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
 }
 
 // Stage one 64x128 bf16 tile; rows >= valid_rows are zero-filled instead of read.
-__device__ __forceinline__ void stage_tile(uint32_t smem_base, const bf16* __restrict__ g, int valid_rows, int tid) {
+template <typename T>
+__device__ __forceinline__ void stage_tile(uint32_t smem_base, const T* __restrict__ g, int valid_rows, int tid) {
 #pragma unroll
   for (int i = 0; i < 1024 / kThreads; ++i) {
     const int c = tid + i * kThreads;
@@ -72,17 +72,18 @@ __device__ __forceinline__ float quad_sum(float x) {
 // rows of a swizzled tile, then copy those rows to global memory with 16-byte stores.
 // With `comb` the gated combine with the pooled branch (pooled_row = the query block's pooled output row, gate_g
 // optional) is written beside it.
+template <typename T>
 __device__ __forceinline__ void store_warp_rows(uint8_t* tile, uint32_t tile_u32, const float (&acc)[16][4], float mul0,
-                                                float mul1, bf16* __restrict__ g, int warp, int lane,
-                                                const bf16* __restrict__ pooled_row = nullptr,
-                                                const bf16* __restrict__ gate_g = nullptr,
-                                                bf16* __restrict__ comb = nullptr) {
+                                                float mul1, T* __restrict__ g, int warp, int lane,
+                                                const T* __restrict__ pooled_row = nullptr,
+                                                const T* __restrict__ gate_g = nullptr,
+                                                T* __restrict__ comb = nullptr) {
   const int gq = lane >> 2, t = lane & 3;
   const int r0 = warp * 16 + gq, r1 = r0 + 8;
 #pragma unroll
   for (int nt = 0; nt < 16; ++nt) {
-    *reinterpret_cast<uint32_t*>(tile + tile_off(r0, nt) + 4 * t) = pack_bf16(acc[nt][0] * mul0, acc[nt][1] * mul0);
-    *reinterpret_cast<uint32_t*>(tile + tile_off(r1, nt) + 4 * t) = pack_bf16(acc[nt][2] * mul1, acc[nt][3] * mul1);
+    *reinterpret_cast<uint32_t*>(tile + tile_off(r0, nt) + 4 * t) = Elem<T>::pack(acc[nt][0] * mul0, acc[nt][1] * mul0);
+    *reinterpret_cast<uint32_t*>(tile + tile_off(r1, nt) + 4 * t) = Elem<T>::pack(acc[nt][2] * mul1, acc[nt][3] * mul1);
   }
   __syncwarp();
 #pragma unroll
@@ -95,7 +96,7 @@ __device__ __forceinline__ void store_warp_rows(uint8_t* tile, uint32_t tile_u32
       const uint4 cv = *reinterpret_cast<const uint4*>(pooled_row + ch * 8);
       uint4 gv = make_uint4(0, 0, 0, 0);
       if (gate_g != nullptr) gv = *reinterpret_cast<const uint4*>(gate_g + row * kD + ch * 8);
-      *reinterpret_cast<uint4*>(comb + row * kD + ch * 8) = combine_bf16x8(val, cv, gv, gate_g != nullptr);
+      *reinterpret_cast<uint4*>(comb + row * kD + ch * 8) = combine_x8<T>(val, cv, gv, gate_g != nullptr);
     }
   }
   (void)tile_u32;
@@ -104,12 +105,12 @@ __device__ __forceinline__ void store_warp_rows(uint8_t* tile, uint32_t tile_u32
 // ------------------------------------------------------------------------------------------
 // Forward.  grid = (Lq/64, BH); one CTA = 64 query rows (4 warps x 16 rows).
 // ------------------------------------------------------------------------------------------
-template <int SUB>
+template <typename T, int SUB>
 __global__ void __launch_bounds__(kThreads, 2)
-sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+sparse_fwd_mma_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
-                      bf16* __restrict__ out, float* __restrict__ lse2, const bf16* __restrict__ out_c,
-                      const bf16* __restrict__ gate, bf16* __restrict__ out_comb, long long Lq, long long Lkv,
+                      T* __restrict__ out, float* __restrict__ lse2, const T* __restrict__ out_c,
+                      const T* __restrict__ gate, T* __restrict__ out_comb, long long Lq, long long Lkv,
                       long long kv_shard, int topk, float scale, int redo_only) {
   extern __shared__ __align__(128) uint8_t smem[];
   if (redo_only) {   // only tiles the tcgen05 forward marked with a NaN statistic are recomputed
@@ -191,8 +192,8 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
       for (int np = 0; np < 4; ++np) {
         uint32_t b[4];
         load_b_kcontig(cK, np * 16, ks, lane, b);
-        mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
-        mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+        mma_16816<T>(s[2 * np], qf[ks], b[0], b[1]);
+        mma_16816<T>(s[2 * np + 1], qf[ks], b[2], b[3]);
       }
     }
     float tmax[2] = {-INFINITY, -INFINITY};
@@ -233,16 +234,16 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       uint32_t pa[4];
-      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      pa[0] = Elem<T>::pack(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = Elem<T>::pack(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = Elem<T>::pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = Elem<T>::pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
       for (int dp = 0; dp < 8; ++dp) {
         uint32_t b[4];
         load_b_ncontig(cV, kk * 16, dp, lane, b);
-        mma_bf16(o[2 * dp], pa, b[0], b[1]);
-        mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
+        mma_16816<T>(o[2 * dp], pa, b[0], b[1]);
+        mma_16816<T>(o[2 * dp + 1], pa, b[2], b[3]);
       }
     }
     __syncthreads();
@@ -258,7 +259,7 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
     inv[r] = 1.f / row_sum[r];
   }
   const long long row0 = bh * Lq + (long long)qtile * kTile;
-  bf16* og = out + row0 * kD;
+  T* og = out + row0 * kD;
   if (out_comb != nullptr)
     store_warp_rows(smem, sQ, o, inv[0], inv[1], og, warp, lane, out_c + (bh * Qb + qb) * (long long)kD,
                     gate != nullptr ? gate + row0 * kD : nullptr, out_comb + row0 * kD);
@@ -274,12 +275,12 @@ sparse_fwd_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, co
 // ------------------------------------------------------------------------------------------
 // dQ (query-owned).  grid = (Lq/64, BH).  Also writes delta = rowsum(out_s * dout).
 // ------------------------------------------------------------------------------------------
-template <int SUB>
+template <typename T, int SUB>
 __global__ void __launch_bounds__(kThreads, 2)
-sparse_dq_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, const bf16* __restrict__ k,
-                     const bf16* __restrict__ v, const bf16* __restrict__ out_s, const float* __restrict__ lse2,
+sparse_dq_mma_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __restrict__ k,
+                     const T* __restrict__ v, const T* __restrict__ out_s, const float* __restrict__ lse2,
                      const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
-                     float* __restrict__ delta, bf16* __restrict__ dq, long long Lq, long long Lkv, int topk,
+                     float* __restrict__ delta, T* __restrict__ dq, long long Lq, long long Lkv, int topk,
                      float scale) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem);
@@ -294,8 +295,8 @@ sparse_dq_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, 
   const int Qb = (int)(Lq / (kTile * SUB));
   const int qb = qtile / SUB;
   const int32_t* sel = selected + (bh * Qb + qb) * (long long)topk;
-  const bf16* kbase = k + bh * Lkv * kD;
-  const bf16* vbase = v + bh * Lkv * kD;
+  const T* kbase = k + bh * Lkv * kD;
+  const T* vbase = v + bh * Lkv * kD;
   const long long qrow0 = bh * Lq + (long long)qtile * kTile;
   const int n_iter = topk * SUB;
   const float c = scale * kLog2e;
@@ -334,14 +335,10 @@ sparse_dq_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint4 a = po[i], b = pd[i];
-      const __nv_bfloat162* ea = reinterpret_cast<const __nv_bfloat162*>(&a);
-      const __nv_bfloat162* eb = reinterpret_cast<const __nv_bfloat162*>(&b);
+      const T* ea = reinterpret_cast<const T*>(&a);
+      const T* eb = reinterpret_cast<const T*>(&b);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 fa = __bfloat1622float2(ea[j]), fb = __bfloat1622float2(eb[j]);
-        acc = fmaf(fa.x, fb.x, acc);
-        acc = fmaf(fa.y, fb.y, acc);
-      }
+      for (int j = 0; j < 8; ++j) acc = fmaf(Elem<T>::to(ea[j]), Elem<T>::to(eb[j]), acc);
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     if (half == 0) {
@@ -391,11 +388,11 @@ sparse_dq_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, 
       for (int np = 0; np < 4; ++np) {
         uint32_t b[4];
         load_b_kcontig(cK, np * 16, ks, lane, b);
-        mma_bf16(s[2 * np], aq, b[0], b[1]);
-        mma_bf16(s[2 * np + 1], aq, b[2], b[3]);
+        mma_16816<T>(s[2 * np], aq, b[0], b[1]);
+        mma_16816<T>(s[2 * np + 1], aq, b[2], b[3]);
         load_b_kcontig(cV, np * 16, ks, lane, b);
-        mma_bf16(dp[2 * np], ad, b[0], b[1]);
-        mma_bf16(dp[2 * np + 1], ad, b[2], b[3]);
+        mma_16816<T>(dp[2 * np], ad, b[0], b[1]);
+        mma_16816<T>(dp[2 * np + 1], ad, b[2], b[3]);
       }
     }
 #pragma unroll
@@ -410,16 +407,16 @@ sparse_dq_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, 
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       uint32_t da[4];
-      da[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      da[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      da[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      da[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      da[0] = Elem<T>::pack(s[2 * kk][0], s[2 * kk][1]);
+      da[1] = Elem<T>::pack(s[2 * kk][2], s[2 * kk][3]);
+      da[2] = Elem<T>::pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      da[3] = Elem<T>::pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
       for (int d2 = 0; d2 < 8; ++d2) {
         uint32_t b[4];
         load_b_ncontig(cK, kk * 16, d2, lane, b);
-        mma_bf16(acc_dq[2 * d2], da, b[0], b[1]);
-        mma_bf16(acc_dq[2 * d2 + 1], da, b[2], b[3]);
+        mma_16816<T>(acc_dq[2 * d2], da, b[0], b[1]);
+        mma_16816<T>(acc_dq[2 * d2 + 1], da, b[2], b[3]);
       }
     }
     __syncthreads();
@@ -434,13 +431,13 @@ sparse_dq_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, 
 // dK/dV (key-owned).  grid = (Lkv/64, BH); one CTA = one 64-row key tile, looping over the
 // query blocks that selected its logical block (CSR in-edges), each SUB query tiles long.
 // ------------------------------------------------------------------------------------------
-template <int SUB>
+template <typename T, int SUB>
 __global__ void __launch_bounds__(kThreads, 2)
-sparse_dkdv_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q, const bf16* __restrict__ k,
-                       const bf16* __restrict__ v, const float* __restrict__ lse2, const float* __restrict__ delta,
+sparse_dkdv_mma_kernel(const T* __restrict__ dout, const T* __restrict__ q, const T* __restrict__ k,
+                       const T* __restrict__ v, const float* __restrict__ lse2, const float* __restrict__ delta,
                        const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
                        const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
-                       bf16* __restrict__ dk, bf16* __restrict__ dv, long long Lq, long long Lkv, int topk,
+                       T* __restrict__ dk, T* __restrict__ dv, long long Lq, long long Lkv, int topk,
                        float scale) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sK = smem_u32(smem);
@@ -464,8 +461,8 @@ sparse_dkdv_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q
   const int32_t* inv = inverse + bh * (long long)Qb * topk + offsets[bh * Kb + kvb];
   const int n_iter = cnt * SUB;
   const float c = scale * kLog2e;
-  const bf16* qbase = q + bh * Lq * kD;
-  const bf16* dobase = dout + bh * Lq * kD;
+  const T* qbase = q + bh * Lq * kD;
+  const T* dobase = dout + bh * Lq * kD;
 
   auto stage_q = [&](int it, int stg) {
     const long long row0 = (long long)inv[it / SUB] * (kTile * SUB) + (it % SUB) * kTile;
@@ -515,11 +512,11 @@ sparse_dkdv_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q
         for (int np = 0; np < 2; ++np) {
           uint32_t b[4];
           load_b_kcontig(cQ, h * 32 + np * 16, ks, lane, b);
-          mma_bf16(s[2 * np], ak, b[0], b[1]);
-          mma_bf16(s[2 * np + 1], ak, b[2], b[3]);
+          mma_16816<T>(s[2 * np], ak, b[0], b[1]);
+          mma_16816<T>(s[2 * np + 1], ak, b[2], b[3]);
           load_b_kcontig(cdO, h * 32 + np * 16, ks, lane, b);
-          mma_bf16(dp[2 * np], av, b[0], b[1]);
-          mma_bf16(dp[2 * np + 1], av, b[2], b[3]);
+          mma_16816<T>(dp[2 * np], av, b[0], b[1]);
+          mma_16816<T>(dp[2 * np + 1], av, b[2], b[3]);
         }
       }
       // transposed tile: rows are key tokens, columns are query rows of this half
@@ -537,23 +534,23 @@ sparse_dkdv_mma_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ q
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk) {
         uint32_t pa[4], da[4];
-        pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-        da[0] = pack_bf16(dp[2 * kk][0], dp[2 * kk][1]);
-        da[1] = pack_bf16(dp[2 * kk][2], dp[2 * kk][3]);
-        da[2] = pack_bf16(dp[2 * kk + 1][0], dp[2 * kk + 1][1]);
-        da[3] = pack_bf16(dp[2 * kk + 1][2], dp[2 * kk + 1][3]);
+        pa[0] = Elem<T>::pack(s[2 * kk][0], s[2 * kk][1]);
+        pa[1] = Elem<T>::pack(s[2 * kk][2], s[2 * kk][3]);
+        pa[2] = Elem<T>::pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[3] = Elem<T>::pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        da[0] = Elem<T>::pack(dp[2 * kk][0], dp[2 * kk][1]);
+        da[1] = Elem<T>::pack(dp[2 * kk][2], dp[2 * kk][3]);
+        da[2] = Elem<T>::pack(dp[2 * kk + 1][0], dp[2 * kk + 1][1]);
+        da[3] = Elem<T>::pack(dp[2 * kk + 1][2], dp[2 * kk + 1][3]);
 #pragma unroll
         for (int d2 = 0; d2 < 8; ++d2) {
           uint32_t b[4];
           load_b_ncontig(cdO, h * 32 + kk * 16, d2, lane, b);
-          mma_bf16(acc_dv[2 * d2], pa, b[0], b[1]);
-          mma_bf16(acc_dv[2 * d2 + 1], pa, b[2], b[3]);
+          mma_16816<T>(acc_dv[2 * d2], pa, b[0], b[1]);
+          mma_16816<T>(acc_dv[2 * d2 + 1], pa, b[2], b[3]);
           load_b_ncontig(cQ, h * 32 + kk * 16, d2, lane, b);
-          mma_bf16(acc_dk[2 * d2], da, b[0], b[1]);
-          mma_bf16(acc_dk[2 * d2 + 1], da, b[2], b[3]);
+          mma_16816<T>(acc_dk[2 * d2], da, b[0], b[1]);
+          mma_16816<T>(acc_dk[2 * d2 + 1], da, b[2], b[3]);
         }
       }
     }
@@ -579,71 +576,91 @@ int set_smem(K kernel, int bytes, const char* what) {
 
 }  // namespace
 
-bool sparse_tc_eligible(int D, int be, int dtype) { return dtype == VSA_BF16 && D == 128 && (be == 64 || be == 256); }
+bool sparse_tc_eligible(int D, int be, int dtype) { return (dtype == VSA_BF16 || dtype == VSA_F16) && D == 128 && (be == 64 || be == 256); }
+
+template <typename T>
+static int launch_fwd(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
+                      void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
+                      bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard) {
+  dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
+  auto launch = [&](auto kern) -> int {
+    const int rc = set_smem(kern, kFwdSmem, "sparse forward");
+    if (rc) return rc;
+    kern<<<grid, kThreads, kFwdSmem, st>>>((const T*)q, (const T*)k, (const T*)v, selected, kv_sizes, (T*)out, lse2,
+                                           (const T*)out_c, (const T*)gate, (T*)out_comb, Lq, Lkv, kv_shard, topk, scale,
+                                           redo_only ? 1 : 0);
+    return check_launch("sparse_fwd_mma_kernel");
+  };
+  return be == 64 ? launch(sparse_fwd_mma_kernel<T, 1>) : launch(sparse_fwd_mma_kernel<T, 4>);
+}
+
+template <typename T>
+static int launch_dq(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
+                     const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
+                     int64_t Lkv, int be, int topk, float scale, cudaStream_t st) {
+  dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
+  auto launch = [&](auto kern) -> int {
+    const int rc = set_smem(kern, kDqSmem, "sparse dQ");
+    if (rc) return rc;
+    kern<<<grid, kThreads, kDqSmem, st>>>((const T*)dout, (const T*)q, (const T*)k, (const T*)v, (const T*)out_s, lse2,
+                                          selected, kv_sizes, delta, (T*)dq, Lq, Lkv, topk, scale);
+    return check_launch("sparse_dq_mma_kernel");
+  };
+  return be == 64 ? launch(sparse_dq_mma_kernel<T, 1>) : launch(sparse_dq_mma_kernel<T, 4>);
+}
+
+template <typename T>
+static int launch_dkdv(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                       const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                       const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
+                       float scale, cudaStream_t st) {
+  dim3 grid((unsigned)(Lkv / kTile), (unsigned)BH);
+  auto launch = [&](auto kern) -> int {
+    const int rc = set_smem(kern, kDkdvSmem, "sparse dK/dV");
+    if (rc) return rc;
+    kern<<<grid, kThreads, kDkdvSmem, st>>>((const T*)dout, (const T*)q, (const T*)k, (const T*)v, lse2, delta, counts,
+                                            offsets, inverse, kv_sizes, (T*)dk, (T*)dv, Lq, Lkv, topk, scale);
+    return check_launch("sparse_dkdv_mma_kernel");
+  };
+  return be == 64 ? launch(sparse_dkdv_mma_kernel<T, 1>) : launch(sparse_dkdv_mma_kernel<T, 4>);
+}
 
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                  bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard) {
+                  int dtype, bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb,
+                  int64_t kv_shard) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (kv_shard <= 0) kv_shard = Lkv;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
-  dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
-  int rc;
-  if (be == 64) {
-    if ((rc = set_smem(sparse_fwd_mma_kernel<1>, kFwdSmem, "sparse forward"))) return rc;
-    sparse_fwd_mma_kernel<1><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
-                                                               kv_sizes, (bf16*)out, lse2, (const bf16*)out_c, (const bf16*)gate,
-                                                               (bf16*)out_comb, Lq, Lkv, kv_shard, topk, scale, redo_only ? 1 : 0);
-  } else {
-    if ((rc = set_smem(sparse_fwd_mma_kernel<4>, kFwdSmem, "sparse forward"))) return rc;
-    sparse_fwd_mma_kernel<4><<<grid, kThreads, kFwdSmem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, selected,
-                                                               kv_sizes, (bf16*)out, lse2, (const bf16*)out_c, (const bf16*)gate,
-                                                               (bf16*)out_comb, Lq, Lkv, kv_shard, topk, scale, redo_only ? 1 : 0);
-  }
-  return check_launch("sparse_fwd_mma_kernel");
+  if (dtype == VSA_F16)
+    return launch_fwd<__half>(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, redo_only, st, out_c,
+                              gate, out_comb, kv_shard);
+  return launch_fwd<__nv_bfloat16>(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, redo_only, st,
+                                   out_c, gate, out_comb, kv_shard);
 }
 
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
                  const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
-                 int64_t Lkv, int be, int topk, float scale, cudaStream_t st) {
+                 int64_t Lkv, int be, int topk, float scale, int dtype, cudaStream_t st) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dQ: batch*heads %lld exceeds 65535", (long long)BH);
-  dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
-  int rc;
-  if (be == 64) {
-    if ((rc = set_smem(sparse_dq_mma_kernel<1>, kDqSmem, "sparse dQ"))) return rc;
-    sparse_dq_mma_kernel<1><<<grid, kThreads, kDqSmem, st>>>((const bf16*)dout, (const bf16*)q, (const bf16*)k,
-                                                             (const bf16*)v, (const bf16*)out_s, lse2, selected, kv_sizes,
-                                                             delta, (bf16*)dq, Lq, Lkv, topk, scale);
-  } else {
-    if ((rc = set_smem(sparse_dq_mma_kernel<4>, kDqSmem, "sparse dQ"))) return rc;
-    sparse_dq_mma_kernel<4><<<grid, kThreads, kDqSmem, st>>>((const bf16*)dout, (const bf16*)q, (const bf16*)k,
-                                                             (const bf16*)v, (const bf16*)out_s, lse2, selected, kv_sizes,
-                                                             delta, (bf16*)dq, Lq, Lkv, topk, scale);
-  }
-  return check_launch("sparse_dq_mma_kernel");
+  if (dtype == VSA_F16)
+    return launch_dq<__half>(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale, st);
+  return launch_dq<__nv_bfloat16>(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
+                                  st);
 }
 
 int sparse_dkdv_tc(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                    const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                    const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                   float scale, cudaStream_t st) {
+                   float scale, int dtype, cudaStream_t st) {
   if (BH == 0 || Lkv == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: batch*heads %lld exceeds 65535", (long long)BH);
-  dim3 grid((unsigned)(Lkv / kTile), (unsigned)BH);
-  int rc;
-  if (be == 64) {
-    if ((rc = set_smem(sparse_dkdv_mma_kernel<1>, kDkdvSmem, "sparse dK/dV"))) return rc;
-    sparse_dkdv_mma_kernel<1><<<grid, kThreads, kDkdvSmem, st>>>((const bf16*)dout, (const bf16*)q, (const bf16*)k,
-                                                                 (const bf16*)v, lse2, delta, counts, offsets, inverse,
-                                                                 kv_sizes, (bf16*)dk, (bf16*)dv, Lq, Lkv, topk, scale);
-  } else {
-    if ((rc = set_smem(sparse_dkdv_mma_kernel<4>, kDkdvSmem, "sparse dK/dV"))) return rc;
-    sparse_dkdv_mma_kernel<4><<<grid, kThreads, kDkdvSmem, st>>>((const bf16*)dout, (const bf16*)q, (const bf16*)k,
-                                                                 (const bf16*)v, lse2, delta, counts, offsets, inverse,
-                                                                 kv_sizes, (bf16*)dk, (bf16*)dv, Lq, Lkv, topk, scale);
-  }
-  return check_launch("sparse_dkdv_mma_kernel");
+  if (dtype == VSA_F16)
+    return launch_dkdv<__half>(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
+                               topk, scale, st);
+  return launch_dkdv<__nv_bfloat16>(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv,
+                                    be, topk, scale, st);
 }
 
 }  // namespace vsa

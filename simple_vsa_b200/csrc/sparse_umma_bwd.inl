@@ -60,9 +60,9 @@ template <int SUB>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                      const bf16* __restrict__ dout, const bf16* __restrict__ out_s, const float* __restrict__ lse2,
+                      const elem_t* __restrict__ dout, const elem_t* __restrict__ out_s, const float* __restrict__ lse2,
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
-                      float* __restrict__ delta, bf16* __restrict__ dq, const bf16* __restrict__ mean_grad,
+                      float* __restrict__ delta, elem_t* __restrict__ dq, const elem_t* __restrict__ mean_grad,
                       const int32_t* __restrict__ q_sizes, long long Lq, long long Lkv, long long kv_shard, int topk,
                       float scale) {
   extern __shared__ uint8_t smem_raw[];
@@ -126,14 +126,10 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
     for (int i = 0; i < kDims / 8; ++i) {
       const uint4 a = po[i], b = pd[i];
-      const __nv_bfloat162* ea = reinterpret_cast<const __nv_bfloat162*>(&a);
-      const __nv_bfloat162* eb = reinterpret_cast<const __nv_bfloat162*>(&b);
+      const elem_t* ea = reinterpret_cast<const elem_t*>(&a);
+      const elem_t* eb = reinterpret_cast<const elem_t*>(&b);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 fa = __bfloat1622float2(ea[j]), fb = __bfloat1622float2(eb[j]);
-        acc = fmaf(fa.x, fb.x, acc);
-        acc = fmaf(fa.y, fb.y, acc);
-      }
+      for (int j = 0; j < 8; ++j) acc = fmaf(Elem<elem_t>::to(ea[j]), Elem<elem_t>::to(eb[j]), acc);
     }
 #pragma unroll
     for (int o = 1; o < kPer; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -299,9 +295,9 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
       for (int j4 = 0; j4 < kBwCols / 4; ++j4) {
         const float4 d4 = *reinterpret_cast<const float4*>(s_delta + c0 + 4 * j4);
-        packed[2 * j4] = pack_bf16(pf[4 * j4 + 0] * (__uint_as_float(dv[4 * j4 + 0]) - d4.x),
+        packed[2 * j4] = Elem<elem_t>::pack(pf[4 * j4 + 0] * (__uint_as_float(dv[4 * j4 + 0]) - d4.x),
                                    pf[4 * j4 + 1] * (__uint_as_float(dv[4 * j4 + 1]) - d4.y));
-        packed[2 * j4 + 1] = pack_bf16(pf[4 * j4 + 2] * (__uint_as_float(dv[4 * j4 + 2]) - d4.z),
+        packed[2 * j4 + 1] = Elem<elem_t>::pack(pf[4 * j4 + 2] * (__uint_as_float(dv[4 * j4 + 2]) - d4.z),
                                        pf[4 * j4 + 3] * (__uint_as_float(dv[4 * j4 + 3]) - d4.w));
       }
       if (!live) {   // a padding key row: its scores come from whatever sits in K and V there
@@ -323,14 +319,14 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (ok && n_pairs > 0) ok = VSA_WARP_WAIT(bar(DQ_ACC_FULL), 0);
     if (!ok && lane == 0) report_timeout(15);
     tc_fence_after();
-    bf16* stage = reinterpret_cast<bf16*>(sm + DqSmem::k);      // [64 query rows][128 dims]; every MMA is done
+    elem_t* stage = reinterpret_cast<elem_t*>(sm + DqSmem::k);      // [64 query rows][128 dims]; every MMA is done
     // block-mean backward folded in (optional): query row r of the block also receives dmean[block] / max(size, 1)
     // while r < size (vsa/fused_common.py:62-103 of the reference); here lane t is the head dim, a column a row
     float gm = 0.f;
     int rows_live = 0;
     if (mean_grad != nullptr) {
       const int size = q_sizes[qb];
-      gm = __bfloat162float(mean_grad[(bh * Qb + qb) * (long long)kD + t]) / (float)(size > 1 ? size : 1);
+      gm = Elem<elem_t>::to(mean_grad[(bh * Qb + qb) * (long long)kD + t]) / (float)(size > 1 ? size : 1);
       rows_live = size - (qtile % SUB) * kTile;
     }
     if (ok && n_pairs > 0) {
@@ -339,12 +335,12 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < kBwCols; ++j)
-        stage[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]) + ((c0 + j) < rows_live ? gm : 0.f));
+        stage[(c0 + j) * kD + t] = Elem<elem_t>::from(__uint_as_float(av[j]) + ((c0 + j) < rows_live ? gm : 0.f));
     } else {
-      for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = __float2bfloat16_rn((c0 + j) < rows_live ? gm : 0.f);
+      for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = Elem<elem_t>::from((c0 + j) < rows_live ? gm : 0.f);
     }
     named_barrier(1, kBwEwThreads);
-    bf16* og = dq + qrow0 * kD;
+    elem_t* og = dq + qrow0 * kD;
 #pragma unroll
     for (int i = 0; i < 1024 / kBwEwThreads; ++i) {
       const int cidx = st + kBwEwThreads * i;
@@ -399,8 +395,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const float* __restrict__ lse2, const float* __restrict__ delta,
                         const int32_t* __restrict__ counts, const int32_t* __restrict__ offsets,
                         const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
-                        bf16* __restrict__ dk, bf16* __restrict__ dv, const bf16* __restrict__ mean_grad_k,
-                        const bf16* __restrict__ mean_grad_v, bf16* __restrict__ ds_ws, long long Lq, long long Lkv,
+                        elem_t* __restrict__ dk, elem_t* __restrict__ dv, const elem_t* __restrict__ mean_grad_k,
+                        const elem_t* __restrict__ mean_grad_v, elem_t* __restrict__ ds_ws, long long Lq, long long Lkv,
                         long long kv_shard, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
@@ -431,12 +427,12 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     for (int i = tid; i < 1024; i += (int)blockDim.x) {
       uint4 ok4 = make_uint4(0, 0, 0, 0), ov4 = make_uint4(0, 0, 0, 0);
       if (mean_grad_k != nullptr && (i >> 4) < valid) {     // 16 chunks of eight dims per row
-        bf16* ek = reinterpret_cast<bf16*>(&ok4);
-        bf16* ev = reinterpret_cast<bf16*>(&ov4);
+        elem_t* ek = reinterpret_cast<elem_t*>(&ok4);
+        elem_t* ev = reinterpret_cast<elem_t*>(&ov4);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          ek[e] = __float2bfloat16_rn(__bfloat162float(mean_grad_k[mean_off + (i & 15) * 8 + e]) * mean_inv);
-          ev[e] = __float2bfloat16_rn(__bfloat162float(mean_grad_v[mean_off + (i & 15) * 8 + e]) * mean_inv);
+          ek[e] = Elem<elem_t>::from(Elem<elem_t>::to(mean_grad_k[mean_off + (i & 15) * 8 + e]) * mean_inv);
+          ev[e] = Elem<elem_t>::from(Elem<elem_t>::to(mean_grad_v[mean_off + (i & 15) * 8 + e]) * mean_inv);
         }
       }
       gk[i] = ok4;
@@ -630,8 +626,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
       for (int ch = 0; ch < kBwCols / 8; ++ch)
         *reinterpret_cast<uint4*>(prow + ((((kBwCols / 8) * cg + ch) ^ (t & 7)) << 4)) =
-            make_uint4(pack_bf16(pf[8 * ch], pf[8 * ch + 1]), pack_bf16(pf[8 * ch + 2], pf[8 * ch + 3]),
-                       pack_bf16(pf[8 * ch + 4], pf[8 * ch + 5]), pack_bf16(pf[8 * ch + 6], pf[8 * ch + 7]));
+            make_uint4(Elem<elem_t>::pack(pf[8 * ch], pf[8 * ch + 1]), Elem<elem_t>::pack(pf[8 * ch + 2], pf[8 * ch + 3]),
+                       Elem<elem_t>::pack(pf[8 * ch + 4], pf[8 * ch + 5]), Elem<elem_t>::pack(pf[8 * ch + 6], pf[8 * ch + 7]));
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(DK_P_FULL));
@@ -649,14 +645,14 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (!ragged) {
 #pragma unroll
         for (int j2 = 0; j2 < kBwCols / 2; ++j2)
-          pg[j2] = pack_bf16(pf[2 * j2] * (__uint_as_float(dvv[2 * j2]) - dl),
+          pg[j2] = Elem<elem_t>::pack(pf[2 * j2] * (__uint_as_float(dvv[2 * j2]) - dl),
                              pf[2 * j2 + 1] * (__uint_as_float(dvv[2 * j2 + 1]) - dl));
       } else {   // dP of a padding column comes from whatever sits in V there
 #pragma unroll
         for (int j2 = 0; j2 < kBwCols / 2; ++j2) {
           const float g0 = (c0 + 2 * j2) < valid ? pf[2 * j2] * (__uint_as_float(dvv[2 * j2]) - dl) : 0.f;
           const float g1 = (c0 + 2 * j2 + 1) < valid ? pf[2 * j2 + 1] * (__uint_as_float(dvv[2 * j2 + 1]) - dl) : 0.f;
-          pg[j2] = pack_bf16(g0, g1);
+          pg[j2] = Elem<elem_t>::pack(g0, g1);
         }
       }
       if (DS && dst >= 0) {   // chunk-major tile: chunk c of row r at c * 1024 + r * 16 bytes
@@ -679,8 +675,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (ok) ok = VSA_WARP_WAIT(bar(DK_ACC_FULL), 0);
     if (!ok && lane == 0) report_timeout(25);
     tc_fence_after();
-    bf16* stage_k = reinterpret_cast<bf16*>(sm + DkSmem::q);          // [64 key rows][128 dims] each; all MMAs done
-    bf16* stage_v = stage_k + kTile * kD;
+    elem_t* stage_k = reinterpret_cast<elem_t*>(sm + DkSmem::q);          // [64 key rows][128 dims] each; all MMAs done
+    elem_t* stage_v = stage_k + kTile * kD;
     if (ok) {
       uint32_t ak[kBwCols], av[kBwCols];
       tmem_ld(tmem_dk + lane_addr + c0, ak);
@@ -688,24 +684,24 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tmem_ld_wait();
       float gmk = 0.f, gmv = 0.f;            // lane t is the head dim here, a column a key row
       if (mean_grad_k != nullptr) {
-        gmk = __bfloat162float(mean_grad_k[mean_off + t]) * mean_inv;
-        gmv = __bfloat162float(mean_grad_v[mean_off + t]) * mean_inv;
+        gmk = Elem<elem_t>::to(mean_grad_k[mean_off + t]) * mean_inv;
+        gmv = Elem<elem_t>::to(mean_grad_v[mean_off + t]) * mean_inv;
       }
 #pragma unroll
       for (int j = 0; j < kBwCols; ++j) {
         const bool row_live = (c0 + j) < valid;
-        stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(ak[j]) * scale + (row_live ? gmk : 0.f));
-        stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]) + (row_live ? gmv : 0.f));
+        stage_k[(c0 + j) * kD + t] = Elem<elem_t>::from(__uint_as_float(ak[j]) * scale + (row_live ? gmk : 0.f));
+        stage_v[(c0 + j) * kD + t] = Elem<elem_t>::from(__uint_as_float(av[j]) + (row_live ? gmv : 0.f));
       }
     } else {
       for (int j = 0; j < kBwCols; ++j) {
-        stage_k[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
-        stage_v[(c0 + j) * kD + t] = __float2bfloat16_rn(0.f);
+        stage_k[(c0 + j) * kD + t] = Elem<elem_t>::from(0.f);
+        stage_v[(c0 + j) * kD + t] = Elem<elem_t>::from(0.f);
       }
     }
     named_barrier(1, kBwEwThreads);
-    bf16* gk = dk + krow0 * kD;
-    bf16* gv = dv + krow0 * kD;
+    elem_t* gk = dk + krow0 * kD;
+    elem_t* gv = dv + krow0 * kD;
 #pragma unroll
     for (int i = 0; i < 1024 / kBwEwThreads; ++i) {
       const int cidx = st + kBwEwThreads * i;
@@ -746,9 +742,9 @@ enum DqdsBar { DD_FULL = 0, DD_EMPTY = kDsStages, DD_ACC_FULL = 2 * kDsStages };
 
 template <int SUB>
 __global__ void __launch_bounds__(kDsThreads, 1)
-sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const bf16* __restrict__ ds_ws,
+sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const elem_t* __restrict__ ds_ws,
                          const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
-                         bf16* __restrict__ dq, const bf16* __restrict__ mean_grad, const int32_t* __restrict__ q_sizes,
+                         elem_t* __restrict__ dq, const elem_t* __restrict__ mean_grad, const int32_t* __restrict__ q_sizes,
                          long long Lq, long long Lkv, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
@@ -846,7 +842,7 @@ sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const bf16* 
     }
     if (!ok && lane == 0) report_timeout(34);
   } else if (warp == 1) {
-    constexpr uint32_t idesc = instr_desc(128, 64, 1, 0);     // A = K^T (dims contiguous), B = dS (keys contiguous)
+    constexpr uint32_t idesc = instr_desc(128, 64, 1, 0, kInFmt);     // A = K^T (dims contiguous), B = dS (keys contiguous)
     constexpr uint32_t hi = desc_hi(1024);
     // B: un-swizzled K-major, core matrices of 8 query rows x 16 bytes; the next 8 rows 128 bytes on, the next
     // 8 key tokens (chunk) 1024 bytes on; one MMA consumes two chunks
@@ -905,13 +901,13 @@ sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const bf16* 
     int rows_live = 0;
     if (mean_grad != nullptr) {   // block-mean backward folded in, as in the recomputing dQ kernel
       const int size = q_sizes[qb];
-      gm = __bfloat162float(mean_grad[(bh * Qb + qb) * (long long)kD + t]) / (float)(size > 1 ? size : 1);
+      gm = Elem<elem_t>::to(mean_grad[(bh * Qb + qb) * (long long)kD + t]) / (float)(size > 1 ? size : 1);
       rows_live = size - qsub * kTile;
     }
     if (n_live > 0) ok = VSA_WARP_WAIT(bar(DD_ACC_FULL), 0);
     if (!ok && lane == 0) report_timeout(33);
     tc_fence_after();
-    bf16* stage = reinterpret_cast<bf16*>(sm + DqdsSmem::ring);     // [64 query rows][128 dims]; every MMA is done
+    elem_t* stage = reinterpret_cast<elem_t*>(sm + DqdsSmem::ring);     // [64 query rows][128 dims]; every MMA is done
 #pragma unroll
     for (int hcol = 0; hcol < 2; ++hcol) {
       uint32_t av[32];
@@ -925,11 +921,11 @@ sparse_dq_from_ds_kernel(const __grid_constant__ CUtensorMap map_k, const bf16* 
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const int c = hcol * 32 + j;
-        stage[c * kD + t] = __float2bfloat16_rn(__uint_as_float(av[j]) * scale + (c < rows_live ? gm : 0.f));
+        stage[c * kD + t] = Elem<elem_t>::from(__uint_as_float(av[j]) * scale + (c < rows_live ? gm : 0.f));
       }
     }
     named_barrier(1, 128);
-    bf16* og = dq + qrow0 * kD;
+    elem_t* og = dq + qrow0 * kD;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int cidx = st + 128 * i;

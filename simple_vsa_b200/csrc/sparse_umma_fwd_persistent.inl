@@ -38,9 +38,9 @@ template <int SUB>
 __global__ void __launch_bounds__(kFwdPThreads, 1)
 sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                   const __grid_constant__ CUtensorMap map_v, const int32_t* __restrict__ selected,
-                                  const int32_t* __restrict__ kv_sizes, bf16* __restrict__ out,
-                                  float* __restrict__ lse2, const bf16* __restrict__ out_c,
-                                  const bf16* __restrict__ gate, bf16* __restrict__ out_comb, long long BH, long long Lq,
+                                  const int32_t* __restrict__ kv_sizes, elem_t* __restrict__ out,
+                                  float* __restrict__ lse2, const elem_t* __restrict__ out_c,
+                                  const elem_t* __restrict__ gate, elem_t* __restrict__ out_comb, long long BH, long long Lq,
                                   long long Lkv, long long kv_shard, int topk, float scale) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;   // an earlier wait ran out: drain without touching anything
@@ -239,7 +239,7 @@ sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, con
     float* m_warp = reinterpret_cast<float*>(sm + FwdPSmem::m_warp);
     float* m_col = reinterpret_cast<float*>(sm + FwdPSmem::m_col);
     float* l_col = reinterpret_cast<float*>(sm + FwdPSmem::l_col);
-    bf16* stage = reinterpret_cast<bf16*>(sm + FwdPSmem::stage);
+    elem_t* stage = reinterpret_cast<elem_t*>(sm + FwdPSmem::stage);
     volatile uint32_t* flag = misc + 3;
     unsigned cnt = 0;
     int j = 0;
@@ -307,8 +307,8 @@ sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, con
           const float p2 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 2]), c, -m4.z)) : 0.f;
           const float p3 = live ? fast_exp2(fmaf(__uint_as_float(sv[4 * j4 + 3]), c, -m4.w)) : 0.f;
           lsum[4 * j4 + 0] += p0; lsum[4 * j4 + 1] += p1; lsum[4 * j4 + 2] += p2; lsum[4 * j4 + 3] += p3;
-          packed[2 * j4] = pack_bf16(p0, p1);
-          packed[2 * j4 + 1] = pack_bf16(p2, p3);
+          packed[2 * j4] = Elem<elem_t>::pack(p0, p1);
+          packed[2 * j4 + 1] = Elem<elem_t>::pack(p2, p3);
         }
         uint8_t* prow = sm + FwdPSmem::p + s * kPairHalf + t * 128;
 #pragma unroll
@@ -347,19 +347,19 @@ sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, con
           const float l = l_col[qi];
           const float o = __uint_as_float(ov[i]) / l;
           finite = finite && (fabsf(o) <= 3.0e38f) && (l <= 3.0e38f);
-          stage[qi * kD + t] = __float2bfloat16_rn(o);
+          stage[qi * kD + t] = Elem<elem_t>::from(o);
         }
       } else {
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(PO_EMPTY + b));
-        for (int i = 0; i < kEwCols; ++i) stage[(c0 + i) * kD + t] = __float2bfloat16_rn(NAN);
+        for (int i = 0; i < kEwCols; ++i) stage[(c0 + i) * kD + t] = Elem<elem_t>::from(NAN);
       }
       // vote across the softmax threads through shared memory
       if (!finite) *flag = 1u;
       named_barrier(1, kEwThreads);
       const bool redo = (*flag != 0u);
       const long long row0 = bh * Lq + (long long)qtile * kTile;
-      bf16* og = out + row0 * kD;
+      elem_t* og = out + row0 * kD;
 #pragma unroll
       for (int i = 0; i < 1024 / kEwThreads; ++i) {
         const int cidx = st + kEwThreads * i;         // 1024 chunks of 16 bytes
@@ -370,7 +370,7 @@ sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, con
           const uint4 cv = *reinterpret_cast<const uint4*>(out_c + (bh * Qb + qb) * (long long)kD + ch * 8);
           uint4 gv = make_uint4(0, 0, 0, 0);
           if (gate != nullptr) gv = *reinterpret_cast<const uint4*>(gate + (row0 + row) * kD + ch * 8);
-          *reinterpret_cast<uint4*>(out_comb + (row0 + row) * kD + ch * 8) = combine_bf16x8(sv4, cv, gv, gate != nullptr);
+          *reinterpret_cast<uint4*>(out_comb + (row0 + row) * kD + ch * 8) = combine_x8<elem_t>(sv4, cv, gv, gate != nullptr);
         }
       }
       if (st < 64) {

@@ -171,10 +171,10 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
-// major: 0 = K-major operand, 1 = MN-major operand.
-__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+// Instruction descriptor for kind::f16 with 16-bit inputs and fp32 accumulation.
+// major: 0 = K-major operand, 1 = MN-major operand.  in_fmt: format of both inputs, 1 = bf16, 0 = fp16.
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int a_mn_major, int b_mn_major, uint32_t in_fmt = 1u) {
+  return (1u << 4) | (in_fmt << 7) | (in_fmt << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 

@@ -430,9 +430,12 @@ class _ShardedVideoSparseAttention(torch.autograd.Function):
 
 
 def sharded_supported(q: Tensor, be: int, topk: int) -> bool:
-    """Whether the shard-major kernels cover these tensors (bf16, head dim 128, block volume 64 or 256, CUDA)."""
-    return bool(q.is_cuda and q.dtype == torch.bfloat16 and
-                _lib.lib.vsa_sparse_sharded_supported(q.shape[-1], be, topk, _lib.VSA_BF16))
+    """Whether the shard-major kernels cover these tensors (bf16 or fp16, head dim 128, block volume 64 or 256,
+    CUDA)."""
+    if not q.is_cuda or q.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    dt = _lib.VSA_BF16 if q.dtype == torch.bfloat16 else _lib.VSA_F16
+    return bool(_lib.lib.vsa_sparse_sharded_supported(q.shape[-1], be, topk, dt))
 
 
 def vsa_on_gathered_shards(q, k_sh, v_sh, kc, vc, variable_block_sizes, q_variable_block_sizes, topk: int,
@@ -461,7 +464,7 @@ def vsa_on_gathered_shards(q, k_sh, v_sh, kc, vc, variable_block_sizes, q_variab
     if gate is not None and gate.shape != q.shape:
         raise ValueError("compress_attn_weight must have the same shape as q")
     if not sharded_supported(q, be, topk):
-        raise ValueError("the shard-major path needs bfloat16 CUDA tensors with head dim 128 and block volume 64 or 256")
+        raise ValueError("the shard-major path needs bfloat16 or float16 CUDA tensors with head dim 128 and block volume 64 or 256")
     scale = 1.0 / math.sqrt(D)
     with torch.cuda.device(q.device):
         q, k_sh, v_sh = _dense(q), _dense(k_sh), _dense(v_sh)

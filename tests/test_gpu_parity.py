@@ -821,13 +821,14 @@ def test_the_two_schedules_of_the_forward_give_the_same_bits(be, nb, tk, monkeyp
     assert torch.isnan(out_s.float().cpu()[~live]).all()
 
 
-@pytest.mark.parametrize("seed", list(range(10)))
+@pytest.mark.parametrize("seed", list(range(14)))
 def test_random_shapes_tensor_path_matches_cuda_core_path(seed, monkeypatch):
     """Seeded random problems (block 64 or 256, 1..40 blocks, any topk, query length != key length, random ragged
     and empty blocks, with and without a gate): the whole operator on the tcgen05 kernels against the same call on
-    the CUDA-core kernels, forward and every gradient.  The routes are fixed by the first run's Top-K (pooled scores
+    the CUDA-core kernels, forward and every gradient; seeds from 10 up run in fp16, the others in bf16.  The routes are fixed by the first run's Top-K (pooled scores
     are computed by the same kernels in both runs)."""
     V = _V()
+    dt = torch.float16 if seed >= 10 else torch.bfloat16
     g = torch.Generator().manual_seed(1000 + seed)
     ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
     be = 64 if ri(0, 3) else 256
@@ -835,10 +836,10 @@ def test_random_shapes_tensor_path_matches_cuda_core_path(seed, monkeypatch):
     Qb = ri(1, 24 if be == 64 else 6)
     tk = ri(1, Kb)
     B, H, D = ri(1, 2), ri(1, 3), 128
-    q = torch.randn(B, H, Qb * be, D, generator=g).to(torch.bfloat16)
-    k, v = (torch.randn(B, H, Kb * be, D, generator=g).to(torch.bfloat16) for _ in range(2))
-    dout = torch.randn(B, H, Qb * be, D, generator=g).to(torch.bfloat16)
-    gate = torch.randn(B, H, Qb * be, D, generator=g).to(torch.bfloat16) if ri(0, 1) else None
+    q = torch.randn(B, H, Qb * be, D, generator=g).to(dt)
+    k, v = (torch.randn(B, H, Kb * be, D, generator=g).to(dt) for _ in range(2))
+    dout = torch.randn(B, H, Qb * be, D, generator=g).to(dt)
+    gate = torch.randn(B, H, Qb * be, D, generator=g).to(dt) if ri(0, 1) else None
     kv_sizes = torch.full((Kb,), be)
     q_sizes = torch.full((Qb,), be)
     for sizes in (kv_sizes, q_sizes):
