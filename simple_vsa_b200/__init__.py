@@ -106,10 +106,53 @@ def topk_block_mask(scores: Tensor, topk: int) -> Tensor:
     return mask.view(scores.shape)
 
 
+class _HeadMajorLinear(torch.autograd.Function):
+    """``y[b, h, s, :] = x[b, s, :] @ W[h*D:(h+1)*D, :]^T + bias[h*D:(h+1)*D]`` written straight into a dense
+    ``[B, H, S, D]`` tensor: one library GEMM per batch entry, batched over the heads (the hidden states are the
+    shared left operand, broadcast with a zero batch stride; every head's slice of the weight is a right operand).
+    The reference's layer (``vsa/common.py:317-328``) returns ``Linear(x).view(B,S,H,D).transpose(1,2)``, a strided
+    view that the attention operator has to copy into the dense layout its kernels read; here the GEMM's own
+    store does the re-layout.  The backward brings the gate gradient back to ``[B, S, H*D]`` once (the copy
+    autograd makes on the reference path too) and runs the two usual GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, heads):
+        B, S, dim_in = x.shape
+        dim_out = weight.shape[0]
+        D = dim_out // heads
+        wt = weight.view(heads, D, dim_in).transpose(1, 2)                 # [H, dim_in, D], a view
+        out = torch.empty((B, heads, S, D), device=x.device, dtype=x.dtype)
+        for b in range(B):
+            xb = x[b].unsqueeze(0).expand(heads, S, dim_in)
+            if bias is None:
+                torch.bmm(xb, wt, out=out[b])
+            else:
+                torch.baddbmm(bias.view(heads, 1, D), xb, wt, out=out[b])
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        B, S, dim_in = x.shape
+        dyt = dy.transpose(1, 2).reshape(B * S, weight.shape[0])            # [B*S, H*D]: the one re-layout copy
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = (dyt @ weight).view(B, S, dim_in)
+        if ctx.needs_input_grad[1]:
+            dw = dyt.t() @ x.reshape(B * S, dim_in)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dyt.sum(0)
+        return dx, dw, db, None
+
+
 class CompressionGate(nn.Module):
-    """Produces ``compress_attn_weight``: a bias-optional ``Linear(dim, dim)`` on the hidden
-    states, reshaped to ``[batch, heads, seq_len, head_dim]`` (no activation).  It sits
-    outside the attention operator; kept here so model code can import it from one place."""
+    """Produces ``compress_attn_weight``: a bias-optional ``Linear(dim, dim)`` on the hidden states (no
+    activation), returned as ``[batch, heads, seq_len, head_dim]`` -- same parameters (``to_gate_compress``), same
+    numbers and same ``ValueError`` as the reference's layer (``vsa/common.py:288-328``).  The result is DENSE in
+    that layout: the GEMM writes every head's ``[seq_len, head_dim]`` panel where the attention kernels read it,
+    so no transposing copy sits between this layer and the operator."""
 
     def __init__(self, dim: int, num_heads: int, bias: bool = True) -> None:
         super().__init__()
@@ -121,5 +164,5 @@ class CompressionGate(nn.Module):
     def forward(self, hidden_states: Tensor) -> Tensor:
         if hidden_states.ndim != 3:
             raise ValueError("hidden_states must have shape [batch, seq_len, dim]")
-        b, s, _ = hidden_states.shape
-        return self.to_gate_compress(hidden_states).view(b, s, self.num_heads, -1).transpose(1, 2)
+        layer = self.to_gate_compress
+        return _HeadMajorLinear.apply(hidden_states, layer.weight, layer.bias, self.num_heads)

@@ -102,6 +102,32 @@ def test_compression_gate_shape_layout_and_argument_check():
         V.CompressionGate(dim=10, num_heads=3)
 
 
+@pytest.mark.parametrize("bias", [True, False])
+def test_compression_gate_is_dense_head_major_and_equals_the_linear_layer(bias):
+    """The layer writes the gate in the dense [B,H,S,D] layout the kernels read (the reference returns a
+    transposed view of Linear's output, vsa/common.py:326-328); values and all three gradients are those of the
+    plain Linear + view + transpose."""
+    import torch
+
+    import simple_vsa_b200 as V
+    torch.manual_seed(3)
+    B, H, S, D = 2, 3, 10, 8
+    layer = V.CompressionGate(H * D, H, bias=bias).double()
+    x = torch.randn(B, S, H * D, dtype=torch.double, requires_grad=True)
+    gate = layer(x)
+    assert gate.is_contiguous() and gate.shape == (B, H, S, D)
+    want = layer.to_gate_compress(x).view(B, S, H, D).transpose(1, 2)
+    torch.testing.assert_close(gate, want, atol=1e-12, rtol=1e-12)
+    w = torch.randn_like(gate)
+    params = [x, layer.to_gate_compress.weight] + ([layer.to_gate_compress.bias] if bias else [])
+    got = torch.autograd.grad((gate * w).sum(), params)
+    ref = torch.autograd.grad((want * w).sum(), params)
+    for a, b in zip(got, ref):
+        torch.testing.assert_close(a, b, atol=1e-12, rtol=1e-12)
+    # the parameters keep the reference's names, so its checkpoints load
+    assert set(layer.state_dict()) == {"to_gate_compress.weight"} | ({"to_gate_compress.bias"} if bias else set())
+
+
 def test_workspace_sizes_and_support_queries_need_no_gpu():
     import simple_vsa_b200._lib as L
     lib = L.lib

@@ -608,6 +608,35 @@ def test_compression_gate_trains_through_the_operator():
     _assert_close(grad, layer_c.to_gate_compress.weight.grad, atol=1e-5, rtol=1e-4)
 
 
+def test_compression_gate_writes_the_operator_layout_without_a_transposing_copy():
+    """bf16, 4 heads of 128: the gate comes out dense in [B,H,S,D] (the operator's ``_dense`` then copies nothing),
+    equals the reference form Linear(x).view(B,S,H,D).transpose(1,2) up to one bf16 rounding of the same fp32 sums,
+    and the batched GEMM does not materialise the hidden states once per head."""
+    V = _V()
+    torch.manual_seed(5)
+    B, H, S, D = 2, 4, 4096, 128
+    dim = H * D
+    layer = V.CompressionGate(dim, H).to(DEV).to(torch.bfloat16)
+    x = (torch.randn(B, S, dim, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    before = torch.cuda.memory_allocated()
+    gate = layer(x)
+    torch.cuda.synchronize()
+    grown = torch.cuda.max_memory_allocated() - before
+    assert gate.is_contiguous() and gate.shape == (B, H, S, D)
+    assert grown < 2 * gate.numel() * 2 + (8 << 20), grown          # the output (+ library workspace), not H copies of x
+    want = layer.to_gate_compress(x).view(B, S, H, D).transpose(1, 2)
+    _assert_close(gate.detach(), want.detach(), atol=2e-2, rtol=2e-2)
+    w = torch.randn_like(gate)
+    params = [x, layer.to_gate_compress.weight, layer.to_gate_compress.bias]
+    got = torch.autograd.grad((gate.float() * w.float()).sum(), params)
+    ref = torch.autograd.grad((want.float() * w.float()).sum(), params)
+    for a, b in zip(got, ref):
+        scale = max(1.0, float(b.float().abs().max()))
+        _assert_close(a, b, atol=2e-2 * scale, rtol=2e-2)
+
+
 @pytest.mark.parametrize("kernels", ["auto", "mma", "scalar"])
 def test_route_ids_outside_the_key_table_count_as_empty_blocks(kernels, monkeypatch):
     """A caller-supplied routing table may hold ids that are not key blocks (negative, or >= Kb).  Every consumer
