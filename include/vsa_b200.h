@@ -19,7 +19,7 @@
  *   counts, offsets                 [BH, Kb]         int32 (CSR of key block -> query blocks)
  *   inverse                         [BH, Qb*topk]    int32 query-block ids grouped by key block
  *
- * dtype: VSA_BF16 or VSA_F16 (tensor-core kernels for D = 128 and be = 64 or 256, scalar
+ * dtype: VSA_BF16 or VSA_F16 (tensor-core kernels for D = 128 and be = 64, 128 or 256, scalar
  * kernels otherwise; the reference accepts both) or VSA_F32 (scalar kernels, the fp32
  * validation mode).
  *
@@ -235,7 +235,7 @@ int vsa_sparse_bwd_dkdv_fused(const void* dout, const void* q, const void* k, co
  * rounding, deterministic, 16 of 56 tensor-core products per pair of edges fewer -- paid for with 8 KB per
  * edge written and read back, which on a B200 costs the key-owned pass about what the dQ pass gains; the
  * Python operator therefore uses it only on request.  Tensor path only: vsa_sparse_bwd_ds_supported() says
- * whether a shape qualifies (bf16 or fp16, D = 128, be = 64 or 256).
+ * whether a shape qualifies (bf16 or fp16, D = 128, be = 64, 128 or 256).
  *
  * ds_ws holds one 16-bit tile (the dtype of the call) of 64 query rows x 64 key tokens (8 KB, stored as 8 chunks of 8 key tokens, each
  * chunk [64 rows][16 bytes]) per (query tile, selected key tile):
@@ -289,7 +289,7 @@ int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int3
  * tokens (a multiple of be).  So no re-layout copy follows the gather, and the partial dK/dV are contiguous
  * per owner rank, ready for the reduce-scatter.  q, out, dq ... are this rank's [BH, Lq, D] as usual;
  * selected holds GLOBAL key-block ids; kv_sizes lists all Kb = Lkv/be blocks.  Tensor path only (bf16 or
- * fp16, D = 128, be = 64 or 256), VSA_ERR_UNSUPPORTED otherwise.  kv_shard = Lkv is the ordinary layout. */
+ * fp16, D = 128, be = 64, 128 or 256), VSA_ERR_UNSUPPORTED otherwise.  kv_shard = Lkv is the ordinary layout. */
 
 /* 1 if the three entry points below cover (D, be, topk, dtype) in this process, else 0. */
 int vsa_sparse_sharded_supported(int D, int be, int topk, int dtype);

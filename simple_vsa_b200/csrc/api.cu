@@ -339,7 +339,7 @@ int vsa_sparse_bwd_dkdv_ds(const void* dout, const void* q, const void* k, const
               "sparse dK/dV (dS stored): null pointer");
   VSA_REQUIRE((dk_mean == nullptr) == (dv_mean == nullptr), "sparse dK/dV (dS stored): give both pooled gradients or neither");
   if (!vsa_sparse_bwd_ds_supported(D, be, topk, dtype))
-    return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV (dS stored): needs bf16 or fp16, head dim 128, block volume 64 or 256");
+    return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV (dS stored): needs bf16 or fp16, head dim 128, block volume 64, 128 or 256");
   return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse_edges, kv_sizes, dk, dv, BH, Lq, Lkv, be,
                           topk, scale, dtype, (cudaStream_t)stream, dk_mean, dv_mean, ds_ws);
 }
@@ -352,7 +352,7 @@ int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int3
   VSA_REQUIRE(k && selected && kv_sizes && ds_ws && dq, "sparse dQ (from dS): null pointer");
   VSA_REQUIRE((dq_mean == nullptr) == (q_sizes == nullptr), "sparse dQ (from dS): give the pooled gradient and the query sizes, or neither");
   if (!vsa_sparse_bwd_ds_supported(D, be, topk, dtype))
-    return fail(VSA_ERR_UNSUPPORTED, "sparse dQ (from dS): needs bf16 or fp16, head dim 128, block volume 64 or 256");
+    return fail(VSA_ERR_UNSUPPORTED, "sparse dQ (from dS): needs bf16 or fp16, head dim 128, block volume 64, 128 or 256");
   return sparse_dq_from_ds_umma(k, selected, kv_sizes, ds_ws, dq, BH, Lq, Lkv, be, topk, scale, dtype,
                                 (cudaStream_t)stream, dq_mean, q_sizes);
 }
@@ -361,12 +361,12 @@ int vsa_sparse_bwd_dq_from_ds(const void* k, const int32_t* selected, const int3
 // After an all-gather over W ranks the K/V shards lie one after another, [W][BH][Lkv/W][D].  These three entry
 // points read (and, for dK/dV, write) that layout in place: row of (slice, token) = ((token / shard) * BH + slice)
 // * shard + token % shard with shard = kv_shard tokens, so no re-layout copy follows the gather and the partial
-// dK/dV are ready for the reduce-scatter.  Tensor path only (bf16 or fp16, D = 128, block volume 64 or 256).
+// dK/dV are ready for the reduce-scatter.  Tensor path only (bf16 or fp16, D = 128, block volume 64, 128 or 256).
 static int check_sharded(int64_t Lkv, int64_t kv_shard, int D, int be, int topk, int dtype, const char* what) {
   VSA_REQUIRE(kv_shard > 0 && Lkv % kv_shard == 0 && kv_shard % be == 0,
               "%s: kv_shard must divide Lkv and be a multiple of block_elements=%d", what, be);
   if (scalar_forced() || mma_forced() || !sparse_umma_eligible(D, be, dtype, topk))
-    return fail(VSA_ERR_UNSUPPORTED, "%s: the shard-major layout needs bf16 or fp16, head dim 128, block volume 64 or 256", what);
+    return fail(VSA_ERR_UNSUPPORTED, "%s: the shard-major layout needs bf16 or fp16, head dim 128, block volume 64, 128 or 256", what);
   return VSA_OK;
 }
 

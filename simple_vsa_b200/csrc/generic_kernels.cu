@@ -3,7 +3,7 @@
 // Two roles: (1) the bandwidth-bound pieces of every configuration -- block
 // means, pooled softmax, Top-K, gated combine, route inversion -- and (2) the
 // fine attention forward/backward for shapes the tensor-core kernels do not
-// cover (fp32 validation mode, block volumes other than 64/256, head dims
+// cover (fp32 validation mode, block volumes other than 64/128/256, head dims
 // other than 128).  Arithmetic follows the reference project's conventions:
 // fp32 accumulation, base-2 log-sum-exp, masks from the per-block sizes.
 #include <cuda_fp16.h>

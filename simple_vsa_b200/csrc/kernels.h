@@ -41,7 +41,7 @@ int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const voi
                        const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
                        int topk, float scale, int dtype, cudaStream_t st);
 
-// ---- tensor-core kernels, bf16 or fp16, head dim 128, block volume 64 or 256 (sparse_mma.cu) ------
+// ---- tensor-core kernels, bf16 or fp16, head dim 128, block volume 64, 128 or 256 (sparse_mma.cu) ------
 bool sparse_tc_eligible(int D, int be, int dtype);
 // redo_only: recompute only the 64-row query tiles whose first lse2 entry is NaN (the marker the
 // tcgen05 forward leaves on a tile whose fixed softmax shift ran out of range).

@@ -1,6 +1,6 @@
 // Fine (block-sparse) attention on the warp-level tensor path: forward, the
 // query-owned dQ pass and the key-owned dK/dV pass, for bf16, head dim 128 and a
-// logical block volume of 64 or 256 tokens.
+// logical block volume of 64, 128 or 256 tokens.
 //
 // Every kernel works on 64-token x 128-dim tiles (16 KB, contiguous in global
 // memory because a block's tokens are consecutive rows).  A logical block of 256
@@ -576,7 +576,7 @@ int set_smem(K kernel, int bytes, const char* what) {
 
 }  // namespace
 
-bool sparse_tc_eligible(int D, int be, int dtype) { return (dtype == VSA_BF16 || dtype == VSA_F16) && D == 128 && (be == 64 || be == 256); }
+bool sparse_tc_eligible(int D, int be, int dtype) { return (dtype == VSA_BF16 || dtype == VSA_F16) && D == 128 && (be == 64 || be == 128 || be == 256); }
 
 template <typename T>
 static int launch_fwd(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
@@ -591,7 +591,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, const int32_t
                                            redo_only ? 1 : 0);
     return check_launch("sparse_fwd_mma_kernel");
   };
-  return be == 64 ? launch(sparse_fwd_mma_kernel<T, 1>) : launch(sparse_fwd_mma_kernel<T, 4>);
+  return be == 64 ? launch(sparse_fwd_mma_kernel<T, 1>) : be == 128 ? launch(sparse_fwd_mma_kernel<T, 2>) : launch(sparse_fwd_mma_kernel<T, 4>);
 }
 
 template <typename T>
@@ -606,7 +606,7 @@ static int launch_dq(const void* dout, const void* q, const void* k, const void*
                                           selected, kv_sizes, delta, (T*)dq, Lq, Lkv, topk, scale);
     return check_launch("sparse_dq_mma_kernel");
   };
-  return be == 64 ? launch(sparse_dq_mma_kernel<T, 1>) : launch(sparse_dq_mma_kernel<T, 4>);
+  return be == 64 ? launch(sparse_dq_mma_kernel<T, 1>) : be == 128 ? launch(sparse_dq_mma_kernel<T, 2>) : launch(sparse_dq_mma_kernel<T, 4>);
 }
 
 template <typename T>
@@ -622,7 +622,7 @@ static int launch_dkdv(const void* dout, const void* q, const void* k, const voi
                                             offsets, inverse, kv_sizes, (T*)dk, (T*)dv, Lq, Lkv, topk, scale);
     return check_launch("sparse_dkdv_mma_kernel");
   };
-  return be == 64 ? launch(sparse_dkdv_mma_kernel<T, 1>) : launch(sparse_dkdv_mma_kernel<T, 4>);
+  return be == 64 ? launch(sparse_dkdv_mma_kernel<T, 1>) : be == 128 ? launch(sparse_dkdv_mma_kernel<T, 2>) : launch(sparse_dkdv_mma_kernel<T, 4>);
 }
 
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,

@@ -242,6 +242,10 @@ int check_kv_shard(int64_t Lkv, int be, int64_t* kv_shard, const char* what) {
 
 }  // namespace
 
+// A logical block of 64, 128 or 256 tokens is walked as 1, 2 or 4 tiles of 64 tokens (the kernels' SUB parameter).
+#define VSA_BY_BLOCK_VOLUME(be_, launch_, kernel_) \
+  return (be_) == 64 ? launch_(kernel_<1>) : (be_) == 128 ? launch_(kernel_<2>) : launch_(kernel_<4>)
+
 // The kernels exist once per 16-bit element type: same code, other input format in the instruction descriptor and
 // the tensor maps, other conversions in the epilogues.
 namespace tc_bf16 {
@@ -264,8 +268,7 @@ constexpr int kDtypeCode = VSA_F16;
 // ---- host entry points ---------------------------------------------------------------------------------------
 bool sparse_umma_eligible(int D, int be, int dtype, int topk) {
   if ((dtype != VSA_BF16 && dtype != VSA_F16) || D != 128) return false;
-  if (be == 64) return topk <= kMaxTiles;
-  if (be == 256) return topk * 4 <= kMaxTiles;
+  if (be == 64 || be == 128 || be == 256) return topk * (be / kTile) <= kMaxTiles;
   return false;
 }
 

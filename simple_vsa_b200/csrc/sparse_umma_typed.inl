@@ -391,23 +391,17 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
                                               (const elem_t*)gate, (elem_t*)out_comb, (long long)BH, Lq, Lkv, kv_shard, topk, scale);
       return check_launch("sparse_fwd_umma_persistent_kernel");
     };
-    return be == 64 ? launch(sparse_fwd_umma_persistent_kernel<1>) : launch(sparse_fwd_umma_persistent_kernel<4>);
+    VSA_BY_BLOCK_VOLUME(be, launch, sparse_fwd_umma_persistent_kernel);
   }
   const int smem = FwdSmem::total + 1024;
   dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
-  cudaError_t e;
-  if (be == 64) {
-    e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
-    sparse_fwd_umma_kernel<1><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (elem_t*)out, lse2, (const elem_t*)out_c,
-                                                               (const elem_t*)gate, (elem_t*)out_comb, Lq, Lkv, kv_shard, topk, scale);
-  } else {
-    e = cudaFuncSetAttribute(sparse_fwd_umma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(VSA_ERR_LAUNCH, "sparse forward: shared memory: %s", cudaGetErrorString(e));
-    sparse_fwd_umma_kernel<4><<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (elem_t*)out, lse2, (const elem_t*)out_c,
-                                                               (const elem_t*)gate, (elem_t*)out_comb, Lq, Lkv, kv_shard, topk, scale);
-  }
-  return check_launch("sparse_fwd_umma_kernel");
+  auto launch = [&](auto kern) -> int {
+    if ((rc = reserve_smem(kern, smem, "sparse forward"))) return rc;
+    kern<<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (elem_t*)out, lse2, (const elem_t*)out_c,
+                                          (const elem_t*)gate, (elem_t*)out_comb, Lq, Lkv, kv_shard, topk, scale);
+    return check_launch("sparse_fwd_umma_kernel");
+  };
+  VSA_BY_BLOCK_VOLUME(be, launch, sparse_fwd_umma_kernel);
 }
 
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
@@ -425,18 +419,13 @@ int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v
   if ((rc = make_map(&mv, v, BH * Lkv, "sparse dQ (v)"))) return rc;
   const int smem = DqSmem::total + 1024;
   dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
-  if (be == 64) {
-    if ((rc = reserve_smem(sparse_dq_umma_kernel<1>, smem, "sparse dQ"))) return rc;
-    sparse_dq_umma_kernel<1><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const elem_t*)dout, (const elem_t*)out_s, lse2,
-                                                              selected, kv_sizes, delta, (elem_t*)dq, (const elem_t*)dq_mean, q_sizes, Lq, Lkv,
-                                                              kv_shard, topk, scale);
-  } else {
-    if ((rc = reserve_smem(sparse_dq_umma_kernel<4>, smem, "sparse dQ"))) return rc;
-    sparse_dq_umma_kernel<4><<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const elem_t*)dout, (const elem_t*)out_s, lse2,
-                                                              selected, kv_sizes, delta, (elem_t*)dq, (const elem_t*)dq_mean, q_sizes, Lq, Lkv,
-                                                              kv_shard, topk, scale);
-  }
-  return check_launch("sparse_dq_umma_kernel");
+  auto launch = [&](auto kern) -> int {
+    if ((rc = reserve_smem(kern, smem, "sparse dQ"))) return rc;
+    kern<<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const elem_t*)dout, (const elem_t*)out_s, lse2, selected, kv_sizes,
+                                          delta, (elem_t*)dq, (const elem_t*)dq_mean, q_sizes, Lq, Lkv, kv_shard, topk, scale);
+    return check_launch("sparse_dq_umma_kernel");
+  };
+  VSA_BY_BLOCK_VOLUME(be, launch, sparse_dq_umma_kernel);
 }
 
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
@@ -467,6 +456,7 @@ int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void*
     return check_launch("sparse_dkdv_umma_kernel");
   };
   if (be == 64) return ds_ws ? launch(sparse_dkdv_umma_kernel<1, true>) : launch(sparse_dkdv_umma_kernel<1, false>);
+  if (be == 128) return ds_ws ? launch(sparse_dkdv_umma_kernel<2, true>) : launch(sparse_dkdv_umma_kernel<2, false>);
   return ds_ws ? launch(sparse_dkdv_umma_kernel<4, true>) : launch(sparse_dkdv_umma_kernel<4, false>);
 }
 
@@ -488,7 +478,7 @@ int sparse_dq_from_ds_umma(const void* k, const int32_t* selected, const int32_t
                                          q_sizes, Lq, Lkv, topk, scale);
     return check_launch("sparse_dq_from_ds_kernel");
   };
-  return be == 64 ? launch(sparse_dq_from_ds_kernel<1>) : launch(sparse_dq_from_ds_kernel<4>);
+  VSA_BY_BLOCK_VOLUME(be, launch, sparse_dq_from_ds_kernel);
 }
 
 // C[batch, M, N] = A * B.  a_rows/a_cols and b_rows/b_cols describe the operands as stored in memory.

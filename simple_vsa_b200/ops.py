@@ -430,7 +430,7 @@ class _ShardedVideoSparseAttention(torch.autograd.Function):
 
 
 def sharded_supported(q: Tensor, be: int, topk: int) -> bool:
-    """Whether the shard-major kernels cover these tensors (bf16 or fp16, head dim 128, block volume 64 or 256,
+    """Whether the shard-major kernels cover these tensors (bf16 or fp16, head dim 128, block volume 64, 128 or 256,
     CUDA)."""
     if not q.is_cuda or q.dtype not in (torch.bfloat16, torch.float16):
         return False
@@ -464,7 +464,7 @@ def vsa_on_gathered_shards(q, k_sh, v_sh, kc, vc, variable_block_sizes, q_variab
     if gate is not None and gate.shape != q.shape:
         raise ValueError("compress_attn_weight must have the same shape as q")
     if not sharded_supported(q, be, topk):
-        raise ValueError("the shard-major path needs bfloat16 or float16 CUDA tensors with head dim 128 and block volume 64 or 256")
+        raise ValueError("the shard-major path needs bfloat16 or float16 CUDA tensors with head dim 128 and block volume 64, 128 or 256")
     scale = 1.0 / math.sqrt(D)
     with torch.cuda.device(q.device):
         q, k_sh, v_sh = _dense(q), _dense(k_sh), _dense(v_sh)

@@ -14,7 +14,7 @@ Two modes, neither of which exists in the reference project (its kernels index e
   all-gathered.  The rank then runs pooled scores ``[Qb/W, Kb]``, Top-K and the fine kernels with its
   local queries on global key-block ids (``Lq != Lkv``).  Remote data is always copied into the GPU's
   own memory first; no kernel reads a peer's memory.  Tensors the shard-major kernels do not cover
-  (anything but bf16 / head dim 128 / block volume 64 or 256, and CPU ranks with a stand-in operator)
+  (anything but bf16 / head dim 128 / block volume 64, 128 or 256, and CPU ranks with a stand-in operator)
   take the generic form: gather, re-lay-out to ``[B, H, L, D]``, ordinary operator.
 """
 

@@ -145,8 +145,11 @@ def test_workspace_sizes_and_support_queries_need_no_gpu():
     assert lib.vsa_workspace_bytes(9, BH, Lq, Lkv, D, be, tk, L.VSA_BF16) == -1
     assert lib.vsa_workspace_bytes(0, BH, Lq, Lkv, D, be, tk, 7) == -1
     assert lib.vsa_sparse_bwd_ds_workspace_bytes(1, 1024, 48, 3) == -1
-    # the tensor path covers bf16, head dim 128, block volume 64 or 256 only
+    # the tensor path covers bf16 and fp16, head dim 128, block volume 64, 128 or 256
     assert lib.vsa_sparse_sharded_supported(128, 64, 180, L.VSA_BF16) == 1
+    assert lib.vsa_sparse_sharded_supported(128, 128, 90, L.VSA_F16) == 1
+    assert lib.vsa_sparse_sharded_supported(128, 192, 4, L.VSA_BF16) == 0
+    assert lib.vsa_sparse_sharded_supported(128, 128, 513, L.VSA_BF16) == 0      # 1026 tiles: beyond the tile list
     assert lib.vsa_sparse_sharded_supported(64, 64, 4, L.VSA_BF16) == 0
     assert lib.vsa_sparse_bwd_ds_supported(128, 256, 20, L.VSA_BF16) == 1
     assert lib.vsa_sparse_bwd_ds_supported(128, 64, 180, L.VSA_F32) == 0

@@ -323,7 +323,7 @@ def _zipf_routes(B, H, Qb, Kb, tk, seed):
     return perm[(logw + gumbel).topk(tk, dim=-1).indices].to(torch.int32)
 
 
-@pytest.mark.parametrize("be,nb,tk,ragged", [(64, 24, 6, False), (64, 24, 6, True), (256, 8, 3, True)])
+@pytest.mark.parametrize("be,nb,tk,ragged", [(64, 24, 6, False), (64, 24, 6, True), (256, 8, 3, True), (128, 12, 5, True)])
 def test_fine_attention_midsize_matches_oracle(be, nb, tk, ragged, monkeypatch):
     V = _V()
     torch.manual_seed(41)
@@ -669,7 +669,7 @@ def test_route_ids_outside_the_key_table_count_as_empty_blocks(kernels, monkeypa
     assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
 
 
-@pytest.mark.parametrize("be,nb,tk,ragged", [(64, 24, 6, True), (64, 33, 5, False), (256, 8, 3, True)])
+@pytest.mark.parametrize("be,nb,tk,ragged", [(64, 24, 6, True), (64, 33, 5, False), (256, 8, 3, True), (128, 14, 4, True)])
 def test_backward_that_stores_ds_equals_the_recomputing_backward(be, nb, tk, ragged, monkeypatch):
     """``VSA_B200_BACKWARD=stored_ds`` forms dS once (key-owned pass stores it, query-owned pass multiplies it by K);
     the default backward forms it twice, once per pass.  Same dQ up to the rounding point of the scale (before or
@@ -777,7 +777,7 @@ def test_forward_with_the_combine_folded_in_equals_the_two_step_form(kernels, wi
                       atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("be,nb,tk,W", [(64, 16, 5, 2), (64, 24, 6, 4), (256, 8, 3, 2)])
+@pytest.mark.parametrize("be,nb,tk,W", [(64, 16, 5, 2), (64, 24, 6, 4), (256, 8, 3, 2), (128, 12, 4, 2)])
 def test_shard_major_kv_layout_equals_the_ordinary_layout(be, nb, tk, W):
     """The kernels of the sequence-parallel mode read K/V (and write dK/dV) in the rank-major layout an all-gather
     leaves, ``[W,B,H,L/W,D]``.  One GPU, no collective: the same operator on the same numbers in both layouts, a
@@ -819,7 +819,7 @@ def test_shard_major_kv_layout_equals_the_ordinary_layout(be, nb, tk, W):
                                    sizes, q_sizes, tk, (1, 1, be))
 
 
-@pytest.mark.parametrize("be,nb,tk", [(64, 40, 7), (64, 24, 24), (256, 6, 3)])
+@pytest.mark.parametrize("be,nb,tk", [(64, 40, 7), (64, 24, 24), (256, 6, 3), (128, 10, 6)])
 def test_the_two_schedules_of_the_forward_give_the_same_bits(be, nb, tk, monkeypatch):
     """One CTA per query tile and the persistent form (one CTA per SM walking the query tiles, chosen for short
     routes) run the same arithmetic in the same order: outputs, statistics and combined outputs are bit-identical,
@@ -850,19 +850,21 @@ def test_the_two_schedules_of_the_forward_give_the_same_bits(be, nb, tk, monkeyp
     assert torch.isnan(out_s.float().cpu()[~live]).all()
 
 
-@pytest.mark.parametrize("seed", list(range(14)))
+@pytest.mark.parametrize("seed", list(range(18)))
 def test_random_shapes_tensor_path_matches_cuda_core_path(seed, monkeypatch):
-    """Seeded random problems (block 64 or 256, 1..40 blocks, any topk, query length != key length, random ragged
+    """Seeded random problems (block 64, 128 or 256, 1..40 blocks, any topk, query length != key length, random ragged
     and empty blocks, with and without a gate): the whole operator on the tcgen05 kernels against the same call on
-    the CUDA-core kernels, forward and every gradient; seeds from 10 up run in fp16, the others in bf16.  The routes are fixed by the first run's Top-K (pooled scores
+    the CUDA-core kernels, forward and every gradient; seeds 10-13 run in fp16, the others in bf16; seeds from 14 up use blocks of 128 tokens.  The routes are fixed by the first run's Top-K (pooled scores
     are computed by the same kernels in both runs)."""
     V = _V()
-    dt = torch.float16 if seed >= 10 else torch.bfloat16
+    dt = torch.float16 if 10 <= seed < 14 else torch.bfloat16
     g = torch.Generator().manual_seed(1000 + seed)
     ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
     be = 64 if ri(0, 3) else 256
-    Kb = ri(1, 40 if be == 64 else 10)
-    Qb = ri(1, 24 if be == 64 else 6)
+    if seed >= 14:
+        be = 128
+    Kb = ri(1, {64: 40, 128: 20, 256: 10}[be])
+    Qb = ri(1, {64: 24, 128: 12, 256: 6}[be])
     tk = ri(1, Kb)
     B, H, D = ri(1, 2), ri(1, 3), 128
     q = torch.randn(B, H, Qb * be, D, generator=g).to(dt)

@@ -31,7 +31,7 @@ def _no_device_timeouts():
     assert _lib.device_status() == 0
 
 
-@pytest.mark.parametrize("be,nb,tk,ragged", [(64, 24, 6, False), (64, 24, 7, True), (256, 8, 3, True)])
+@pytest.mark.parametrize("be,nb,tk,ragged", [(64, 24, 6, False), (64, 24, 7, True), (256, 8, 3, True), (128, 12, 5, True)])
 def test_fp16_fine_attention_matches_oracle_on_every_kernel_family(be, nb, tk, ragged, monkeypatch):
     V = _V()
     torch.manual_seed(141)
