@@ -326,6 +326,49 @@ int vsa_sparse_bwd_dkdv_sharded(const void* dout, const void* q, const void* k_s
 int vsa_gather_rows(const void* src, const int32_t* map, void* dst,
                     int64_t batch, int64_t src_rows, int64_t dst_rows, int64_t row_bytes, void* stream);
 
+/* ---- raster-order activations: the tiling front end folded into the kernels --------------------------------
+ * (No single reference counterpart: the reference tiles with index ops, vsa/fastvideo_tiling.py:128-145, and model
+ * code transposes [B,S,H,D] to [B,H,L,D] around the operator.)  A model keeps q/k/v, the gate and the output as
+ * [B, S, H, D] in raster (t, h, w) token order; the kernels read tile-order [B*H, L, D] operands.
+ * vsa_gather_rows_heads builds an operand in one pass (row gather + head transpose + zero padding; to_tiled = 1:
+ * dst [B,H,dst_rows,row] from src [B,src_rows,H,row] with dst row l = src row map[l] or zero where map[l] < 0;
+ * to_tiled = 0: dst [B,dst_rows,H,row] from src [B,H,src_rows,row]; rows are multiples of 16 bytes).
+ * The three *_raster entry points are vsa_sparse_fwd_combine / vsa_sparse_bwd_dq_fused / vsa_sparse_bwd_dkdv_fused
+ * with one difference: the gate is read, and out / dq / dk / dv are written, at the token's raster row
+ * (b*raster_rows + map[token])*heads + h of a [B, raster_rows, heads, D] tensor (BH = B*heads; map[token] < 0 is a
+ * padding row: nothing is read or written for it).  q, k, v, dout, out_s stay tile-order.  Tensor path only
+ * (vsa_sparse_raster_supported), VSA_ERR_UNSUPPORTED otherwise. */
+int vsa_sparse_raster_supported(int D, int be, int topk, int dtype);
+
+int vsa_gather_rows_heads(const void* src, const int32_t* map, void* dst,
+                          int64_t batch, int heads, int64_t src_rows, int64_t dst_rows, int64_t row_bytes,
+                          int to_tiled, void* stream);
+
+int vsa_sparse_fwd_combine_raster(const void* q, const void* k, const void* v,
+                                  const int32_t* selected, const int32_t* kv_sizes,
+                                  void* out_s, float* lse2, const void* out_c,
+                                  const void* gate_raster, void* out_raster,
+                                  const int32_t* q_map, int64_t raster_rows, int heads,
+                                  int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                                  float scale, int dtype, void* stream);
+
+int vsa_sparse_bwd_dq_raster(const void* dout, const void* q, const void* k, const void* v,
+                             const void* out_s, const float* lse2,
+                             const int32_t* selected, const int32_t* kv_sizes,
+                             float* delta, void* dq_raster, const void* dq_mean, const int32_t* q_sizes,
+                             const int32_t* q_map, int64_t raster_rows, int heads,
+                             int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                             float scale, int dtype, void* stream);
+
+int vsa_sparse_bwd_dkdv_raster(const void* dout, const void* q, const void* k, const void* v,
+                               const float* lse2, const float* delta,
+                               const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
+                               const int32_t* kv_sizes, void* dk_raster, void* dv_raster,
+                               const void* dk_mean, const void* dv_mean,
+                               const int32_t* kv_map, int64_t raster_rows, int heads,
+                               int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                               float scale, int dtype, void* stream);
+
 /* out = out_s + out_c[block] * gate (gate may be NULL) in fp32, one rounding.
  * Replaces _combine_forward_kernel: vsa/fused_common.py:175-199,259-295. */
 int vsa_combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out,

@@ -23,6 +23,7 @@ from torch import Tensor, nn
 
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is absent)
 from .tiling import build_vsa_metadata, tile, tile_with, untile, untile_with
+from .raster import tile_heads, untile_heads, video_sparse_attn_raster
 from .ops import (
     BlockSize,
     as_block_elements,
@@ -39,6 +40,7 @@ __all__ = [
     "block_mean", "topk_block_mask", "CompressionGate", "invert_routes",
     "as_block_elements", "validate_vsa_inputs",
     "build_vsa_metadata", "tile", "untile", "tile_with", "untile_with",
+    "video_sparse_attn_raster", "tile_heads", "untile_heads",
 ]
 
 

@@ -44,6 +44,10 @@ SIGNATURES = {
     "vsa_sparse_bwd_dkdv_sharded": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, I, I, I, F, I, P],
     "vsa_combine_fwd": [P, P, P, P, L, L, I, I, I, P],
     "vsa_gather_rows": [P, P, P, L, L, L, L, P],
+    "vsa_gather_rows_heads": [P, P, P, L, I, L, L, L, I, P],
+    "vsa_sparse_fwd_combine_raster": [P, P, P, P, P, P, P, P, P, P, P, L, I, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_bwd_dq_raster": [P, P, P, P, P, P, P, P, P, P, P, P, P, L, I, L, L, L, I, I, I, F, I, P],
+    "vsa_sparse_bwd_dkdv_raster": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, I, L, L, L, I, I, I, F, I, P],
     "vsa_selftest_umma": [P, P, P, I, P],
     "vsa_device_status": [P],
     "vsa_selftest_wait_timeout": [L, P, P],
@@ -54,6 +58,7 @@ PLAIN = {"vsa_last_error_string": ([], c_char_p), "vsa_version": ([], c_int),
          "vsa_workspace_bytes": ([I, L, L, L, I, I, I, I], c_int64),
          "vsa_sparse_bwd_ds_supported": ([I, I, I, I], c_int),
          "vsa_sparse_sharded_supported": ([I, I, I, I], c_int),
+         "vsa_sparse_raster_supported": ([I, I, I, I], c_int),
          "vsa_sparse_bwd_ds_workspace_bytes": ([L, L, I, I], c_int64)}
 
 

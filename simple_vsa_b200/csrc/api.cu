@@ -421,6 +421,81 @@ int vsa_sparse_bwd_dkdv_sharded(const void* dout, const void* q, const void* k_s
                           topk, scale, dtype, (cudaStream_t)stream, dk_mean, dv_mean, nullptr, kv_shard);
 }
 
+// ---- raster-order activations (tiling front end folded into the kernels' stores) ----------------------------
+// A model holds q/k/v, the gate and the output as [B, S, H, D] in raster (t, h, w) token order; the kernels read
+// tile-order [B*H, L, D] operands through TMA.  vsa_gather_rows_heads makes the operands in one pass each
+// (gather + head transpose + zero padding); the three entry points below then read the gate and write the
+// combined output and the three gradients straight at the tokens' raster rows, so nothing is moved back.
+// map: tile-order token -> raster row or -1 (padding).  Tensor path only.
+static int check_raster(const int32_t* map, int64_t rows, int heads, int64_t BH, int D, int be, int topk, int dtype,
+                        const char* what) {
+  VSA_REQUIRE(map != nullptr && rows >= 0 && heads >= 1 && BH % heads == 0, "%s: bad raster map, row count or head count", what);
+  if (scalar_forced() || mma_forced() || !sparse_umma_eligible(D, be, dtype, topk))
+    return fail(VSA_ERR_UNSUPPORTED, "%s: raster-order stores need bf16 or fp16, head dim 128, block volume 64, 128 or 256", what);
+  return VSA_OK;
+}
+
+int vsa_sparse_raster_supported(int D, int be, int topk, int dtype) {
+  return !scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk) ? 1 : 0;
+}
+
+int vsa_gather_rows_heads(const void* src, const int32_t* map, void* dst, int64_t batch, int heads, int64_t src_rows,
+                          int64_t dst_rows, int64_t row_bytes, int to_tiled, void* stream) {
+  VSA_REQUIRE(src && map && dst, "gather rows (heads): null pointer");
+  VSA_REQUIRE(batch >= 0 && heads >= 0 && src_rows >= 0 && dst_rows >= 0 && row_bytes >= 0, "gather rows (heads): negative extent");
+  return gather_rows_heads(src, map, dst, batch, heads, src_rows, dst_rows, row_bytes, to_tiled != 0, (cudaStream_t)stream);
+}
+
+int vsa_sparse_fwd_combine_raster(const void* q, const void* k, const void* v, const int32_t* selected,
+                                  const int32_t* kv_sizes, void* out_s, float* lse2, const void* out_c,
+                                  const void* gate_raster, void* out_raster, const int32_t* q_map, int64_t raster_rows,
+                                  int heads, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale,
+                                  int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(q && k && v && selected && kv_sizes && out_s && lse2 && out_c && out_raster,
+              "sparse forward (raster): null pointer");
+  if ((rc = check_raster(q_map, raster_rows, heads, BH, D, be, topk, dtype, "sparse forward (raster)"))) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  rc = sparse_fwd_umma(q, k, v, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, st, out_c,
+                       gate_raster, out_raster, 0, q_map, raster_rows, heads);
+  if (rc) return rc;
+  return sparse_fwd_tc(q, k, v, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, true, st, out_c,
+                       gate_raster, out_raster, 0, q_map, raster_rows, heads);
+}
+
+int vsa_sparse_bwd_dq_raster(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
+                             const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta,
+                             void* dq_raster, const void* dq_mean, const int32_t* q_sizes, const int32_t* q_map,
+                             int64_t raster_rows, int heads, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
+                             float scale, int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && q && k && v && out_s && lse2 && selected && kv_sizes && delta && dq_raster,
+              "sparse dQ (raster): null pointer");
+  VSA_REQUIRE((dq_mean == nullptr) == (q_sizes == nullptr), "sparse dQ (raster): give the pooled gradient and the query sizes, or neither");
+  if ((rc = check_raster(q_map, raster_rows, heads, BH, D, be, topk, dtype, "sparse dQ (raster)"))) return rc;
+  return sparse_dq_umma(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq_raster, BH, Lq, Lkv, be, topk, scale,
+                        dtype, (cudaStream_t)stream, dq_mean, q_sizes, 0, q_map, raster_rows, heads);
+}
+
+int vsa_sparse_bwd_dkdv_raster(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
+                               const float* delta, const int32_t* counts, const int32_t* offsets,
+                               const int32_t* inverse, const int32_t* kv_sizes, void* dk_raster, void* dv_raster,
+                               const void* dk_mean, const void* dv_mean, const int32_t* kv_map, int64_t raster_rows,
+                               int heads, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale,
+                               int dtype, void* stream) {
+  int rc = check_sparse(BH, Lq, Lkv, D, be, topk, dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout && q && k && v && lse2 && delta && counts && offsets && inverse && kv_sizes && dk_raster && dv_raster,
+              "sparse dK/dV (raster): null pointer");
+  VSA_REQUIRE((dk_mean == nullptr) == (dv_mean == nullptr), "sparse dK/dV (raster): give both pooled gradients or neither");
+  if ((rc = check_raster(kv_map, raster_rows, heads, BH, D, be, topk, dtype, "sparse dK/dV (raster)"))) return rc;
+  return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk_raster, dv_raster, BH, Lq,
+                          Lkv, be, topk, scale, dtype, (cudaStream_t)stream, dk_mean, dv_mean, nullptr, 0, kv_map,
+                          raster_rows, heads);
+}
+
 int vsa_gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
                     int64_t row_bytes, void* stream) {
   VSA_REQUIRE(src && map && dst, "gather rows: null pointer");

@@ -87,6 +87,22 @@ __device__ __forceinline__ long long kv_tensor_row(long long bh, long long BH, l
   return (r * BH + bh) * shard + (token - r * shard);
 }
 
+// Optional re-layout of per-token rows on the way in or out of a kernel.  The attention kernels work on tile-order
+// tensors [BH][L][D] (L = blocks x block volume, padding rows included); a model keeps its activations in raster
+// order [B][S][H][D].  With a map, tile-order token t of slice (b, h) lives at raster row (b*S + map[t])*H + h;
+// map[t] < 0 marks a padding row, which has no raster counterpart.  map == nullptr: no re-layout.
+struct RasterMap {
+  const int32_t* map;
+  long long rows;   // S
+  int heads;        // H
+};
+__device__ __forceinline__ long long raster_row(const RasterMap& rm, long long bh, long long token) {
+  const int s = rm.map[token];
+  if (s < 0) return -1;
+  const int b = (int)bh / rm.heads;          // bh < 65536: a 32-bit division
+  return ((long long)b * rm.rows + s) * rm.heads + ((int)bh - b * rm.heads);
+}
+
 // Gated combine of eight 16-bit values: out = out_s + out_c * gate (gate optional) in fp32, one rounding -- the
 // arithmetic of the stand-alone combine pass, so fusing it into a kernel's store changes no bit.
 template <typename T>

@@ -1091,6 +1091,109 @@ int gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, i
   return check_launch("gather_rows_kernel");
 }
 
+// Row gather that also moves the head axis: raster-order activations [B][S][H][row] <-> tile-order operands
+// [B][H][L][row].  TO_TILED: dst (b, h, l) = src (b, map[l], h), zero where map[l] < 0 (the padding rows of a
+// clipped tile); otherwise dst (b, s, h) = src (b, h, map[s]).  One pass instead of a gather plus a transpose.
+template <bool TO_TILED>
+__global__ void __launch_bounds__(256) gather_rows_heads_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ map,
+                                                                uint4* __restrict__ dst, int heads, long long src_rows,
+                                                                long long dst_rows, int words_per_row, long long total_words) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_words;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row_all = i / words_per_row;
+    const int w = (int)(i - row_all * words_per_row);
+    long long b, r;
+    int h;
+    if (TO_TILED) {                       // destination [B][H][dst_rows]
+      const long long bh = row_all / dst_rows;
+      r = row_all - bh * dst_rows;
+      b = bh / heads;
+      h = (int)(bh - b * heads);
+    } else {                              // destination [B][dst_rows][H]
+      const long long bs = row_all / heads;
+      h = (int)(row_all - bs * heads);
+      b = bs / dst_rows;
+      r = bs - b * dst_rows;
+    }
+    const int m = map[r];
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (m >= 0)
+      val = TO_TILED ? src[((b * src_rows + m) * heads + h) * words_per_row + w]
+                     : src[((b * heads + h) * src_rows + m) * words_per_row + w];
+    dst[i] = val;
+  }
+}
+
+// The same move for rows of 2^k 16-byte words (k <= 8) and fewer than 2^31 rows per side, which is every case the
+// attention path produces.  A block owns 256 >> k consecutive DESTINATION tokens of one batch entry and walks the
+// heads in its inner loop, so that everything it touches within a few microseconds lies together in memory on both
+// sides: whole [H x row] token records on the raster side, runs of consecutive tile-order rows per head on the other
+// (a loop over independent rows leaves one side as scattered 256-byte pieces, which DRAM serves at half rate).
+template <bool TO_TILED>
+__global__ void __launch_bounds__(256) gather_rows_heads_pow2_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ map,
+                                                                     uint4* __restrict__ dst, unsigned heads, unsigned src_rows,
+                                                                     unsigned dst_rows, int log2_words, unsigned groups_per_batch,
+                                                                     unsigned total_groups) {
+  const unsigned rows_per_block = 256u >> log2_words;
+  const unsigned w = threadIdx.x & ((1u << log2_words) - 1u);
+  for (unsigned g = blockIdx.x; g < total_groups; g += gridDim.x) {
+    const unsigned b = g / groups_per_batch;
+    const unsigned r = (g - b * groups_per_batch) * rows_per_block + (threadIdx.x >> log2_words);
+    if (r >= dst_rows) continue;
+    const int m = map[r];
+#pragma unroll 4
+    for (unsigned h = 0; h < heads; ++h) {
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (m >= 0) {
+        const unsigned long long srow = TO_TILED ? ((unsigned long long)b * src_rows + (unsigned)m) * heads + h
+                                                 : ((unsigned long long)b * heads + h) * src_rows + (unsigned)m;
+        val = src[(srow << log2_words) + w];
+      }
+      const unsigned long long drow = TO_TILED ? ((unsigned long long)b * heads + h) * dst_rows + r
+                                               : ((unsigned long long)b * dst_rows + r) * heads + h;
+      dst[(drow << log2_words) + w] = val;
+    }
+  }
+}
+
+int gather_rows_heads(const void* src, const int32_t* map, void* dst, int64_t batch, int heads, int64_t src_rows,
+                      int64_t dst_rows, int64_t row_bytes, bool to_tiled, cudaStream_t st) {
+  if (batch == 0 || heads == 0 || dst_rows == 0 || row_bytes == 0) return VSA_OK;
+  if (row_bytes % 16 || reinterpret_cast<uintptr_t>(src) % 16 || reinterpret_cast<uintptr_t>(dst) % 16)
+    return fail(VSA_ERR_UNSUPPORTED, "gather rows (heads): rows must be multiples of 16 bytes and 16-byte aligned");
+  const long long wpr = row_bytes / 16;
+  const long long rows = batch * heads * dst_rows;
+  int log2_words = 0;
+  while ((1LL << log2_words) < wpr) ++log2_words;
+  if ((1LL << log2_words) == wpr && log2_words <= 8 && dst_rows < 0x7fffffffLL && src_rows < 0x7fffffffLL) {
+    const long long rows_per_block = 256 >> log2_words;
+    const long long groups_per_batch = (dst_rows + rows_per_block - 1) / rows_per_block;
+    const long long groups = batch * groups_per_batch;
+    if (groups < 0xffffffffLL) {
+      const unsigned blocks = (unsigned)(groups < 148LL * 64 ? groups : 148LL * 64);
+      if (to_tiled)
+        gather_rows_heads_pow2_kernel<true><<<blocks, 256, 0, st>>>((const uint4*)src, map, (uint4*)dst, (unsigned)heads,
+                                                                    (unsigned)src_rows, (unsigned)dst_rows, log2_words,
+                                                                    (unsigned)groups_per_batch, (unsigned)groups);
+      else
+        gather_rows_heads_pow2_kernel<false><<<blocks, 256, 0, st>>>((const uint4*)src, map, (uint4*)dst, (unsigned)heads,
+                                                                     (unsigned)src_rows, (unsigned)dst_rows, log2_words,
+                                                                     (unsigned)groups_per_batch, (unsigned)groups);
+      return check_launch("gather_rows_heads_pow2_kernel");
+    }
+  }
+  const long long total = rows * wpr;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (to_tiled)
+    gather_rows_heads_kernel<true><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)src, map, (uint4*)dst, heads, src_rows,
+                                                                     dst_rows, (int)wpr, total);
+  else
+    gather_rows_heads_kernel<false><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)src, map, (uint4*)dst, heads, src_rows,
+                                                                      dst_rows, (int)wpr, total);
+  return check_launch("gather_rows_heads_kernel");
+}
+
 // =========================================================================================
 // Scalar fine attention (any block volume, any head dim <= 256, bf16 or fp32): one warp
 // per query row (forward, dQ) or per key row (dK/dV).  Lane l holds dims l, l+32, ...

@@ -25,6 +25,9 @@ int route_invert_static(const int32_t* selected, int32_t* counts, int32_t* offse
                         int Qb, int Kb, int topk, cudaStream_t st);
 int gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, int64_t src_rows, int64_t dst_rows,
                 int64_t row_bytes, cudaStream_t st);
+// raster [B][S][H][row] <-> tile order [B][H][L][row] in one pass (to_tiled: dst rows = L, zero fill where map < 0)
+int gather_rows_heads(const void* src, const int32_t* map, void* dst, int64_t batch, int heads, int64_t src_rows,
+                      int64_t dst_rows, int64_t row_bytes, bool to_tiled, cudaStream_t st);
 int combine_fwd(const void* out_s, const void* out_c, const void* gate, void* out, int64_t BH, int64_t Lq, int D,
                 int be, int dtype, cudaStream_t st);
 int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,
@@ -50,7 +53,8 @@ bool sparse_tc_eligible(int D, int be, int dtype);
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
                   int dtype, bool redo_only, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
-                  void* out_comb = nullptr, int64_t kv_shard = 0);
+                  void* out_comb = nullptr, int64_t kv_shard = 0, const int32_t* comb_map = nullptr,
+                  int64_t comb_rows = 0, int comb_heads = 1);
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
                  const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
                  int64_t Lkv, int be, int topk, float scale, int dtype, cudaStream_t st);
@@ -64,17 +68,22 @@ bool sparse_umma_eligible(int D, int be, int dtype, int topk);
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
                     int dtype, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
-                    void* out_comb = nullptr, int64_t kv_shard = 0);   // kv_shard: tokens per shard of a shard-major K/V buffer (0 = ordinary layout)
+                    void* out_comb = nullptr, int64_t kv_shard = 0,   // kv_shard: tokens per shard of a shard-major K/V buffer (0 = ordinary layout)
+                    const int32_t* comb_map = nullptr, int64_t comb_rows = 0, int comb_heads = 1);
+// comb_map (optional, with out_comb): tile-order token -> raster row (or -1); gate is then read, and out_comb written, in
+// the raster layout [B, comb_rows, comb_heads, D] (BH = B * comb_heads) instead of tile order
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
                    int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, int dtype,
                    cudaStream_t st, const void* dq_mean = nullptr, const int32_t* q_sizes = nullptr,
-                   int64_t kv_shard = 0);
+                   int64_t kv_shard = 0, const int32_t* out_map = nullptr, int64_t out_rows = 0, int out_heads = 1);
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
                      float scale, int dtype, cudaStream_t st, const void* dk_mean = nullptr,
-                     const void* dv_mean = nullptr, void* ds_ws = nullptr, int64_t kv_shard = 0);
+                     const void* dv_mean = nullptr, void* ds_ws = nullptr, int64_t kv_shard = 0,
+                     const int32_t* out_map = nullptr, int64_t out_rows = 0, int out_heads = 1);
+// out_map (optional): dq (dk, dv) rows are written at the token's raster row of a [B, out_rows, out_heads, D] tensor
 // the backward that forms dS once: the key-owned pass (above, with ds_ws and packed edges) stores it, this
 // query-owned pass multiplies it by K
 int64_t sparse_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk);

@@ -77,7 +77,9 @@ __device__ __forceinline__ void store_warp_rows(uint8_t* tile, uint32_t tile_u32
                                                 float mul1, T* __restrict__ g, int warp, int lane,
                                                 const T* __restrict__ pooled_row = nullptr,
                                                 const T* __restrict__ gate_g = nullptr,
-                                                T* __restrict__ comb = nullptr) {
+                                                T* __restrict__ comb = nullptr, long long comb_row0 = 0,
+                                                RasterMap comb_map = RasterMap{nullptr, 0, 1}, long long bh = 0,
+                                                long long token0 = 0) {
   const int gq = lane >> 2, t = lane & 3;
   const int r0 = warp * 16 + gq, r1 = r0 + 8;
 #pragma unroll
@@ -92,11 +94,14 @@ __device__ __forceinline__ void store_warp_rows(uint8_t* tile, uint32_t tile_u32
     const int row = warp * 16 + (c >> 4), ch = c & 15;
     const uint4 val = *reinterpret_cast<const uint4*>(tile + tile_off(row, ch));
     *reinterpret_cast<uint4*>(g + row * kD + ch * 8) = val;
-    if (comb != nullptr) {
+    if (comb != nullptr) {   // gate and comb are whole-tensor pointers: tile order (comb_row0 + row) or raster rows
       const uint4 cv = *reinterpret_cast<const uint4*>(pooled_row + ch * 8);
       uint4 gv = make_uint4(0, 0, 0, 0);
-      if (gate_g != nullptr) gv = *reinterpret_cast<const uint4*>(gate_g + row * kD + ch * 8);
-      *reinterpret_cast<uint4*>(comb + row * kD + ch * 8) = combine_x8<T>(val, cv, gv, gate_g != nullptr);
+      const long long crow = comb_map.map == nullptr ? comb_row0 + row : raster_row(comb_map, bh, token0 + row);
+      if (crow >= 0) {
+        if (gate_g != nullptr) gv = *reinterpret_cast<const uint4*>(gate_g + crow * kD + ch * 8);
+        *reinterpret_cast<uint4*>(comb + crow * kD + ch * 8) = combine_x8<T>(val, cv, gv, gate_g != nullptr);
+      }
     }
   }
   (void)tile_u32;
@@ -111,7 +116,7 @@ sparse_fwd_mma_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
                       T* __restrict__ out, float* __restrict__ lse2, const T* __restrict__ out_c,
                       const T* __restrict__ gate, T* __restrict__ out_comb, long long Lq, long long Lkv,
-                      long long kv_shard, int topk, float scale, int redo_only) {
+                      long long kv_shard, int topk, float scale, int redo_only, RasterMap comb_map) {
   extern __shared__ __align__(128) uint8_t smem[];
   if (redo_only) {   // only tiles the tcgen05 forward marked with a NaN statistic are recomputed
     const float mark = lse2[(long long)blockIdx.y * Lq + (long long)blockIdx.x * kTile];
@@ -261,8 +266,8 @@ sparse_fwd_mma_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   const long long row0 = bh * Lq + (long long)qtile * kTile;
   T* og = out + row0 * kD;
   if (out_comb != nullptr)
-    store_warp_rows(smem, sQ, o, inv[0], inv[1], og, warp, lane, out_c + (bh * Qb + qb) * (long long)kD,
-                    gate != nullptr ? gate + row0 * kD : nullptr, out_comb + row0 * kD);
+    store_warp_rows(smem, sQ, o, inv[0], inv[1], og, warp, lane, out_c + (bh * Qb + qb) * (long long)kD, gate, out_comb, row0,
+                    comb_map, bh, (long long)qtile * kTile);
   else
     store_warp_rows(smem, sQ, o, inv[0], inv[1], og, warp, lane);
   if (lse2 && t == 0) {
@@ -581,14 +586,15 @@ bool sparse_tc_eligible(int D, int be, int dtype) { return (dtype == VSA_BF16 ||
 template <typename T>
 static int launch_fwd(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                       void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                      bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard) {
+                      bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard,
+                      RasterMap comb_map) {
   dim3 grid((unsigned)(Lq / kTile), (unsigned)BH);
   auto launch = [&](auto kern) -> int {
     const int rc = set_smem(kern, kFwdSmem, "sparse forward");
     if (rc) return rc;
     kern<<<grid, kThreads, kFwdSmem, st>>>((const T*)q, (const T*)k, (const T*)v, selected, kv_sizes, (T*)out, lse2,
                                            (const T*)out_c, (const T*)gate, (T*)out_comb, Lq, Lkv, kv_shard, topk, scale,
-                                           redo_only ? 1 : 0);
+                                           redo_only ? 1 : 0, comb_map);
     return check_launch("sparse_fwd_mma_kernel");
   };
   return be == 64 ? launch(sparse_fwd_mma_kernel<T, 1>) : be == 128 ? launch(sparse_fwd_mma_kernel<T, 2>) : launch(sparse_fwd_mma_kernel<T, 4>);
@@ -628,15 +634,16 @@ static int launch_dkdv(const void* dout, const void* q, const void* k, const voi
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                   void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
                   int dtype, bool redo_only, cudaStream_t st, const void* out_c, const void* gate, void* out_comb,
-                  int64_t kv_shard) {
+                  int64_t kv_shard, const int32_t* comb_map, int64_t comb_rows, int comb_heads) {
+  const RasterMap rm{comb_map, (long long)comb_rows, comb_heads > 0 ? comb_heads : 1};
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (kv_shard <= 0) kv_shard = Lkv;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
   if (dtype == VSA_F16)
     return launch_fwd<__half>(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, redo_only, st, out_c,
-                              gate, out_comb, kv_shard);
+                              gate, out_comb, kv_shard, rm);
   return launch_fwd<__nv_bfloat16>(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, redo_only, st,
-                                   out_c, gate, out_comb, kv_shard);
+                                   out_c, gate, out_comb, kv_shard, rm);
 }
 
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,

@@ -279,26 +279,31 @@ int64_t sparse_ds_workspace_bytes(int64_t BH, int64_t Lq, int be, int topk) {
 
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                    int dtype, cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard) {
+                    int dtype, cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard,
+                    const int32_t* comb_map, int64_t comb_rows, int comb_heads) {
+  const RasterMap rm{comb_map, (long long)comb_rows, comb_heads > 0 ? comb_heads : 1};
   return VSA_BY_DTYPE(dtype, sparse_fwd_umma(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, st,
-                                             out_c, gate, out_comb, kv_shard));
+                                             out_c, gate, out_comb, kv_shard, rm));
 }
 
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
                    int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, int dtype, cudaStream_t st,
-                   const void* dq_mean, const int32_t* q_sizes, int64_t kv_shard) {
+                   const void* dq_mean, const int32_t* q_sizes, int64_t kv_shard, const int32_t* out_map,
+                   int64_t out_rows, int out_heads) {
+  const RasterMap rm{out_map, (long long)out_rows, out_heads > 0 ? out_heads : 1};
   return VSA_BY_DTYPE(dtype, sparse_dq_umma(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be,
-                                            topk, scale, st, dq_mean, q_sizes, kv_shard));
+                                            topk, scale, st, dq_mean, q_sizes, kv_shard, rm));
 }
 
 int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
                      float scale, int dtype, cudaStream_t st, const void* dk_mean, const void* dv_mean, void* ds_ws,
-                     int64_t kv_shard) {
+                     int64_t kv_shard, const int32_t* out_map, int64_t out_rows, int out_heads) {
+  const RasterMap rm{out_map, (long long)out_rows, out_heads > 0 ? out_heads : 1};
   return VSA_BY_DTYPE(dtype, sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH,
-                                              Lq, Lkv, be, topk, scale, st, dk_mean, dv_mean, ds_ws, kv_shard));
+                                              Lq, Lkv, be, topk, scale, st, dk_mean, dv_mean, ds_ws, kv_shard, rm));
 }
 
 int sparse_dq_from_ds_umma(const void* k, const int32_t* selected, const int32_t* kv_sizes, const void* ds_ws, void* dq,

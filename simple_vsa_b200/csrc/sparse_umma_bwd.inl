@@ -64,7 +64,7 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const int32_t* __restrict__ selected, const int32_t* __restrict__ kv_sizes,
                       float* __restrict__ delta, elem_t* __restrict__ dq, const elem_t* __restrict__ mean_grad,
                       const int32_t* __restrict__ q_sizes, long long Lq, long long Lkv, long long kv_shard, int topk,
-                      float scale) {
+                      float scale, RasterMap out_map) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -340,12 +340,14 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int j = 0; j < kBwCols; ++j) stage[(c0 + j) * kD + t] = Elem<elem_t>::from((c0 + j) < rows_live ? gm : 0.f);
     }
     named_barrier(1, kBwEwThreads);
-    elem_t* og = dq + qrow0 * kD;
 #pragma unroll
     for (int i = 0; i < 1024 / kBwEwThreads; ++i) {
       const int cidx = st + kBwEwThreads * i;
       const int row = cidx >> 4, ch = cidx & 15;
-      *reinterpret_cast<uint4*>(og + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
+      // with a raster map the gradient row goes straight to the token's raster row (padding rows have none)
+      const long long drow = out_map.map == nullptr ? qrow0 + row : raster_row(out_map, bh, (long long)qtile * kTile + row);
+      if (drow >= 0)
+        *reinterpret_cast<uint4*>(dq + drow * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage + row * kD + ch * 8);
     }
   }
   tc_fence_before();
@@ -397,7 +399,7 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int32_t* __restrict__ inverse, const int32_t* __restrict__ kv_sizes,
                         elem_t* __restrict__ dk, elem_t* __restrict__ dv, const elem_t* __restrict__ mean_grad_k,
                         const elem_t* __restrict__ mean_grad_v, elem_t* __restrict__ ds_ws, long long Lq, long long Lkv,
-                        long long kv_shard, int topk, float scale) {
+                        long long kv_shard, int topk, float scale, RasterMap out_map) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -422,9 +424,9 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const float mean_inv = 1.f / (float)(kv_sizes[kvb] > 1 ? kv_sizes[kvb] : 1);
   const long long mean_off = (bh * Kb + kvb) * (long long)kD;
   if (n_pairs == 0) {   // nobody selected this tile, or it is all padding: no fine gradient, no pipeline
-    uint4* gk = reinterpret_cast<uint4*>(dk + krow0 * kD);
-    uint4* gv = reinterpret_cast<uint4*>(dv + krow0 * kD);
     for (int i = tid; i < 1024; i += (int)blockDim.x) {
+      const long long drow = out_map.map == nullptr ? krow0 + (i >> 4) : raster_row(out_map, bh, (long long)ktile * kTile + (i >> 4));
+      if (drow < 0) continue;
       uint4 ok4 = make_uint4(0, 0, 0, 0), ov4 = make_uint4(0, 0, 0, 0);
       if (mean_grad_k != nullptr && (i >> 4) < valid) {     // 16 chunks of eight dims per row
         elem_t* ek = reinterpret_cast<elem_t*>(&ok4);
@@ -435,8 +437,8 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           ev[e] = Elem<elem_t>::from(Elem<elem_t>::to(mean_grad_v[mean_off + (i & 15) * 8 + e]) * mean_inv);
         }
       }
-      gk[i] = ok4;
-      gv[i] = ov4;
+      *reinterpret_cast<uint4*>(dk + drow * kD + (i & 15) * 8) = ok4;
+      *reinterpret_cast<uint4*>(dv + drow * kD + (i & 15) * 8) = ov4;
     }
     return;
   }
@@ -700,14 +702,15 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
     }
     named_barrier(1, kBwEwThreads);
-    elem_t* gk = dk + krow0 * kD;
-    elem_t* gv = dv + krow0 * kD;
 #pragma unroll
     for (int i = 0; i < 1024 / kBwEwThreads; ++i) {
       const int cidx = st + kBwEwThreads * i;
       const int row = cidx >> 4, ch = cidx & 15;
-      *reinterpret_cast<uint4*>(gk + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_k + row * kD + ch * 8);
-      *reinterpret_cast<uint4*>(gv + row * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_v + row * kD + ch * 8);
+      const long long drow = out_map.map == nullptr ? krow0 + row : raster_row(out_map, bh, (long long)ktile * kTile + row);
+      if (drow >= 0) {
+        *reinterpret_cast<uint4*>(dk + drow * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_k + row * kD + ch * 8);
+        *reinterpret_cast<uint4*>(dv + drow * kD + ch * 8) = *reinterpret_cast<const uint4*>(stage_v + row * kD + ch * 8);
+      }
     }
   }
   tc_fence_before();

@@ -41,7 +41,7 @@ sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, con
                                   const int32_t* __restrict__ kv_sizes, elem_t* __restrict__ out,
                                   float* __restrict__ lse2, const elem_t* __restrict__ out_c,
                                   const elem_t* __restrict__ gate, elem_t* __restrict__ out_comb, long long BH, long long Lq,
-                                  long long Lkv, long long kv_shard, int topk, float scale) {
+                                  long long Lkv, long long kv_shard, int topk, float scale, RasterMap comb_map) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;   // an earlier wait ran out: drain without touching anything
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -369,8 +369,12 @@ sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, con
         if (out_comb != nullptr) {   // gated combine with the pooled branch on the way out (the fine output is kept: delta needs it)
           const uint4 cv = *reinterpret_cast<const uint4*>(out_c + (bh * Qb + qb) * (long long)kD + ch * 8);
           uint4 gv = make_uint4(0, 0, 0, 0);
-          if (gate != nullptr) gv = *reinterpret_cast<const uint4*>(gate + (row0 + row) * kD + ch * 8);
-          *reinterpret_cast<uint4*>(out_comb + (row0 + row) * kD + ch * 8) = combine_x8<elem_t>(sv4, cv, gv, gate != nullptr);
+          // with a raster map the gate is read, and the combined output written, at the token's raster row
+          const long long crow = comb_map.map == nullptr ? row0 + row : raster_row(comb_map, bh, (long long)qtile * kTile + row);
+          if (crow >= 0) {
+            if (gate != nullptr) gv = *reinterpret_cast<const uint4*>(gate + crow * kD + ch * 8);
+            *reinterpret_cast<uint4*>(out_comb + crow * kD + ch * 8) = combine_x8<elem_t>(sv4, cv, gv, gate != nullptr);
+          }
         }
       }
       if (st < 64) {

@@ -65,7 +65,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const int32_t* __restrict__ selected,
                        const int32_t* __restrict__ kv_sizes, elem_t* __restrict__ out, float* __restrict__ lse2,
                        const elem_t* __restrict__ out_c, const elem_t* __restrict__ gate, elem_t* __restrict__ out_comb,
-                       long long Lq, long long Lkv, long long kv_shard, int topk, float scale) {
+                       long long Lq, long long Lkv, long long kv_shard, int topk, float scale, RasterMap comb_map) {
   extern __shared__ uint8_t smem_raw[];
   if (*(volatile int*)&g_device_status != 0) return;   // an earlier wait ran out: drain without touching anything
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -339,8 +339,12 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (out_comb != nullptr) {   // gated combine with the pooled branch on the way out (the fine output is kept: delta needs it)
         const uint4 cv = *reinterpret_cast<const uint4*>(out_c + (bh * Qb + qb) * (long long)kD + ch * 8);
         uint4 gv = make_uint4(0, 0, 0, 0);
-        if (gate != nullptr) gv = *reinterpret_cast<const uint4*>(gate + (row0 + row) * kD + ch * 8);
-        *reinterpret_cast<uint4*>(out_comb + (row0 + row) * kD + ch * 8) = combine_x8<elem_t>(sv, cv, gv, gate != nullptr);
+        // with a raster map the gate is read, and the combined output written, at the token's raster row
+        const long long crow = comb_map.map == nullptr ? row0 + row : raster_row(comb_map, bh, (long long)qtile * kTile + row);
+        if (crow >= 0) {
+          if (gate != nullptr) gv = *reinterpret_cast<const uint4*>(gate + crow * kD + ch * 8);
+          *reinterpret_cast<uint4*>(out_comb + crow * kD + ch * 8) = combine_x8<elem_t>(sv, cv, gv, gate != nullptr);
+        }
       }
     }
     if (st < 64) {
@@ -360,7 +364,8 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // ---- host launchers of this element type ----------------------------------------------------------------------
 int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                     void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
-                    cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard) {
+                    cudaStream_t st, const void* out_c, const void* gate, void* out_comb, int64_t kv_shard,
+                    RasterMap comb_map) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   { const int rc0 = check_kv_shard(Lkv, be, &kv_shard, "sparse forward"); if (rc0) return rc0; }
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse forward: batch*heads %lld exceeds 65535", (long long)BH);
@@ -388,7 +393,8 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
     auto launch = [&](auto kern) -> int {
       if ((rc = reserve_smem(kern, psmem, "sparse forward"))) return rc;
       kern<<<ctas, kFwdPThreads, psmem, st>>>(mq, mk, mv, selected, kv_sizes, (elem_t*)out, lse2, (const elem_t*)out_c,
-                                              (const elem_t*)gate, (elem_t*)out_comb, (long long)BH, Lq, Lkv, kv_shard, topk, scale);
+                                              (const elem_t*)gate, (elem_t*)out_comb, (long long)BH, Lq, Lkv, kv_shard, topk, scale,
+                                              comb_map);
       return check_launch("sparse_fwd_umma_persistent_kernel");
     };
     VSA_BY_BLOCK_VOLUME(be, launch, sparse_fwd_umma_persistent_kernel);
@@ -398,7 +404,7 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
   auto launch = [&](auto kern) -> int {
     if ((rc = reserve_smem(kern, smem, "sparse forward"))) return rc;
     kern<<<grid, kFwdThreads, smem, st>>>(mq, mk, mv, selected, kv_sizes, (elem_t*)out, lse2, (const elem_t*)out_c,
-                                          (const elem_t*)gate, (elem_t*)out_comb, Lq, Lkv, kv_shard, topk, scale);
+                                          (const elem_t*)gate, (elem_t*)out_comb, Lq, Lkv, kv_shard, topk, scale, comb_map);
     return check_launch("sparse_fwd_umma_kernel");
   };
   VSA_BY_BLOCK_VOLUME(be, launch, sparse_fwd_umma_kernel);
@@ -407,7 +413,7 @@ int sparse_fwd_umma(const void* q, const void* k, const void* v, const int32_t* 
 int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v, const void* out_s,
                    const float* lse2, const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq,
                    int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale, cudaStream_t st,
-                   const void* dq_mean, const int32_t* q_sizes, int64_t kv_shard) {
+                   const void* dq_mean, const int32_t* q_sizes, int64_t kv_shard, RasterMap out_map) {
   if (BH == 0 || Lq == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dQ: batch*heads %lld exceeds 65535", (long long)BH);
   { const int rc0 = check_kv_shard(Lkv, be, &kv_shard, "sparse dQ"); if (rc0) return rc0; }
@@ -422,7 +428,8 @@ int sparse_dq_umma(const void* dout, const void* q, const void* k, const void* v
   auto launch = [&](auto kern) -> int {
     if ((rc = reserve_smem(kern, smem, "sparse dQ"))) return rc;
     kern<<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, (const elem_t*)dout, (const elem_t*)out_s, lse2, selected, kv_sizes,
-                                          delta, (elem_t*)dq, (const elem_t*)dq_mean, q_sizes, Lq, Lkv, kv_shard, topk, scale);
+                                          delta, (elem_t*)dq, (const elem_t*)dq_mean, q_sizes, Lq, Lkv, kv_shard, topk, scale,
+                                          out_map);
     return check_launch("sparse_dq_umma_kernel");
   };
   VSA_BY_BLOCK_VOLUME(be, launch, sparse_dq_umma_kernel);
@@ -432,7 +439,7 @@ int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void*
                      const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
                      const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
                      float scale, cudaStream_t st, const void* dk_mean, const void* dv_mean, void* ds_ws,
-                     int64_t kv_shard) {
+                     int64_t kv_shard, RasterMap out_map) {
   if (BH == 0 || Lkv == 0) return VSA_OK;
   if (BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "sparse dK/dV: batch*heads %lld exceeds 65535", (long long)BH);
   { const int rc0 = check_kv_shard(Lkv, be, &kv_shard, "sparse dK/dV"); if (rc0) return rc0; }
@@ -452,7 +459,7 @@ int sparse_dkdv_umma(const void* dout, const void* q, const void* k, const void*
     if ((rc = reserve_smem(kern, smem, "sparse dK/dV"))) return rc;
     kern<<<grid, kBwdThreads, smem, st>>>(mq, mdo, mk, mv, lse2, delta, counts, offsets, inverse, kv_sizes, (elem_t*)dk,
                                           (elem_t*)dv, (const elem_t*)dk_mean, (const elem_t*)dv_mean, (elem_t*)ds_ws, Lq, Lkv,
-                                          kv_shard, topk, scale);
+                                          kv_shard, topk, scale, out_map);
     return check_launch("sparse_dkdv_umma_kernel");
   };
   if (be == 64) return ds_ws ? launch(sparse_dkdv_umma_kernel<1, true>) : launch(sparse_dkdv_umma_kernel<1, false>);

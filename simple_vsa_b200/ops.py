@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import math
 import os
+import warnings
 from typing import Optional, Sequence, Tuple, Union
 
 import torch
@@ -72,6 +73,24 @@ def _check_device_dtype(q: Tensor, k: Tensor, v: Tensor) -> int:
     if q.dtype == torch.float16:
         return _lib.VSA_F16
     raise ValueError("the B200 path supports bfloat16, float16 and float32")
+
+
+_warned_slow_path = False
+
+
+def _warn_if_far_off_the_tensor_path(dt: int, B: int, H: int, Lq: int, D: int, be: int, topk: int) -> None:
+    """One warning per process when a large problem lands on the CUDA-core kernels.  They exist as the validation
+    mode (fp32) and for shapes the reference accepts but its benchmarks never use; per FLOP they are two to three
+    orders of magnitude slower than the tcgen05 kernels, which a caller should learn from more than a slow step."""
+    global _warned_slow_path
+    if _warned_slow_path or 14.0 * B * H * Lq * topk * be * D < 1e11:
+        return
+    if _lib.lib.vsa_sparse_sharded_supported(D, be, topk, dt):      # the tensor path's own eligibility answer
+        return
+    _warned_slow_path = True
+    warnings.warn("simple_vsa_b200: this shape runs on the CUDA-core validation kernels (the tensor-core path needs "
+                  "bf16 or fp16, head dim 128, block volume 64, 128 or 256, topk*ceil(block/64) <= 1024, and "
+                  "VSA_B200_KERNELS unset); expect a step hundreds of times slower per FLOP", RuntimeWarning, stacklevel=3)
 
 
 def _dense(x: Tensor) -> Tensor:
@@ -272,7 +291,7 @@ def sparse_attention(q, k, v, selected, variable_block_sizes, *, block_size: Blo
                      sm_scale: Optional[float] = None) -> Tensor:
     """Fine attention on caller-supplied routes ``selected [B,H,Qb,topk]`` (``vsa/triton_impl.py:1583-1652``)."""
     be = as_block_elements(block_size)
-    _check_device_dtype(q, k, v)
+    dt = _check_device_dtype(q, k, v)
     if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
         raise ValueError("q, k, and v must have shape [batch, heads, seq_len, dim]")
     B, H, Lq, D = q.shape
@@ -289,6 +308,7 @@ def sparse_attention(q, k, v, selected, variable_block_sizes, *, block_size: Blo
             f"variable_block_sizes must have {Lkv // be} entries, got {variable_block_sizes.numel()}")
     scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(D)
     with torch.cuda.device(q.device):
+        _warn_if_far_off_the_tensor_path(dt, B, H, Lq, D, be, tk)
         q, k, v = _dense(q), _dense(k), _dense(v)
         selected = selected.to(device=q.device, dtype=torch.int32).contiguous()
         sizes = _sizes(variable_block_sizes, q.device)
@@ -485,12 +505,13 @@ def vsa_forward_full(q, k, v, variable_block_sizes, q_variable_block_sizes, topk
     validate_vsa_inputs(q, k, v, variable_block_sizes, q_variable_block_sizes, topk, be)
     if compress_attn_weight is not None and compress_attn_weight.shape != q.shape:
         raise ValueError("compress_attn_weight must have the same shape as q")
-    _check_device_dtype(q, k, v)
+    dt = _check_device_dtype(q, k, v)
     gate = compress_attn_weight
     if gate is not None and (gate.device != q.device or gate.dtype != q.dtype):
         gate = gate.to(device=q.device, dtype=q.dtype)
     scale = float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(q.shape[-1])
     with torch.cuda.device(q.device):
+        _warn_if_far_off_the_tensor_path(dt, q.shape[0], q.shape[1], q.shape[2], q.shape[3], be, int(topk))
         q, k, v = _dense(q), _dense(k), _dense(v)
         gate = _dense(gate) if gate is not None else None
         kv_sizes = _sizes(variable_block_sizes, q.device)

@@ -608,6 +608,35 @@ def test_compression_gate_trains_through_the_operator():
     _assert_close(grad, layer_c.to_gate_compress.weight.grad, atol=1e-5, rtol=1e-4)
 
 
+def test_a_large_problem_off_the_tensor_path_warns_once():
+    """Head dim 64 is served by the CUDA-core kernels only; a problem of 1e11 useful FLOPs or more says so once per
+    process, a tensor-path shape and small validation-size problems never do."""
+    import warnings
+
+    from simple_vsa_b200 import ops
+    V = _V()
+    torch.manual_seed(7)
+    be, tk = 64, 32
+    sizes = torch.full((256,), be)
+    small = [torch.randn(1, 1, 4 * be, 64, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    big64 = [torch.randn(1, 4, 256 * be, 64, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    big128 = [torch.randn(1, 2, 256 * be, 128, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    ops._warned_slow_path = False
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        with torch.no_grad():
+            V.video_sparse_attn(*small, sizes[:4], sizes[:4], 2, (4, 4, 4))
+            V.video_sparse_attn(*big128, sizes, sizes, tk, (4, 4, 4))
+    with pytest.warns(RuntimeWarning, match="CUDA-core validation kernels"), torch.no_grad():
+        out = V.video_sparse_attn(*big64, sizes, sizes, tk, (4, 4, 4))
+    assert torch.isfinite(out.float()).all()
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")                      # the second large call stays quiet
+        with torch.no_grad():
+            V.video_sparse_attn(*big64, sizes, sizes, tk, (4, 4, 4))
+    ops._warned_slow_path = False
+
+
 def test_compression_gate_writes_the_operator_layout_without_a_transposing_copy():
     """bf16, 4 heads of 128: the gate comes out dense in [B,H,S,D] (the operator's ``_dense`` then copies nothing),
     equals the reference form Linear(x).view(B,S,H,D).transpose(1,2) up to one bf16 rounding of the same fp32 sums,

@@ -127,3 +127,85 @@ def test_gradient_flows_through_tile_and_untile(path):
     pad = torch.ones(w.shape[1], dtype=torch.bool, device="cuda:0")
     pad[npi] = False
     assert float(t.grad[:, pad].abs().sum()) == 0.0 and float(t.grad[:, ~pad].min()) == 1.0
+
+
+# ---------------------------------------------------------------------------------------------
+# the operator on raster-order [B,S,H,D] tensors (layout moves folded into the kernels' stores)
+# ---------------------------------------------------------------------------------------------
+def _two_step(V, meta, q, k, v, gate, topk, tile_size):
+    """tile -> transpose -> operator -> transpose -> untile, the form a DiT layer writes around the operator."""
+    to_tiles = lambda x: V.tile_with(meta, x).transpose(1, 2).contiguous()
+    sizes = meta["variable_block_sizes"]
+    out_t = V.b200_vsa(to_tiles(q), to_tiles(k), to_tiles(v), sizes, sizes, topk, tile_size,
+                       to_tiles(gate) if gate is not None else None)
+    return V.untile_with(meta, out_t.transpose(1, 2).contiguous())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("grid,tile_size,dtype", [((6, 10, 9), (4, 4, 4), torch.bfloat16),
+                                                  ((8, 8, 8), (4, 4, 4), torch.float16),
+                                                  ((5, 16, 12), (4, 8, 8), torch.bfloat16),
+                                                  ((4, 9, 16), (2, 8, 8), torch.bfloat16)])
+@pytest.mark.parametrize("with_gate", [False, True])
+def test_raster_order_operator_equals_the_two_step_form(grid, tile_size, dtype, with_gate):
+    """Clipped tiles on every axis, full tiles, blocks of 64 / 128 / 256 tokens: out, dq and dgate bit for bit (same
+    kernels, same arithmetic, other store addresses); dk/dv up to the order of the fp32 sums over CSR rows."""
+    import simple_vsa_b200 as V
+    dev = "cuda:0"
+    torch.manual_seed(11)
+    B, H, D, topk = 2, 3, 128, 3
+    S = grid[0] * grid[1] * grid[2]
+    meta = V.build_vsa_metadata(grid, tile_size, device=dev)
+    make = lambda: torch.randn(B, S, H, D, device=dev).to(dtype)
+    q, k, v, dout = make(), make(), make(), make()
+    gate = make() if with_gate else None
+    a = [t.clone().requires_grad_() for t in (q, k, v)] + ([gate.clone().requires_grad_()] if with_gate else [])
+    b = [t.clone().requires_grad_() for t in (q, k, v)] + ([gate.clone().requires_grad_()] if with_gate else [])
+    out_a = V.video_sparse_attn_raster(a[0], a[1], a[2], meta, topk, a[3] if with_gate else None)
+    out_b = _two_step(V, meta, b[0], b[1], b[2], b[3] if with_gate else None, topk, tile_size)
+    assert out_a.shape == (B, S, H, D) and torch.isfinite(out_a.float()).all()
+    assert torch.equal(out_a, out_b)
+    out_a.backward(dout)
+    out_b.backward(dout)
+    assert torch.equal(a[0].grad, b[0].grad)
+    if with_gate:
+        assert torch.equal(a[3].grad, b[3].grad)
+    for x, y in zip(a[1:3], b[1:3]):
+        torch.testing.assert_close(x.grad.float(), y.grad.float(), atol=2e-2, rtol=2e-2)
+    with torch.no_grad():                                    # the inference path (nothing saved) gives the same bits
+        assert torch.equal(V.video_sparse_attn_raster(q, k, v, meta, topk, gate), out_a)
+
+
+@pytest.mark.gpu
+def test_raster_order_operator_other_shapes_take_the_two_step_form():
+    """Head dim 64 is off the tensor path: the raster-order entry point still answers, through separate layout passes."""
+    import simple_vsa_b200 as V
+    dev = "cuda:0"
+    torch.manual_seed(12)
+    grid, tile_size, B, H, D, topk = (5, 6, 7), (4, 4, 4), 1, 2, 64, 2
+    S = grid[0] * grid[1] * grid[2]
+    meta = V.build_vsa_metadata(grid, tile_size, device=dev)
+    q, k, v = (torch.randn(B, S, H, D, device=dev).to(torch.bfloat16).requires_grad_() for _ in range(3))
+    out = V.video_sparse_attn_raster(q, k, v, meta, topk)
+    ref = _two_step(V, meta, q.detach(), k.detach(), v.detach(), None, topk, tile_size)
+    assert torch.equal(out, ref)
+    out.float().square().mean().backward()
+    assert all(t.grad is not None and torch.isfinite(t.grad.float()).all() for t in (q, k, v))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [8, 24, 128])          # rows of 1, 3 (not a power of two: the general kernel) and 16 words
+def test_tile_heads_is_tile_plus_transpose_in_one_pass(D):
+    import simple_vsa_b200 as V
+    dev = "cuda:0"
+    torch.manual_seed(13)
+    grid = (3, 5, 6)
+    meta = V.build_vsa_metadata(grid, (2, 2, 4), device=dev)
+    x = torch.randn(2, 90, 3, D, device=dev).to(torch.bfloat16).requires_grad_()
+    got = V.tile_heads(x, meta)
+    want = V.tile_with(meta, x.detach()).transpose(1, 2)
+    assert got.is_contiguous() and torch.equal(got, want)
+    assert torch.equal(V.untile_heads(got, meta), x)
+    w = torch.randn_like(got)
+    (got.float() * w.float()).sum().backward()
+    assert torch.equal(x.grad, V.untile_heads(w, meta))
