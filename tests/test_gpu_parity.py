@@ -926,3 +926,42 @@ def test_random_shapes_tensor_path_matches_cuda_core_path(seed, monkeypatch):
     if bool(finite.all()):
         for x, y in zip(a[2:], b[2:]):
             _assert_close(x, y, atol=3e-2, rtol=3e-2)
+
+
+def test_whole_step_replays_from_a_cuda_graph():
+    """Forward + backward of the operator captured once into a CUDA graph and replayed on new numbers in the same
+    buffers: no launch of the path synchronises, allocates outside torch's capturable pool, or keeps host-side state
+    that a replay would miss.  The replay must give what an eager call gives on the same inputs."""
+    V = _V()
+    torch.manual_seed(301)
+    B, H, L, D, be, tk = 1, 4, 4096, 128, 64, 8
+    sizes = torch.full((L // be,), be, dtype=torch.int32, device=DEV)
+    sizes[5], sizes[-1] = 33, 1
+    static = [torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16).requires_grad_() for _ in range(4)]   # q, k, v, gate
+    dout = torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16)
+
+    def step():
+        out = V.b200_vsa(static[0], static[1], static[2], sizes, sizes, tk, (4, 4, 4), static[3])
+        grads = torch.autograd.grad(out, static, dout)
+        return (out,) + grads
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):                      # warm-up outside the capture: attributes, tensor maps, allocator
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = step()
+    fresh = [torch.randn(B, H, L, D, device=DEV).to(torch.bfloat16) for _ in range(4)]
+    with torch.no_grad():
+        for s, f in zip(static, fresh):
+            s.copy_(f)
+    graph.replay()
+    torch.cuda.synchronize()
+    got = [t.clone() for t in captured]
+    want = step()
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]) and torch.equal(got[4], want[4])   # out, dq, dgate
+    for g, w in zip(got[2:4], want[2:4]):                                                                 # dk, dv: CSR row order
+        _assert_close(g, w, atol=2e-2, rtol=2e-2)
