@@ -107,6 +107,12 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     fence_barrier_init();
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
+    // Q and dO of this tile depend on nothing the prologue computes: their loads fly under the tile-list build and delta
+    mbar_arrive_expect_tx(bar(DQ_QDO_FULL), 4 * kSlab);
+    tma_load_2d(base + DqSmem::q, &map_q, 0, (int)qrow0, bar(DQ_QDO_FULL));
+    tma_load_2d(base + DqSmem::q + kSlab, &map_q, 64, (int)qrow0, bar(DQ_QDO_FULL));
+    tma_load_2d(base + DqSmem::d_o, &map_do, 0, (int)qrow0, bar(DQ_QDO_FULL));
+    tma_load_2d(base + DqSmem::d_o + kSlab, &map_do, 64, (int)qrow0, bar(DQ_QDO_FULL));
   }
   for (int it = tid; it < n_iter; it += kBwdThreads) {
     const int kvb = sel[it / SUB];
@@ -173,13 +179,6 @@ sparse_dq_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   if (warp == 0 || warp == 1) {
     const bool is_k = warp == 0;
-    if (is_k && lane == 0) {
-      mbar_arrive_expect_tx(bar(DQ_QDO_FULL), 4 * kSlab);
-      tma_load_2d(base + DqSmem::q, &map_q, 0, (int)qrow0, bar(DQ_QDO_FULL));
-      tma_load_2d(base + DqSmem::q + kSlab, &map_q, 64, (int)qrow0, bar(DQ_QDO_FULL));
-      tma_load_2d(base + DqSmem::d_o, &map_do, 0, (int)qrow0, bar(DQ_QDO_FULL));
-      tma_load_2d(base + DqSmem::d_o + kSlab, &map_do, 64, (int)qrow0, bar(DQ_QDO_FULL));
-    }
     const int which = lane & 1, dhalf = (lane >> 1) & 1;
     const CUtensorMap* map = is_k ? &map_k : &map_v;
     const int full0 = is_k ? DQ_K_FULL : DQ_V_FULL, empty0 = is_k ? DQ_K_EMPTY : DQ_V_EMPTY;
@@ -479,6 +478,12 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     fence_barrier_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_do);
+    // the tile's own K and V, resident for the whole CTA: in flight before anything else
+    mbar_arrive_expect_tx(bar(DK_KV_FULL), 4 * kSlab);
+    tma_load_2d(base + DkSmem::k, &map_k, 0, (int)krow0, bar(DK_KV_FULL));
+    tma_load_2d(base + DkSmem::k + kSlab, &map_k, 64, (int)krow0, bar(DK_KV_FULL));
+    tma_load_2d(base + DkSmem::v, &map_v, 0, (int)krow0, bar(DK_KV_FULL));
+    tma_load_2d(base + DkSmem::v + kSlab, &map_v, 64, (int)krow0, bar(DK_KV_FULL));
   }
   if (warp == 1) {
     tmem_alloc(base + DkSmem::misc, kTmemCols);
@@ -493,13 +498,6 @@ sparse_dkdv_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   if (warp == 0 || warp == 1) {
     const bool is_q = warp == 0;
-    if (is_q && lane == 0) {
-      mbar_arrive_expect_tx(bar(DK_KV_FULL), 4 * kSlab);
-      tma_load_2d(base + DkSmem::k, &map_k, 0, (int)krow0, bar(DK_KV_FULL));
-      tma_load_2d(base + DkSmem::k + kSlab, &map_k, 64, (int)krow0, bar(DK_KV_FULL));
-      tma_load_2d(base + DkSmem::v, &map_v, 0, (int)krow0, bar(DK_KV_FULL));
-      tma_load_2d(base + DkSmem::v + kSlab, &map_v, 64, (int)krow0, bar(DK_KV_FULL));
-    }
     const int which = lane & 1, dhalf = (lane >> 1) & 1;
     const CUtensorMap* map = is_q ? &map_q : &map_do;
     const int full0 = is_q ? DK_Q_FULL : DK_DO_FULL, empty0 = is_q ? DK_Q_EMPTY : DK_DO_EMPTY;
