@@ -38,9 +38,12 @@ def _no_device_timeouts():
     assert _lib.device_status() == 0
 
 
+_DT = torch.bfloat16      # element type of the generated tensors; one test switches it to fp16
+
+
 def _randn(shape, seed, scale=1.0):
     g = torch.Generator(device=DEV).manual_seed(seed)
-    return (torch.randn(shape, device=DEV, generator=g) * scale).to(torch.bfloat16)
+    return (torch.randn(shape, device=DEV, generator=g) * scale).to(_DT)
 
 
 def _rows(blocks, be):
@@ -154,6 +157,26 @@ def test_explicit_zipf_routes_92k_tokens_block64_topk180():
     wc = torch.stack([torch.bincount(selected[0, h].reshape(-1).long(), minlength=nb) for h in range(H)])
     assert torch.equal(counts[0].long(), wc)
     assert torch.equal(offsets[0].long(), wc.cumsum(-1) - wc)
+
+
+@pytest.mark.parametrize("be,tk,dtype", [(64, 180, torch.float16), (128, 90, torch.bfloat16)])
+def test_explicit_zipf_routes_92k_tokens_fp16_and_128_token_blocks(be, tk, dtype, monkeypatch):
+    """The same size through the other instantiations of the tensor path: fp16 inputs (90 pairs per query CTA with P
+    kept inside fp16's range by the redo rule), and blocks of 128 tokens (two 64-token tiles per block, 720 blocks)."""
+    import sys
+    monkeypatch.setattr(sys.modules[__name__], "_DT", dtype)
+    B, H, L, D = 1, 2, 92160, 128
+    nb = L // be
+    q, k, v, dout = (_randn((B, H, L, D), 500 + i) for i in range(4))
+    selected = _zipf_routes(H, nb, nb, tk, 17)
+    kv_sizes = torch.full((nb,), be)
+    kv_sizes[3], kv_sizes[nb // 2] = be // 3, be - 1
+    out, lse, dq, dk, dv = _run_fine(q, k, v, dout, selected, kv_sizes, be)
+    assert out.dtype == dtype
+    for t in (out, dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+    _check_fine_branch(q, k, v, dout, selected, kv_sizes, be, out, lse, dq, dk, dv,
+                       q_blocks=_pick_blocks(nb, 5, 2), key_head=0, key_extra=1, seed=4)
 
 
 def test_whole_operator_92k_tokens_block64_topk180():
