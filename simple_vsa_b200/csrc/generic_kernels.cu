@@ -1056,17 +1056,21 @@ int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_o
 template <typename W>
 __global__ void __launch_bounds__(256) gather_rows_kernel(const W* __restrict__ src, const int32_t* __restrict__ map,
                                                           W* __restrict__ dst, long long src_rows, long long dst_rows,
-                                                          int words_per_row, long long total_words) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_words;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long row_all = i / words_per_row;
-    const int w = (int)(i - row_all * words_per_row);
+                                                          int words_per_row, long long total_rows) {
+  // blockDim = (tx, ty): ty destination rows per block, tx threads walking the words of a row, so that the row
+  // index is split once per row and thread and the inner loop has no division
+  for (long long row_all = (long long)blockIdx.x * blockDim.y + threadIdx.y; row_all < total_rows;
+       row_all += (long long)gridDim.x * blockDim.y) {
     const long long b = row_all / dst_rows;
     const long long r = row_all - b * dst_rows;
     const int m = map[r];
-    W val{};
-    if (m >= 0) val = src[(b * src_rows + m) * words_per_row + w];
-    dst[i] = val;
+    W* d = dst + row_all * words_per_row;
+    if (m >= 0) {
+      const W* s = src + (b * src_rows + m) * words_per_row;
+      for (int w = threadIdx.x; w < words_per_row; w += blockDim.x) d[w] = s[w];
+    } else {
+      for (int w = threadIdx.x; w < words_per_row; w += blockDim.x) d[w] = W{};
+    }
   }
 }
 
@@ -1079,15 +1083,18 @@ int gather_rows(const void* src, const int32_t* map, void* dst, int64_t batch, i
   const int unit = wide ? 16 : (row_bytes % 4 == 0 ? 4 : 2);
   const long long wpr = row_bytes / unit;
   if (wpr > 0x7fffffffLL) return fail(VSA_ERR_UNSUPPORTED, "gather rows: row too long");
-  const long long total = batch * dst_rows * wpr;
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  const long long rows = batch * dst_rows;
+  unsigned tx = 1;
+  while (tx < 256 && tx < wpr) tx <<= 1;
+  const dim3 block(tx, 256 / tx);
+  long long blocks = (rows + block.y - 1) / block.y;
+  if (blocks > 148LL * 64) blocks = 148LL * 64;
   if (unit == 16)
-    gather_rows_kernel<uint4><<<(unsigned)blocks, 256, 0, st>>>((const uint4*)src, map, (uint4*)dst, src_rows, dst_rows, (int)wpr, total);
+    gather_rows_kernel<uint4><<<(unsigned)blocks, block, 0, st>>>((const uint4*)src, map, (uint4*)dst, src_rows, dst_rows, (int)wpr, rows);
   else if (unit == 4)
-    gather_rows_kernel<uint32_t><<<(unsigned)blocks, 256, 0, st>>>((const uint32_t*)src, map, (uint32_t*)dst, src_rows, dst_rows, (int)wpr, total);
+    gather_rows_kernel<uint32_t><<<(unsigned)blocks, block, 0, st>>>((const uint32_t*)src, map, (uint32_t*)dst, src_rows, dst_rows, (int)wpr, rows);
   else
-    gather_rows_kernel<uint16_t><<<(unsigned)blocks, 256, 0, st>>>((const uint16_t*)src, map, (uint16_t*)dst, src_rows, dst_rows, (int)wpr, total);
+    gather_rows_kernel<uint16_t><<<(unsigned)blocks, block, 0, st>>>((const uint16_t*)src, map, (uint16_t*)dst, src_rows, dst_rows, (int)wpr, rows);
   return check_launch("gather_rows_kernel");
 }
 
