@@ -253,6 +253,7 @@ using elem_t = __nv_bfloat16;
 constexpr uint32_t kInFmt = 1u;
 constexpr CUtensorMapDataType kTmaElem = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
 constexpr int kDtypeCode = VSA_BF16;
+constexpr float kShiftBias = 0.f;
 #include "sparse_umma_typed.inl"
 }  // namespace tc_bf16
 namespace tc_f16 {
@@ -260,6 +261,12 @@ using elem_t = __half;
 constexpr uint32_t kInFmt = 0u;
 constexpr CUtensorMapDataType kTmaElem = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 constexpr int kDtypeCode = VSA_F16;
+// The forward's fixed softmax shift is the first pair's column maximum plus this many binades, so that P = 2^(s - shift)
+// of the first pair tops out at 2^-4: fp16 then holds later scores up to 20 binades (13.9 nats) above the first pair's
+// maximum before P overflows (and the tile goes to the exact kernel) and keeps scores down to 20 binades below it --
+// the middle of fp16's 2^-24 .. 2^16 instead of its top.  The row sum uses the same shift, so O/l and the saved
+// statistic are unchanged.  bf16 has 2^127 above the first pair's maximum and needs no bias.
+constexpr float kShiftBias = 4.f;
 #include "sparse_umma_typed.inl"
 }  // namespace tc_f16
 

@@ -282,7 +282,7 @@ sparse_fwd_umma_persistent_kernel(const __grid_constant__ CUtensorMap map_q, con
             if (lane == 0) m_warp[quarter * 64 + c0 + i] = x;
           }
           named_barrier(1, kEwThreads);
-          if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st]));
+          if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st])) + kShiftBias;
           named_barrier(1, kEwThreads);
         }
         // padding rows of a ragged tile (and the repeated tile of an odd tail): whatever sits in V there

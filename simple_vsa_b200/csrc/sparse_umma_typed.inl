@@ -4,6 +4,7 @@
 //     kInFmt      its code in the tcgen05 instruction descriptor (1 = bf16, 0 = fp16),
 //     kTmaElem    its CUtensorMapDataType,
 //     kDtypeCode  its VSA_* dtype code,
+//     kShiftBias  binades added to the forward's fixed softmax shift (centres P in the type's exponent range),
 // and includes this file; everything else (tiling, barriers, pipelines, tensor-memory use) is the same for both.
 int make_map(CUtensorMap* map, const void* ptr, int64_t rows, const char* what, int cols = kD) {
   return make_map_of(map, kTmaElem, ptr, rows, what, cols);
@@ -255,7 +256,7 @@ sparse_fwd_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (lane == 0) m_warp[quarter * 64 + c0 + j] = x;
         }
         named_barrier(1, kEwThreads);
-        if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st]));
+        if (st < 64) m_col[st] = fmaxf(fmaxf(m_warp[st], m_warp[64 + st]), fmaxf(m_warp[128 + st], m_warp[192 + st])) + kShiftBias;
         named_barrier(1, kEwThreads);
       }
       // padding rows of a ragged tile (and the repeated tile of an odd tail): whatever sits in V there

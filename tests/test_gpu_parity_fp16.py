@@ -84,11 +84,12 @@ def test_fp16_whole_operator_with_gate_matches_oracle():
         _assert_close(leaf.grad, oleaf.grad, atol=3e-2, rtol=3e-2)
 
 
-@pytest.mark.parametrize("factor", [6.0, 40.0])
+@pytest.mark.parametrize("factor", [3.5, 6.0, 40.0])
 def test_fp16_forward_out_of_range_tiles_are_recomputed_exactly(factor):
-    """A later key block scores far above the first pair.  With factor 6 the gap (~30-40 in log2 units) fits bf16
-    and fp32 but not fp16, whose P = 2^(s-m) overflows at 2^16; with factor 40 it overflows everything.  Either
-    way the tile must be handed to the exact kernel and match the oracle, log-sum-exp included."""
+    """A later key block scores far above the first pair.  Factor 3.5 gives a gap of ~18 binades: above 2^16, inside
+    the 20 binades the fp16 forward leaves above the first pair's maximum (its softmax shift is biased by four
+    binades).  With factor 6 the gap (~30-40 binades) fits bf16 and fp32 but not fp16; with factor 40 it overflows
+    everything.  Whatever the tile's route through the kernels, it must match the oracle, log-sum-exp included."""
     torch.manual_seed(161)
     be, nb, D = 64, 8, 128
     q, k, v = (torch.randn(1, 1, be * nb, D).to(F16) for _ in range(3))
