@@ -652,15 +652,34 @@ __global__ void __launch_bounds__(256) topk_warp_kernel(const T* __restrict__ sc
   for (int j = 0; j < SLOTS; ++j) above += key[j] > thr ? 1 : 0;
   above = __reduce_add_sync(0xffffffffu, above);
   const int take_eq = topk - above;            // ids equal to the threshold that are kept (lowest first)
+  // The best-scoring block goes first (lowest id among equals, so it is in the kept set), the rest follow in
+  // ascending id order.  The order of a route does not change what is attended to, but the fine forward takes its
+  // softmax shift from the first pair of tiles it meets: with the best block there the shift is next to the row
+  // maximum, P stays near or below 1, and the out-of-range recomputation stays the exception on real score
+  // distributions (above all for fp16, whose P overflows 2^16).
+  uint32_t best = 0;
+#pragma unroll
+  for (int j = 0; j < SLOTS; ++j) best = key[j] > best ? key[j] : best;      // slots beyond n hold 0
+  best = __reduce_max_sync(0xffffffffu, best);
+  int first = 0x7fffffff;
+#pragma unroll
+  for (int j = SLOTS - 1; j >= 0; --j) {
+    const int i = j * 32 + lane;
+    first = (key[j] == best && i < n) ? i : first;                         // descending j: the lowest id wins
+  }
+  const int lead = __reduce_min_sync(0xffffffffu, first);
+  if (lane == 0) out[0] = lead;
+  const int n_lead = 1;
   const unsigned lt = (1u << lane) - 1u;
-  int written = 0, eq_seen = 0;
+  int written = n_lead, eq_seen = 0;
 #pragma unroll
   for (int j = 0; j < SLOTS; ++j) {
     const int i = j * 32 + lane;
     const bool gt = key[j] > thr;
     const bool eq = key[j] == thr && i < n;
     const unsigned eq_b = __ballot_sync(0xffffffffu, eq);
-    const bool take = gt || (eq && eq_seen + __popc(eq_b & lt) < take_eq);
+    const bool kept = gt || (eq && eq_seen + __popc(eq_b & lt) < take_eq);
+    const bool take = kept && i != lead;
     const unsigned tk_b = __ballot_sync(0xffffffffu, take);
     const int pos = written + __popc(tk_b & lt);
     if (take && pos < topk) out[pos] = i;

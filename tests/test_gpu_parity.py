@@ -221,6 +221,27 @@ def test_topk_kernel_with_ties(dtype):
         assert taken[:n_taken].all() and not taken[n_taken:].any()
 
 
+@pytest.mark.parametrize("n,k", [(1440, 180), (256, 32), (40, 1), (8, 8)])
+def test_topk_routes_start_with_the_best_block(n, k):
+    """Order of a route: the best-scoring block (lowest id among equals), then the rest by ascending id.  The fine
+    forward takes its softmax shift from the first pair of tiles it meets, so the best block leads."""
+    from simple_vsa_b200 import _lib
+    torch.manual_seed(4)
+    rows = 37
+    scores = (torch.randn(rows, n) * 0.05).to(torch.bfloat16).to(DEV)
+    scores[5, :] = 0.25                                      # a row of equal scores
+    sel = torch.empty(rows, k, dtype=torch.int32, device=DEV)
+    _lib.call("vsa_topk", scores.data_ptr(), sel.data_ptr(), rows, n, k, _lib.VSA_BF16,
+              torch.cuda.current_stream().cuda_stream)
+    sel = sel.cpu().long()
+    s = scores.float().cpu()
+    for r in range(rows):
+        assert len(set(sel[r].tolist())) == k
+        assert int(sel[r, 0]) == int((s[r] == float(s[r].max())).nonzero()[0])
+        tail = sel[r, 1:]
+        assert torch.equal(tail, tail.sort().values)
+
+
 # ---------------------------------------------------------------------------------------------
 # route-explicit fine attention against the reference's vectors
 # ---------------------------------------------------------------------------------------------
