@@ -659,12 +659,12 @@ def test_a_large_problem_off_the_tensor_path_warns_once():
 
 
 def test_compression_gate_writes_the_operator_layout_without_a_transposing_copy():
-    """bf16, 4 heads of 128: the gate comes out dense in [B,H,S,D] (the operator's ``_dense`` then copies nothing),
+    """bf16, 8 heads of 128: the gate comes out dense in [B,H,S,D] (the operator's ``_dense`` then copies nothing),
     equals the reference form Linear(x).view(B,S,H,D).transpose(1,2) up to one bf16 rounding of the same fp32 sums,
     and the batched GEMM does not materialise the hidden states once per head."""
     V = _V()
     torch.manual_seed(5)
-    B, H, S, D = 2, 4, 4096, 128
+    B, H, S, D = 2, 8, 16384, 128
     dim = H * D
     layer = V.CompressionGate(dim, H).to(DEV).to(torch.bfloat16)
     x = (torch.randn(B, S, dim, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
@@ -675,7 +675,8 @@ def test_compression_gate_writes_the_operator_layout_without_a_transposing_copy(
     torch.cuda.synchronize()
     grown = torch.cuda.max_memory_allocated() - before
     assert gate.is_contiguous() and gate.shape == (B, H, S, D)
-    assert grown < 2 * gate.numel() * 2 + (8 << 20), grown          # the output (+ library workspace), not H copies of x
+    # the output (64 MB) and at most a library workspace -- not the hidden states once per head (256 MB per batch entry)
+    assert grown < 2 * gate.numel() * 2 + (40 << 20), grown
     want = layer.to_gate_compress(x).view(B, S, H, D).transpose(1, 2)
     _assert_close(gate.detach(), want.detach(), atol=2e-2, rtol=2e-2)
     w = torch.randn_like(gate)
