@@ -67,6 +67,8 @@ WORKLOADS = {
     # the reference's own CPU-runnable case: fp32, 16 full blocks of 64, head dim 64, topk 4 (fp32 runs on the CUDA-core kernels)
     # the profiling case with blocks of 128 tokens (two 64-token tiles per block), same useful FLOPs as be 64 / topk 180
     "mid_92k_h8_be128_tk90_gate": dict(B=1, H=8, L=92160, D=128, block_size=(4, 4, 8), topk=90, gate=True),
+    # c2 at head dim 64: the warp-level (mma.sync) tensor-core kernels; VSA_B200_KERNELS=scalar times the CUDA-core ones
+    "c2_d64_16k_be64_tk32_gate": dict(B=1, H=12, L=16384, D=64, block_size=(4, 4, 4), topk=32, gate=True),
     # the profiling case in fp16: the same tcgen05 kernels instantiated for the other 16-bit input format
     "mid_92k_h8_tk180_gate_fp16": dict(B=1, H=8, L=92160, D=128, block_size=(4, 4, 4), topk=180, gate=True, dtype="f16"),
     "c1_1k_be64_tk4_fp32": dict(B=1, H=2, L=1024, D=64, block_size=(1, 1, 64), topk=4, gate=False, dtype="f32"),

@@ -19,8 +19,9 @@
  *   counts, offsets                 [BH, Kb]         int32 (CSR of key block -> query blocks)
  *   inverse                         [BH, Qb*topk]    int32 query-block ids grouped by key block
  *
- * dtype: VSA_BF16 or VSA_F16 (tensor-core kernels for D = 128 and be = 64, 128 or 256, scalar
- * kernels otherwise; the reference accepts both) or VSA_F32 (scalar kernels, the fp32
+ * dtype: VSA_BF16 or VSA_F16 (tcgen05 kernels for D = 128 and be = 64, 128 or 256, warp-level
+ * tensor-core kernels for D = 64 at those block volumes, scalar kernels otherwise; the reference
+ * accepts both) or VSA_F32 (scalar kernels, the fp32
  * validation mode).
  *
  * Each comment names the function of the reference project (path inside that
@@ -325,6 +326,12 @@ int vsa_sparse_bwd_dkdv_sharded(const void* dout, const void* q, const void* k_s
  * Replaces tile / untile: vsa/fastvideo_tiling.py:128-145. */
 int vsa_gather_rows(const void* src, const int32_t* map, void* dst,
                     int64_t batch, int64_t src_rows, int64_t dst_rows, int64_t row_bytes, void* stream);
+
+/* Which kernels the fine-attention entry points run for a shape in this process (environment switches included):
+ * 2 = tcgen05/TMA (bf16 or fp16, D = 128, be = 64, 128 or 256, topk*ceil(be/64) <= 1024), 1 = warp-level mma.sync
+ * (bf16 or fp16, D = 64 or 128, be = 64, 128 or 256), 0 = CUDA-core kernels (everything else the reference accepts,
+ * and the fp32 validation mode).  No reference counterpart: its Triton launcher has one kernel family. */
+int vsa_sparse_kernel_family(int D, int be, int topk, int dtype);
 
 /* ---- raster-order activations: the tiling front end folded into the kernels --------------------------------
  * (No single reference counterpart: the reference tiles with index ops, vsa/fastvideo_tiling.py:128-145, and model

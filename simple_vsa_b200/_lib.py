@@ -59,6 +59,7 @@ PLAIN = {"vsa_last_error_string": ([], c_char_p), "vsa_version": ([], c_int),
          "vsa_sparse_bwd_ds_supported": ([I, I, I, I], c_int),
          "vsa_sparse_sharded_supported": ([I, I, I, I], c_int),
          "vsa_sparse_raster_supported": ([I, I, I, I], c_int),
+         "vsa_sparse_kernel_family": ([I, I, I, I], c_int),
          "vsa_sparse_bwd_ds_workspace_bytes": ([L, L, I, I], c_int64)}
 
 

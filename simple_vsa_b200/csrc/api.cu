@@ -175,11 +175,11 @@ static int sparse_fwd_dispatch(const void* q, const void* k, const void* v, cons
                          out_comb);
     if (rc) return rc;
     // exact recomputation of the (normally zero) tiles the fixed-shift softmax marked as out of range
-    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, dtype, true, st, out_c,
+    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype, true, st, out_c,
                          gate, out_comb);
   }
   if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
-    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, be, topk, scale, dtype, false, st, out_c,
+    return sparse_fwd_tc(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype, false, st, out_c,
                          gate, out_comb);
   rc = sparse_fwd_scalar(q, k, v, selected, kv_sizes, out, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype, st);
   if (rc || !out_comb) return rc;
@@ -232,7 +232,7 @@ int vsa_sparse_bwd_dq(const void* dout, const void* q, const void* k, const void
     return sparse_dq_umma(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
                           dtype, (cudaStream_t)stream);
   if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
-    return sparse_dq_tc(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, be, topk, scale,
+    return sparse_dq_tc(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, D, be, topk, scale,
                         dtype, (cudaStream_t)stream);
   return sparse_dq_scalar(dout, q, k, v, out_s, lse2, selected, kv_sizes, delta, dq, BH, Lq, Lkv, D, be, topk, scale,
                           dtype, (cudaStream_t)stream);
@@ -250,7 +250,7 @@ int vsa_sparse_bwd_dkdv(const void* dout, const void* q, const void* k, const vo
     return sparse_dkdv_umma(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
                             topk, scale, dtype, (cudaStream_t)stream);
   if (!scalar_forced() && sparse_tc_eligible(D, be, dtype))
-    return sparse_dkdv_tc(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, be,
+    return sparse_dkdv_tc(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, D, be,
                           topk, scale, dtype, (cudaStream_t)stream);
   return sparse_dkdv_scalar(dout, q, k, v, lse2, delta, counts, offsets, inverse, kv_sizes, dk, dv, BH, Lq, Lkv, D, be,
                             topk, scale, dtype, (cudaStream_t)stream);
@@ -387,7 +387,7 @@ int vsa_sparse_fwd_combine_sharded(const void* q, const void* k_sh, const void* 
   rc = sparse_fwd_umma(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, st, out_c, gate,
                        out, kv_shard);
   if (rc) return rc;
-  return sparse_fwd_tc(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, true, st, out_c,
+  return sparse_fwd_tc(q, k_sh, v_sh, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype, true, st, out_c,
                        gate, out, kv_shard);
 }
 
@@ -435,6 +435,12 @@ static int check_raster(const int32_t* map, int64_t rows, int heads, int64_t BH,
   return VSA_OK;
 }
 
+int vsa_sparse_kernel_family(int D, int be, int topk, int dtype) {
+  if (scalar_forced()) return 0;
+  if (!mma_forced() && sparse_umma_eligible(D, be, dtype, topk)) return 2;
+  return sparse_tc_eligible(D, be, dtype) ? 1 : 0;
+}
+
 int vsa_sparse_raster_supported(int D, int be, int topk, int dtype) {
   return !scalar_forced() && !mma_forced() && sparse_umma_eligible(D, be, dtype, topk) ? 1 : 0;
 }
@@ -460,7 +466,7 @@ int vsa_sparse_fwd_combine_raster(const void* q, const void* k, const void* v, c
   rc = sparse_fwd_umma(q, k, v, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, st, out_c,
                        gate_raster, out_raster, 0, q_map, raster_rows, heads);
   if (rc) return rc;
-  return sparse_fwd_tc(q, k, v, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, be, topk, scale, dtype, true, st, out_c,
+  return sparse_fwd_tc(q, k, v, selected, kv_sizes, out_s, lse2, BH, Lq, Lkv, D, be, topk, scale, dtype, true, st, out_c,
                        gate_raster, out_raster, 0, q_map, raster_rows, heads);
 }
 

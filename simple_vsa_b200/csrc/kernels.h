@@ -44,24 +44,24 @@ int sparse_dkdv_scalar(const void* dout, const void* q, const void* k, const voi
                        const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
                        int topk, float scale, int dtype, cudaStream_t st);
 
-// ---- tensor-core kernels, bf16 or fp16, head dim 128, block volume 64, 128 or 256 (sparse_mma.cu) ------
+// ---- tensor-core kernels, bf16 or fp16, head dim 64 or 128, block volume 64, 128 or 256 (sparse_mma.cu) ------
 bool sparse_tc_eligible(int D, int be, int dtype);
 // redo_only: recompute only the 64-row query tiles whose first lse2 entry is NaN (the marker the
 // tcgen05 forward leaves on a tile whose fixed softmax shift ran out of range).
 // out_comb (optional): out_s + out_c[block] * gate is written there as well (gate may be null)
 // dtype: the forward also exists for fp16 (it is the exact recomputation behind the fp16 tcgen05 forward)
 int sparse_fwd_tc(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
-                  void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk, float scale,
+                  void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk, float scale,
                   int dtype, bool redo_only, cudaStream_t st, const void* out_c = nullptr, const void* gate = nullptr,
                   void* out_comb = nullptr, int64_t kv_shard = 0, const int32_t* comb_map = nullptr,
                   int64_t comb_rows = 0, int comb_heads = 1);
 int sparse_dq_tc(const void* dout, const void* q, const void* k, const void* v, const void* out_s, const float* lse2,
                  const int32_t* selected, const int32_t* kv_sizes, float* delta, void* dq, int64_t BH, int64_t Lq,
-                 int64_t Lkv, int be, int topk, float scale, int dtype, cudaStream_t st);
+                 int64_t Lkv, int D, int be, int topk, float scale, int dtype, cudaStream_t st);
 int sparse_dkdv_tc(const void* dout, const void* q, const void* k, const void* v, const float* lse2,
                    const float* delta, const int32_t* counts, const int32_t* offsets, const int32_t* inverse,
-                   const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int be, int topk,
-                   float scale, int dtype, cudaStream_t st);
+                   const int32_t* kv_sizes, void* dk, void* dv, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be,
+                   int topk, float scale, int dtype, cudaStream_t st);
 
 // ---- tcgen05 / TMA kernels, bf16 or fp16 by `dtype` (sparse_umma.cu) -----------------------------------------------------
 bool sparse_umma_eligible(int D, int be, int dtype, int topk);

@@ -322,7 +322,8 @@ int sparse_dq_from_ds_umma(const void* k, const int32_t* selected, const int32_t
 
 // ---- pooled attention on tcgen05 ---------------------------------------------------------------------------
 bool coarse_umma_eligible(int Qb, int Kb, int D, int dtype) {
-  return (dtype == VSA_BF16 || dtype == VSA_F16) && D == 128 && Qb % 8 == 0 && Kb % 8 == 0;
+  // head dim 64: the same kernel, the second 64-column box of a 128-wide tile lies outside the tensor and is zero-filled
+  return (dtype == VSA_BF16 || dtype == VSA_F16) && (D == 128 || D == 64) && Qb % 8 == 0 && Kb % 8 == 0;
 }
 
 int coarse_fwd_umma(const void* qc, const void* kc, const void* vc, void* scores, void* probs, void* out_c, int64_t BH,

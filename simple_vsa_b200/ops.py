@@ -85,12 +85,11 @@ def _warn_if_far_off_the_tensor_path(dt: int, B: int, H: int, Lq: int, D: int, b
     global _warned_slow_path
     if _warned_slow_path or 14.0 * B * H * Lq * topk * be * D < 1e11:
         return
-    if _lib.lib.vsa_sparse_sharded_supported(D, be, topk, dt):      # the tensor path's own eligibility answer
+    if _lib.lib.vsa_sparse_kernel_family(D, be, topk, dt) > 0:      # tcgen05 or warp-level tensor-core kernels
         return
     _warned_slow_path = True
-    warnings.warn("simple_vsa_b200: this shape runs on the CUDA-core validation kernels (the tensor-core path needs "
-                  "bf16 or fp16, head dim 128, block volume 64, 128 or 256, topk*ceil(block/64) <= 1024, and "
-                  "VSA_B200_KERNELS unset); expect a step hundreds of times slower per FLOP", RuntimeWarning, stacklevel=3)
+    warnings.warn("simple_vsa_b200: this shape runs on the CUDA-core validation kernels (the tensor-core paths need "
+                  "bf16 or fp16, head dim 64 or 128, block volume 64, 128 or 256, and VSA_B200_KERNELS unset or =mma); expect a step hundreds of times slower per FLOP", RuntimeWarning, stacklevel=3)
 
 
 def _dense(x: Tensor) -> Tensor:

@@ -152,6 +152,12 @@ def test_workspace_sizes_and_support_queries_need_no_gpu():
     assert lib.vsa_sparse_sharded_supported(128, 128, 513, L.VSA_BF16) == 0      # 1026 tiles: beyond the tile list
     assert lib.vsa_sparse_sharded_supported(64, 64, 4, L.VSA_BF16) == 0
     assert lib.vsa_sparse_bwd_ds_supported(128, 256, 20, L.VSA_BF16) == 1
+    # kernel families: tcgen05 (2), warp-level tensor cores (1), CUDA cores (0)
+    assert lib.vsa_sparse_kernel_family(128, 64, 180, L.VSA_BF16) == 2
+    assert lib.vsa_sparse_kernel_family(128, 64, 1025, L.VSA_BF16) == 1      # more tiles than the tcgen05 list holds
+    assert lib.vsa_sparse_kernel_family(64, 128, 8, L.VSA_F16) == 1
+    assert lib.vsa_sparse_kernel_family(64, 64, 8, L.VSA_F32) == 0
+    assert lib.vsa_sparse_kernel_family(128, 32, 8, L.VSA_BF16) == 0
     assert lib.vsa_sparse_bwd_ds_supported(128, 64, 180, L.VSA_F32) == 0
 
 

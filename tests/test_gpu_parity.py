@@ -374,6 +374,51 @@ def test_fine_attention_midsize_matches_oracle(be, nb, tk, ragged, monkeypatch):
         assert dk[0, :, be + 1:2 * be].abs().max() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("be,nb,tk", [(64, 20, 6), (128, 10, 4), (256, 6, 3)])
+def test_head_dim_64_runs_on_the_warp_level_tensor_kernels(be, nb, tk, dtype, monkeypatch):
+    """Head dim 64 (bf16 / fp16, blocks of 64, 128, 256): the mma.sync kernels instantiated for 64-wide tiles, against
+    the oracle and against the CUDA-core kernels, ragged blocks included; the whole operator (pooled branch on the
+    CUDA-core GEMMs at this head dim) with a gate as well."""
+    from simple_vsa_b200 import _lib
+    V = _V()
+    torch.manual_seed(81)
+    B, H, D = 1, 3, 64
+    L = be * nb
+    dt_code = _lib.VSA_BF16 if dtype == torch.bfloat16 else _lib.VSA_F16
+    assert _lib.lib.vsa_sparse_kernel_family(D, be, tk, dt_code) == 1
+    assert _lib.lib.vsa_sparse_kernel_family(128, be, tk, dt_code) == 2
+    assert _lib.lib.vsa_sparse_kernel_family(D, be, tk, _lib.VSA_F32) == 0
+    q, k, v, dout = (torch.randn(B, H, L, D).to(dtype) for _ in range(4))
+    sizes = torch.full((nb,), be)
+    sizes[1], sizes[nb // 2], sizes[-1] = 1, be // 2 + 3, be - 1
+    selected = _zipf_routes(B, H, nb, nb, tk, 9)
+    ol = [t.clone().requires_grad_() for t in (q, k, v)]
+    want = O.sparse_attention(*ol, selected, sizes, be, q_blocks_per_chunk=8)
+    want.backward(dout.float())
+    for mode in ("auto", "scalar"):
+        monkeypatch.setenv("VSA_B200_KERNELS", mode)
+        leaves = [t.to(DEV).requires_grad_() for t in (q, k, v)]
+        out = V.b200_sparse_attention(*leaves, selected.to(DEV), sizes, block_size=(1, 1, be))
+        out.backward(dout.to(DEV))
+        _assert_close(out, want, atol=2e-2, rtol=2e-2)
+        for leaf, oleaf in zip(leaves, ol):
+            _assert_close(leaf.grad, oleaf.grad, atol=3e-2, rtol=3e-2)
+        if mode == "auto":
+            assert leaves[1].grad[0, :, be + 1:2 * be].abs().max() == 0      # padded key rows: exactly zero
+    monkeypatch.delenv("VSA_B200_KERNELS")
+    gate = torch.sigmoid(torch.randn(B, H, L, D)).to(dtype)
+    leaves = [t.to(DEV).requires_grad_() for t in (q, k, v, gate)]
+    out, aux = V.video_sparse_attn(leaves[0], leaves[1], leaves[2], sizes, sizes, tk, (1, 1, be), leaves[3], return_aux=True)
+    out.backward(dout.to(DEV))
+    ol = [t.clone().requires_grad_() for t in (q, k, v, gate)]
+    want = O.vsa(ol[0], ol[1], ol[2], sizes, sizes, tk, (1, 1, be), ol[3], selected=aux["selected"].cpu(), q_blocks_per_chunk=8)
+    want.backward(dout)
+    _assert_close(out, want, atol=2e-2, rtol=2e-2)
+    for leaf, oleaf in zip(leaves, ol):
+        _assert_close(leaf.grad, oleaf.grad, atol=3e-2, rtol=3e-2)
+
+
 def test_hot_key_block_all_queries_route_to_block_zero():
     V = _V()
     torch.manual_seed(43)
@@ -522,12 +567,13 @@ def test_more_tiles_than_the_tcgen05_list_holds_uses_the_warp_level_kernels():
     torch.testing.assert_close(vl.grad.float(), vr.grad, atol=3e-2, rtol=3e-2)
 
 
-@pytest.mark.parametrize("Qb,Kb", [(200, 136), (8, 8), (264, 1448)])
-def test_pooled_attention_tensor_core_path_matches_scalar_path(Qb, Kb, monkeypatch):
-    """The tcgen05 pooled GEMMs (ragged M/N/K edges filled by TMA) against the CUDA-core GEMMs and torch."""
+@pytest.mark.parametrize("Qb,Kb,D", [(200, 136, 128), (8, 8, 128), (264, 1448, 128), (200, 136, 64), (256, 256, 64)])
+def test_pooled_attention_tensor_core_path_matches_scalar_path(Qb, Kb, D, monkeypatch):
+    """The tcgen05 pooled GEMMs (ragged M/N/K edges filled by TMA; head dim 64 as half-empty 128-wide tiles) against
+    the CUDA-core GEMMs and torch."""
     from simple_vsa_b200 import _lib
     torch.manual_seed(55)
-    BH, D = 3, 128
+    BH = 3
     scale = D ** -0.5
     qc, kc, vc, dco = (torch.randn(n, device=DEV).to(torch.bfloat16) for n in
                        ((BH, Qb, D), (BH, Kb, D), (BH, Kb, D), (BH, Qb, D)))
@@ -630,8 +676,9 @@ def test_compression_gate_trains_through_the_operator():
 
 
 def test_a_large_problem_off_the_tensor_path_warns_once():
-    """Head dim 64 is served by the CUDA-core kernels only; a problem of 1e11 useful FLOPs or more says so once per
-    process, a tensor-path shape and small validation-size problems never do."""
+    """fp32 (the validation mode) is served by the CUDA-core kernels only; a problem of 1e11 useful FLOPs or more says so
+    once per process; tensor-core shapes (head dim 128 on tcgen05, head dim 64 on the warp-level kernels) and small
+    validation-size problems never do."""
     import warnings
 
     from simple_vsa_b200 import ops
@@ -640,7 +687,8 @@ def test_a_large_problem_off_the_tensor_path_warns_once():
     be, tk = 64, 32
     sizes = torch.full((256,), be)
     small = [torch.randn(1, 1, 4 * be, 64, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
-    big64 = [torch.randn(1, 4, 256 * be, 64, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
+    big64 = [torch.randn(1, 4, 256 * be, 64, device=DEV, dtype=torch.float32) for _ in range(3)]
+    big64_bf16 = [t.to(torch.bfloat16) for t in big64]
     big128 = [torch.randn(1, 2, 256 * be, 128, device=DEV, dtype=torch.bfloat16) for _ in range(3)]
     ops._warned_slow_path = False
     with warnings.catch_warnings():
@@ -648,6 +696,7 @@ def test_a_large_problem_off_the_tensor_path_warns_once():
         with torch.no_grad():
             V.video_sparse_attn(*small, sizes[:4], sizes[:4], 2, (4, 4, 4))
             V.video_sparse_attn(*big128, sizes, sizes, tk, (4, 4, 4))
+            V.video_sparse_attn(*big64_bf16, sizes, sizes, tk, (4, 4, 4))
     with pytest.warns(RuntimeWarning, match="CUDA-core validation kernels"), torch.no_grad():
         out = V.video_sparse_attn(*big64, sizes, sizes, tk, (4, 4, 4))
     assert torch.isfinite(out.float()).all()
