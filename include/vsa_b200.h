@@ -359,6 +359,14 @@ int vsa_sparse_fwd_combine_raster(const void* q, const void* k, const void* v,
                                   int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                                   float scale, int dtype, void* stream);
 
+/* vsa_combine_bwd for raster-order activations: dout_raster and gate_raster are [B, raster_rows, heads, D]; dgate is
+ * written in that layout; dout_tiled [BH, Lq, D] receives dout in tile order (zeros in padding rows) for the two
+ * entry points below.  gate_raster and dgate_raster may both be NULL.  Any dtype and head dim the plain form takes. */
+int vsa_combine_bwd_raster(const void* dout_raster, const void* gate_raster, const void* out_c,
+                           void* d_out_c, void* dgate_raster, void* dout_tiled,
+                           const int32_t* q_map, int64_t raster_rows, int heads,
+                           int64_t BH, int64_t Lq, int D, int be, int dtype, void* stream);
+
 int vsa_sparse_bwd_dq_raster(const void* dout, const void* q, const void* k, const void* v,
                              const void* out_s, const float* lse2,
                              const int32_t* selected, const int32_t* kv_sizes,

@@ -46,6 +46,7 @@ SIGNATURES = {
     "vsa_gather_rows": [P, P, P, L, L, L, L, P],
     "vsa_gather_rows_heads": [P, P, P, L, I, L, L, L, I, P],
     "vsa_sparse_fwd_combine_raster": [P, P, P, P, P, P, P, P, P, P, P, L, I, L, L, L, I, I, I, F, I, P],
+    "vsa_combine_bwd_raster": [P, P, P, P, P, P, P, L, I, L, L, I, I, I, P],
     "vsa_sparse_bwd_dq_raster": [P, P, P, P, P, P, P, P, P, P, P, P, P, L, I, L, L, L, I, I, I, F, I, P],
     "vsa_sparse_bwd_dkdv_raster": [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, I, L, L, L, I, I, I, F, I, P],
     "vsa_selftest_umma": [P, P, P, I, P],

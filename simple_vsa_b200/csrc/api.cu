@@ -452,6 +452,19 @@ int vsa_gather_rows_heads(const void* src, const int32_t* map, void* dst, int64_
   return gather_rows_heads(src, map, dst, batch, heads, src_rows, dst_rows, row_bytes, to_tiled != 0, (cudaStream_t)stream);
 }
 
+int vsa_combine_bwd_raster(const void* dout_raster, const void* gate_raster, const void* out_c, void* d_out_c,
+                           void* dgate_raster, void* dout_tiled, const int32_t* q_map, int64_t raster_rows, int heads,
+                           int64_t BH, int64_t Lq, int D, int be, int dtype, void* stream) {
+  int rc = check_dtype(dtype);
+  if (rc) return rc;
+  VSA_REQUIRE(dout_raster && out_c && d_out_c && dout_tiled && q_map, "combine backward (raster): null pointer");
+  VSA_REQUIRE((gate_raster == nullptr) == (dgate_raster == nullptr), "combine backward (raster): give gate and dgate together, or neither");
+  VSA_REQUIRE(BH >= 0 && Lq >= 0 && D >= 1 && be >= 1 && Lq % be == 0 && heads >= 1 && BH % heads == 0 && raster_rows >= 0,
+              "combine backward (raster): bad extents");
+  return combine_bwd_raster(dout_raster, gate_raster, out_c, d_out_c, dgate_raster, dout_tiled, q_map, raster_rows, heads, BH,
+                            Lq, D, be, dtype, (cudaStream_t)stream);
+}
+
 int vsa_sparse_fwd_combine_raster(const void* q, const void* k, const void* v, const int32_t* selected,
                                   const int32_t* kv_sizes, void* out_s, float* lse2, const void* out_c,
                                   const void* gate_raster, void* out_raster, const int32_t* q_map, int64_t raster_rows,

@@ -1066,6 +1066,95 @@ int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_o
   });
 }
 
+// Combine backward for raster-order activations, with the tile-order copy of dout as a by-product.  dout and the
+// gate are read at each token's raster row ([B][S][H][D], see RasterMap), dgate is written there, and every row of
+// dout is also stored in tile order ([BH][Lq][D], zeros in the padding rows) for the TMA loads of the fine backward:
+// one pass instead of two gathers, the combine backward and an un-tiling of dgate.
+template <typename T, bool GATE>
+__global__ void __launch_bounds__(128) combine_bwd_raster_kernel(const T* __restrict__ dout_raster, const T* __restrict__ gate_raster,
+                                                                 const T* __restrict__ out_c, T* __restrict__ d_out_c,
+                                                                 T* __restrict__ dgate_raster, T* __restrict__ dout_tiled,
+                                                                 RasterMap rm, int blocks_per_slice, int D, int be) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ __align__(16) float part_sm[128 * VEC];     // [row group][D] partial sums
+  const long long blk = blockIdx.x;
+  const long long bh = blk / blocks_per_slice;
+  const long long token0 = (blk - bh * blocks_per_slice) * (long long)be;
+  T* t_do = dout_tiled + blk * (long long)be * D;
+  const int cpr = D / VEC;
+  const int rows_per_pass = blockDim.x / cpr;
+  const int chunk = threadIdx.x % cpr;
+  const int rgrp = threadIdx.x / cpr;
+  if (rgrp < rows_per_pass) {
+    float cvec[VEC], part[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      cvec[i] = Elem<T>::ld(out_c + blk * D + chunk * VEC + i);
+      part[i] = 0.f;
+    }
+#pragma unroll 4
+    for (int r = rgrp; r < be; r += rows_per_pass) {
+      const long long rrow = raster_row(rm, bh, token0 + r);
+      uint4 d_raw = make_uint4(0, 0, 0, 0);
+      if (rrow >= 0) {
+        const long long roff = rrow * D + chunk * VEC;
+        d_raw = *reinterpret_cast<const uint4*>(dout_raster + roff);
+        const T* de = reinterpret_cast<const T*>(&d_raw);
+        if (GATE) {
+          const uint4 g_raw = *reinterpret_cast<const uint4*>(gate_raster + roff);
+          const T* ge = reinterpret_cast<const T*>(&g_raw);
+          uint4 o_raw;
+          T* oe = reinterpret_cast<T*>(&o_raw);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const float dv = Elem<T>::ld(de + i);
+            part[i] += dv * Elem<T>::ld(ge + i);
+            Elem<T>::st(oe + i, dv * cvec[i]);
+          }
+          if (dgate_raster) *reinterpret_cast<uint4*>(dgate_raster + roff) = o_raw;
+        } else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) part[i] += Elem<T>::ld(de + i);
+        }
+      }
+      *reinterpret_cast<uint4*>(t_do + (long long)r * D + chunk * VEC) = d_raw;
+    }
+    float* dst = part_sm + rgrp * D + chunk * VEC;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) dst[i] = part[i];
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float sum = 0.f;
+    for (int g = 0; g < rows_per_pass; ++g) sum += part_sm[g * D + d];     // fixed order: deterministic
+    Elem<T>::st(d_out_c + blk * D + d, sum);
+  }
+}
+
+int combine_bwd_raster(const void* dout_raster, const void* gate_raster, const void* out_c, void* d_out_c,
+                       void* dgate_raster, void* dout_tiled, const int32_t* map, int64_t raster_rows, int heads,
+                       int64_t BH, int64_t Lq, int D, int be, int dtype, cudaStream_t st) {
+  const int vec = elems_per_16_bytes(dtype);
+  if (D % vec != 0 || D / vec > 128 || D > 256)
+    return fail(VSA_ERR_UNSUPPORTED, "combine backward (raster): head dim %d must be a multiple of %d and <= 256", D, vec);
+  const long long blocks = BH * (Lq / be);
+  if (blocks == 0) return VSA_OK;
+  if (blocks > 0x7fffffffLL || BH > 65535) return fail(VSA_ERR_UNSUPPORTED, "combine backward (raster): too many blocks or slices");
+  const RasterMap rm{map, (long long)raster_rows, heads};
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = VSA_TAG_TYPE(tag);
+    if (gate_raster)
+      combine_bwd_raster_kernel<T, true><<<(unsigned)blocks, 128, 0, st>>>((const T*)dout_raster, (const T*)gate_raster, (const T*)out_c,
+                                                                          (T*)d_out_c, (T*)dgate_raster, (T*)dout_tiled, rm,
+                                                                          (int)(Lq / be), D, be);
+    else
+      combine_bwd_raster_kernel<T, false><<<(unsigned)blocks, 128, 0, st>>>((const T*)dout_raster, nullptr, (const T*)out_c,
+                                                                           (T*)d_out_c, nullptr, (T*)dout_tiled, rm,
+                                                                           (int)(Lq / be), D, be);
+    return check_launch("combine_bwd_raster_kernel");
+  });
+}
+
 // =========================================================================================
 // Row gather with zero fill: dst[b, r, :] = map[r] >= 0 ? src[b, map[r], :] : 0.
 // One kernel serves both directions of the 3-D tiling front end (vsa/fastvideo_tiling.py:128-145 of

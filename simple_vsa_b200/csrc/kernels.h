@@ -32,6 +32,10 @@ int combine_fwd(const void* out_s, const void* out_c, const void* gate, void* ou
                 int be, int dtype, cudaStream_t st);
 int combine_bwd(const void* dout, const void* gate, const void* out_c, void* d_out_c, void* dgate, int64_t BH,
                 int64_t Lq, int D, int be, int dtype, cudaStream_t st);
+// combine backward reading dout and the gate, and writing dgate, at raster rows; also stores dout in tile order
+int combine_bwd_raster(const void* dout_raster, const void* gate_raster, const void* out_c, void* d_out_c,
+                       void* dgate_raster, void* dout_tiled, const int32_t* map, int64_t raster_rows, int heads,
+                       int64_t BH, int64_t Lq, int D, int be, int dtype, cudaStream_t st);
 int sparse_fwd_scalar(const void* q, const void* k, const void* v, const int32_t* selected, const int32_t* kv_sizes,
                       void* out, float* lse2, int64_t BH, int64_t Lq, int64_t Lkv, int D, int be, int topk,
                       float scale, int dtype, cudaStream_t st);

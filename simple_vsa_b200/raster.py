@@ -8,8 +8,9 @@ raster order.  The reference path around the operator is ``tile`` (index gather 
 Here every operand is made in ONE pass (``vsa_gather_rows_heads``: gather + head transpose + zero padding, needed
 because TMA reads 64-token tiles as contiguous rows), and nothing is moved back: the forward kernel reads the gate and
 writes the combined output at each token's raster row, and the dQ and dK/dV kernels write the gradients there too.
-Per training step that is 5 layout passes (q, k, v, dout, and the gate for the combine backward) plus one for
-dgate, instead of 18 copies; for inference 3 instead of 10.
+The backward's first kernel (combine backward) reads dout and the gate at raster rows, writes dgate there and leaves
+the tile-order copy of dout the TMA loads need as a by-product.  Per training step that is 3 layout passes (q, k,
+v) and no other tensor-sized copy, instead of 18; for inference 3 instead of 10.
 
 Tensor path only (bf16/fp16, head dim 128, block volume 64, 128 or 256); other CUDA shapes take the two-step form
 with the same numbers.
@@ -88,14 +89,13 @@ class _RasterVideoSparseAttention(torch.autograd.Function):
         with torch.cuda.device(qt.device):
             dt = ops._check_device_dtype(qt, kt, vt)
             st = ops._stream(qt.device)
-            dout_t = _gather_heads(dout, tile_map, L, True)
-            gate_t = _gather_heads(gate, tile_map, L, True) if gate is not None else None
+            # one pass: dout and the gate read at raster rows, dgate written there, dout stored in tile order for TMA
+            dout = ops._dense(dout)
+            dout_t = torch.empty_like(qt)
             d_out_c = torch.empty_like(out_c)
-            dgate_t = torch.empty_like(gate_t) if gate is not None else None
-            call("vsa_combine_bwd", dout_t.data_ptr(), ops._ptr(gate_t), out_c.data_ptr(), d_out_c.data_ptr(),
-                 ops._ptr(dgate_t), B * H, L, D, be, dt, st)
-            dgate = _gather_heads(dgate_t, untile_map, S, False) if gate is not None else None
-            del gate_t, dgate_t
+            dgate = torch.empty_like(gate) if gate is not None else None
+            call("vsa_combine_bwd_raster", dout.data_ptr(), ops._ptr(gate), out_c.data_ptr(), d_out_c.data_ptr(),
+                 ops._ptr(dgate), dout_t.data_ptr(), tile_map.data_ptr(), S, H, B * H, L, D, be, dt, st)
             ds_ws = torch.empty_like(probs)
             rowdot = torch.empty((B, H, nb), device=qt.device, dtype=torch.float32)
             dqc, dkc, dvc = torch.empty_like(qc), torch.empty_like(kc), torch.empty_like(vc)
