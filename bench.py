@@ -715,7 +715,7 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=2)
     ap.add_argument("--no-gpu-reference", action="store_true",
                     help="skip timing the installed reference copy's Triton kernels after the own run (1 GPU only)")
-    ap.add_argument("--e2e-chunk", type=int, default=4, help="(batch,head) slices per pipelined chunk of the host-resident step")
+    ap.add_argument("--e2e-chunk", type=int, default=8, help="(batch,head) slices per pipelined chunk of the host-resident step")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
