@@ -621,9 +621,13 @@ template <typename T> struct KeyBits { static constexpr int low = 0; };
 template <> struct KeyBits<__nv_bfloat16> { static constexpr int low = 16; };
 template <> struct KeyBits<__half> { static constexpr int low = 13; };
 
-template <typename T, int SLOTS>
+// VEC = 1: lane l holds keys l, l + 32, ... (any row length and alignment).  VEC = 16 / sizeof(T): lane l holds VEC
+// consecutive keys per 16-byte load, slot j <-> key ((j / VEC) * 32 + l) * VEC + j % VEC; eight (four) times fewer
+// load instructions, each a full 512-byte warp access.  Needs rows that start on 16 bytes (n a multiple of VEC).
+template <typename T, int SLOTS, int VEC>
 __global__ void __launch_bounds__(256) topk_warp_kernel(const T* __restrict__ scores, int32_t* __restrict__ selected,
                                                         long long rows, int n, int topk) {
+  static_assert(SLOTS % VEC == 0, "slots come in groups of VEC");
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -631,11 +635,24 @@ __global__ void __launch_bounds__(256) topk_warp_kernel(const T* __restrict__ sc
   int32_t* out = selected + row * topk;
   constexpr int kLow = KeyBits<T>::low;
   constexpr uint32_t kMask = kLow ? ~((1u << kLow) - 1u) : 0xffffffffu;
+  auto id_of = [&](int j) -> int { return ((j / VEC) * 32 + lane) * VEC + (j % VEC); };
   uint32_t key[SLOTS];
+  if (VEC == 1) {
 #pragma unroll
-  for (int j = 0; j < SLOTS; ++j) {
-    const int i = j * 32 + lane;
-    key[j] = i < n ? (order_key(Elem<T>::ld(s + i)) & kMask) : 0u;     // 0 sorts below every candidate
+    for (int j = 0; j < SLOTS; ++j) {
+      const int i = id_of(j);
+      key[j] = i < n ? (order_key(Elem<T>::ld(s + i)) & kMask) : 0u;     // 0 sorts below every candidate
+    }
+  } else {
+#pragma unroll
+    for (int g = 0; g < SLOTS / VEC; ++g) {
+      const int i0 = (g * 32 + lane) * VEC;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (i0 < n) raw = *reinterpret_cast<const uint4*>(s + i0);         // n is a multiple of VEC: all or nothing
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int x = 0; x < VEC; ++x) key[g * VEC + x] = i0 < n ? (order_key(Elem<T>::ld(e + x)) & kMask) : 0u;
+    }
   }
   uint32_t thr = 0;
 #pragma unroll 1
@@ -664,27 +681,51 @@ __global__ void __launch_bounds__(256) topk_warp_kernel(const T* __restrict__ sc
   int first = 0x7fffffff;
 #pragma unroll
   for (int j = SLOTS - 1; j >= 0; --j) {
-    const int i = j * 32 + lane;
-    first = (key[j] == best && i < n) ? i : first;                         // descending j: the lowest id wins
+    const int i = id_of(j);
+    first = (key[j] == best && i < n) ? i : first;                         // ids of a lane ascend with j: the lowest wins
   }
   const int lead = __reduce_min_sync(0xffffffffu, first);
   if (lane == 0) out[0] = lead;
-  const int n_lead = 1;
   const unsigned lt = (1u << lane) - 1u;
-  int written = n_lead, eq_seen = 0;
+  int written = 1, eq_seen = 0;
+  // groups of VEC slots; inside a group ids ascend by (lane, slot), so an element's rank is the count over lower lanes
+  // (all slots of the group) plus the count over its own earlier slots
 #pragma unroll
-  for (int j = 0; j < SLOTS; ++j) {
-    const int i = j * 32 + lane;
-    const bool gt = key[j] > thr;
-    const bool eq = key[j] == thr && i < n;
-    const unsigned eq_b = __ballot_sync(0xffffffffu, eq);
-    const bool kept = gt || (eq && eq_seen + __popc(eq_b & lt) < take_eq);
-    const bool take = kept && i != lead;
-    const unsigned tk_b = __ballot_sync(0xffffffffu, take);
-    const int pos = written + __popc(tk_b & lt);
-    if (take && pos < topk) out[pos] = i;
-    eq_seen += __popc(eq_b);
-    written += __popc(tk_b);
+  for (int g = 0; g < SLOTS / VEC; ++g) {
+    unsigned eq_b[VEC];
+    bool eq[VEC], gt[VEC];
+    int eq_lower = 0, eq_all = 0;
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) {
+      const int j = g * VEC + x;
+      gt[x] = key[j] > thr;
+      eq[x] = key[j] == thr && id_of(j) < n;
+      eq_b[x] = __ballot_sync(0xffffffffu, eq[x]);
+      eq_lower += __popc(eq_b[x] & lt);
+      eq_all += __popc(eq_b[x]);
+    }
+    bool take[VEC];
+    int tk_lower = 0, tk_all = 0, own_eq = 0;
+    unsigned tk_b[VEC];
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) {
+      const int j = g * VEC + x;
+      const bool kept = gt[x] || (eq[x] && eq_seen + eq_lower + own_eq < take_eq);
+      own_eq += eq[x] ? 1 : 0;
+      take[x] = kept && id_of(j) != lead;
+      tk_b[x] = __ballot_sync(0xffffffffu, take[x]);
+      tk_lower += __popc(tk_b[x] & lt);
+      tk_all += __popc(tk_b[x]);
+    }
+    int own_tk = 0;
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) {
+      const int pos = written + tk_lower + own_tk;
+      if (take[x] && pos < topk) out[pos] = id_of(g * VEC + x);
+      own_tk += take[x] ? 1 : 0;
+    }
+    eq_seen += eq_all;
+    written += tk_all;
   }
 }
 
@@ -696,18 +737,16 @@ int topk_select(const void* scores, int32_t* selected, int64_t rows, int Kb, int
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = VSA_TAG_TYPE(tag);
     const unsigned grid = (unsigned)((rows + 7) / 8);
-    if (Kb <= 512) {
-      topk_warp_kernel<T, 16><<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
+    constexpr int kVec = 16 / (int)sizeof(T);
+    const bool wide = Kb % kVec == 0 && reinterpret_cast<uintptr_t>(scores) % 16 == 0;
+    auto launch = [&](auto narrow, auto vector) -> int {
+      if (wide) vector<<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
+      else narrow<<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
       return check_launch("topk_warp_kernel");
-    }
-    if (Kb <= 1536) {
-      topk_warp_kernel<T, 48><<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
-      return check_launch("topk_warp_kernel");
-    }
-    if (Kb <= 3072) {
-      topk_warp_kernel<T, 96><<<grid, 256, 0, st>>>((const T*)scores, selected, rows, Kb, topk);
-      return check_launch("topk_warp_kernel");
-    }
+    };
+    if (Kb <= 512) return launch(topk_warp_kernel<T, 16, 1>, topk_warp_kernel<T, 16, kVec>);
+    if (Kb <= 1536) return launch(topk_warp_kernel<T, 48, 1>, topk_warp_kernel<T, 48, kVec>);
+    if (Kb <= 3072) return launch(topk_warp_kernel<T, 96, 1>, topk_warp_kernel<T, 96, kVec>);
     topk_kernel<T><<<(unsigned)rows, kTopkThreads, smem, st>>>((const T*)scores, selected, Kb, topk);
     return check_launch("topk_kernel");
   });
